@@ -1,0 +1,125 @@
+// Public collectives: validate, plan, launch.
+// All argument checks happen before anything is launched; count == 0 is a successful no-op; a
+// single-rank communicator degenerates to a local copy.  The planner's choice (or the forced algorithm)
+// is recorded in comm->lastAlgo.  Inside a group the call is recorded and issued by GroupEnd.
+// Parity: src/coll/coll.cc:16-106 of the reference.
+#include <cstring>
+
+#include "../comm/comm.h"
+
+using namespace mccl;
+
+namespace {
+
+mcclResult_t checkCommon(mcclComm_t comm, mcclDataType_t dt) {
+  if (comm == nullptr) return mcclInvalidArgument;
+  if (mcclDataSize(dt) == 0) return mcclInvalidArgument;
+  if (comm->aborted.load()) return mcclInvalidUsage;
+  return mcclSuccess;
+}
+
+mcclResult_t issue(mcclComm_t comm, std::function<mcclResult_t()> fn) {
+  if (groupActive()) return groupRecordColl(comm, [=]() { return commLaunch(comm, fn); });
+  return commLaunch(comm, std::move(fn));
+}
+
+}  // namespace
+
+extern "C" {
+
+mcclResult_t mcclAllReduce(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count, mcclDataType_t dt,
+                           mcclRedOp_t op, mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if ((unsigned)op >= (unsigned)mcclNumOps) MCCLFAIL(mcclInvalidArgument);
+  if (count == 0) return mcclSuccess;
+  if (sendbuff == nullptr || recvbuff == nullptr) MCCLFAIL(mcclInvalidArgument);
+  const int algo = commPickAlgo(comm, mcclCollAllReduce, count * mcclDataSize(dt), dt, op);
+  return issue(comm, [=]() -> mcclResult_t {
+    comm->lastAlgo.store(algo);
+    if (comm->cuda) return cudaCollective(comm, mcclCollAllReduce, sendbuff, recvbuff, count, dt, op, 0, algo, stream);
+    return cpuAllReduce(comm, sendbuff, recvbuff, count, dt, op, algo);
+  });
+}
+
+mcclResult_t mcclAllGather(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t sendcount, mcclDataType_t dt,
+                           mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if (sendcount == 0) return mcclSuccess;
+  if (sendbuff == nullptr || recvbuff == nullptr) MCCLFAIL(mcclInvalidArgument);
+  const int algo = commPickAlgo(comm, mcclCollAllGather, sendcount * mcclDataSize(dt) * comm->nRanks, dt, mcclSum);
+  return issue(comm, [=]() -> mcclResult_t {
+    comm->lastAlgo.store(algo);
+    if (comm->cuda) return cudaCollective(comm, mcclCollAllGather, sendbuff, recvbuff, sendcount, dt, mcclSum, 0, algo, stream);
+    return cpuAllGather(comm, sendbuff, recvbuff, sendcount, dt, algo);
+  });
+}
+
+mcclResult_t mcclReduceScatter(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t recvcount, mcclDataType_t dt,
+                               mcclRedOp_t op, mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if ((unsigned)op >= (unsigned)mcclNumOps) MCCLFAIL(mcclInvalidArgument);
+  if (recvcount == 0) return mcclSuccess;
+  if (sendbuff == nullptr || recvbuff == nullptr) MCCLFAIL(mcclInvalidArgument);
+  const int algo = commPickAlgo(comm, mcclCollReduceScatter, recvcount * mcclDataSize(dt) * comm->nRanks, dt, op);
+  return issue(comm, [=]() -> mcclResult_t {
+    comm->lastAlgo.store(algo);
+    if (comm->cuda) return cudaCollective(comm, mcclCollReduceScatter, sendbuff, recvbuff, recvcount, dt, op, 0, algo, stream);
+    return cpuReduceScatter(comm, sendbuff, recvbuff, recvcount, dt, op, algo);
+  });
+}
+
+mcclResult_t mcclBroadcast(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count, mcclDataType_t dt, int root,
+                           mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if (root < 0 || root >= comm->nRanks) MCCLFAIL(mcclInvalidArgument);
+  if (count == 0) return mcclSuccess;
+  // Only the root reads sendbuff; everyone writes recvbuff.
+  if (recvbuff == nullptr || (comm->rank == root && sendbuff == nullptr)) MCCLFAIL(mcclInvalidArgument);
+  const int algo = commPickAlgo(comm, mcclCollBroadcast, count * mcclDataSize(dt), dt, mcclSum);
+  return issue(comm, [=]() -> mcclResult_t {
+    comm->lastAlgo.store(algo);
+    if (comm->cuda) return cudaCollective(comm, mcclCollBroadcast, sendbuff, recvbuff, count, dt, mcclSum, root, algo, stream);
+    return cpuBroadcast(comm, sendbuff, recvbuff, count, dt, root, algo);
+  });
+}
+
+mcclResult_t mcclReduce(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count, mcclDataType_t dt, mcclRedOp_t op,
+                        int root, mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if ((unsigned)op >= (unsigned)mcclNumOps) MCCLFAIL(mcclInvalidArgument);
+  if (root < 0 || root >= comm->nRanks) MCCLFAIL(mcclInvalidArgument);
+  if (count == 0) return mcclSuccess;
+  // Everyone reads sendbuff; only the root writes recvbuff.
+  if (sendbuff == nullptr || (comm->rank == root && recvbuff == nullptr)) MCCLFAIL(mcclInvalidArgument);
+  const int algo = commPickAlgo(comm, mcclCollReduce, count * mcclDataSize(dt), dt, op);
+  return issue(comm, [=]() -> mcclResult_t {
+    comm->lastAlgo.store(algo);
+    if (comm->cuda) return cudaCollective(comm, mcclCollReduce, sendbuff, recvbuff, count, dt, op, root, algo, stream);
+    return cpuReduce(comm, sendbuff, recvbuff, count, dt, op, root, algo);
+  });
+}
+
+// count = elements per peer block: block p of sendbuff goes to rank p, block q of recvbuff comes from rank q.
+mcclResult_t mcclAllToAll(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count, mcclDataType_t dt,
+                          mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if (count == 0) return mcclSuccess;
+  if (sendbuff == nullptr || recvbuff == nullptr) MCCLFAIL(mcclInvalidArgument);
+  if (sendbuff == recvbuff && comm->nRanks > 1) MCCLFAIL(mcclInvalidUsage);   // blocks would overwrite each other
+  const size_t blk = count * mcclDataSize(dt);
+  if (comm->cuda) {
+    return issue(comm, [=]() -> mcclResult_t {
+      comm->lastAlgo.store(mcclAlgoOneShot);
+      return cudaCollective(comm, mcclCollAllToAll, sendbuff, recvbuff, count, dt, mcclSum, 0, mcclAlgoOneShot, stream);
+    });
+  }
+  // tcp: self copy + one grouped Send/Recv pair per peer.
+  MCCLCHECK(mcclGroupStart());
+  for (int p = 0; p < comm->nRanks; ++p) {
+    mcclSend(comm, static_cast<const char*>(sendbuff) + (size_t)p * blk, count, dt, p, stream);
+    mcclRecv(comm, static_cast<char*>(recvbuff) + (size_t)p * blk, count, dt, p, stream);
+  }
+  return mcclGroupEnd();
+}
+
+}  // extern "C"

@@ -1,0 +1,223 @@
+// Cost model and algorithm choice.
+//
+//   time_us = alpha[algo] + step[algo] * steps(algo, n) + bytes * traffic(algo, coll, n) / (1000 * bw[algo])
+//
+// steps() counts dependent link crossings, traffic() the bytes that cross a rank's busiest direction per
+// payload byte.  Unlike the reference's model (src/graph/tuning.cc:16-31), whose bandwidth term is the same
+// for ring and tree, the traffic factor differs per algorithm, which is what separates one-shot (latency
+// optimal, (n-1)x traffic) from two-shot/ring (2(n-1)/n) and NVLS (about 1: the switch reduces and
+// replicates).  alpha/step/bw start from the topology (measured where calibration ran) and can be
+// overridden from a cache file.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "graph.h"
+
+namespace mccl {
+
+static int ceilLog2(int n) { int l = 0; while ((1 << l) < n) ++l; return l; }
+
+int algoSteps(int algo, int n) {
+  if (n <= 1) return 0;
+  switch (algo) {
+    case mcclAlgoRing:    return 2 * (n - 1);
+    case mcclAlgoTree:    return 2 * ceilLog2(n);
+    case mcclAlgoOneShot: return 1;
+    case mcclAlgoTwoShot: return 2;
+    case mcclAlgoNvls:    return 2;
+    default:              return 0;
+  }
+}
+
+double algoTraffic(int algo, int coll, int n) {
+  if (n <= 1) return 0.0;
+  const double f = (double)(n - 1) / n;
+  switch (coll) {
+    case mcclCollAllReduce:
+      switch (algo) {
+        case mcclAlgoRing: case mcclAlgoTwoShot: return 2.0 * f;
+        case mcclAlgoTree:    return 2.0;
+        case mcclAlgoOneShot: return (double)(n - 1);
+        case mcclAlgoNvls:    return 1.0 + 1.0 / n;
+      }
+      break;
+    case mcclCollAllGather:      // bytes = total gathered size
+    case mcclCollReduceScatter:  // bytes = total input size
+    case mcclCollAllToAll:
+      switch (algo) {
+        case mcclAlgoTree: return 1.0 + f;        // everything through the hub
+        default:           return f;
+      }
+    case mcclCollBroadcast:
+      switch (algo) {
+        case mcclAlgoRing: return 1.0;
+        case mcclAlgoTree: return 2.0;            // an interior node forwards to two children
+        case mcclAlgoNvls: return 1.0;
+        default:           return (double)(n - 1); // root writes every peer
+      }
+    case mcclCollReduce:
+      switch (algo) {
+        case mcclAlgoRing: return f + 1.0 / n;
+        case mcclAlgoTree: return 2.0;
+        case mcclAlgoNvls: return 1.0;
+        default:           return (double)(n - 1); // root reads every peer
+      }
+  }
+  return 1.0;
+}
+
+mcclResult_t tunerInit(const TopoSystem& sys, const TopoGraph graphs[mcclNumAlgos], bool cudaTransport, TunerModel* out) {
+  if (out == nullptr) MCCLFAIL(mcclInvalidArgument);
+  (void)sys;
+  for (int a = 0; a < mcclNumAlgos; ++a) {
+    out->viable[a] = graphs[a].viable;
+    out->bw[a] = graphs[a].bw;
+    out->stepUs[a] = graphs[a].latencyUs;
+    out->alphaUs[a] = 0.f;
+  }
+  if (cudaTransport) {
+    // Fixed per-launch costs in microseconds (kernel launch + entry/exit barriers), defaults from B200
+    // measurements of this library; the per-step term adds the dependent flag crossings.
+    out->alphaUs[mcclAlgoOneShot] = 4.f;
+    out->alphaUs[mcclAlgoTwoShot] = 6.f;
+    out->alphaUs[mcclAlgoNvls] = 6.f;
+    out->alphaUs[mcclAlgoRing] = 6.f;
+    out->alphaUs[mcclAlgoTree] = 6.f;
+    // Achievable fractions of the port rate: loads/stores over NVLink carry packet headers; NVLS moves
+    // each byte once through the switch and sustains more of it.
+    out->bw[mcclAlgoTwoShot] *= 0.78f;
+    out->bw[mcclAlgoOneShot] *= 0.70f;
+    out->bw[mcclAlgoRing] *= 0.60f;
+    out->bw[mcclAlgoTree] *= 0.45f;
+    out->bw[mcclAlgoNvls] *= 0.85f;
+    out->oneShotMaxBytes = (size_t)envInt("MCCL_DIRECT_MAX_BYTES", 2 << 20);
+    out->oneShotMaxRanks = (int)envInt("MCCL_DIRECT_MAX_RANKS", 16);
+  } else {
+    out->oneShotMaxBytes = (size_t)envInt("MCCL_DIRECT_MAX_BYTES", 2 << 20);
+    out->oneShotMaxRanks = (int)envInt("MCCL_DIRECT_MAX_RANKS", 8);
+  }
+  const char* cache = envStr("MCCL_TUNER_CACHE");
+  if (cache) tunerLoadCache(out, cache);
+  return mcclSuccess;
+}
+
+mcclResult_t tunerLoadCache(TunerModel* m, const char* path) {
+  FILE* f = fopen(path, "r");
+  if (f == nullptr) return mcclSuccess;  // nothing cached yet
+  char name[32];
+  float alpha, step, bw;
+  while (fscanf(f, "%31s %f %f %f", name, &alpha, &step, &bw) == 4) {
+    for (int a = 0; a < mcclNumAlgos; ++a)
+      if (!strcmp(name, mcclAlgoStr(a))) { m->alphaUs[a] = alpha; m->stepUs[a] = step; if (bw > 0.f) m->bw[a] = bw; }
+  }
+  fclose(f);
+  return mcclSuccess;
+}
+
+mcclResult_t tunerSaveCache(const TunerModel& m, const char* path) {
+  FILE* f = fopen(path, "w");
+  if (f == nullptr) MCCLFAIL(mcclSystemError);
+  for (int a = 0; a < mcclNumAlgos; ++a) fprintf(f, "%s %g %g %g\n", mcclAlgoStr(a), m.alphaUs[a], m.stepUs[a], m.bw[a]);
+  fclose(f);
+  return mcclSuccess;
+}
+
+mcclResult_t tunerAlgoTime(const TunerModel& m, int algo, int coll, int n, size_t bytes, float* us) {
+  if (us == nullptr || (unsigned)algo >= (unsigned)mcclNumAlgos) MCCLFAIL(mcclInvalidArgument);
+  if (!m.viable[algo] || m.bw[algo] <= 0.f) { *us = INFINITY; return mcclSuccess; }
+  *us = m.alphaUs[algo] + m.stepUs[algo] * (float)algoSteps(algo, n) +
+        (float)((double)bytes * algoTraffic(algo, coll, n) / (1000.0 * m.bw[algo]));
+  return mcclSuccess;
+}
+
+bool algoSupports(int algo, int coll, int dt, int op, bool cudaTransport) {
+  if (!cudaTransport) {
+    if (algo == mcclAlgoTwoShot || algo == mcclAlgoNvls) return false;
+    if (algo == mcclAlgoOneShot) return coll != mcclCollBroadcast;   // broadcast has ring and tree only
+    return coll != mcclCollAllToAll;
+  }
+  const bool gpuType = dt == mcclFloat32 || dt == mcclFloat16 || dt == mcclBfloat16 || dt == mcclInt32 ||
+                       dt == mcclUint32 || dt == mcclInt64 || dt == mcclUint64 || dt == mcclInt8 ||
+                       dt == mcclUint8 || dt == mcclFloat64;
+  if (!gpuType) return false;
+  const bool reducing = coll == mcclCollAllReduce || coll == mcclCollReduceScatter || coll == mcclCollReduce;
+  switch (algo) {
+    case mcclAlgoNvls:
+      if (coll == mcclCollAllToAll) return false;
+      if (!reducing) return true;
+      // multimem.ld_reduce: add for f32/f16/bf16; add/min/max for 32-bit integers (min/max also 16-bit floats).
+      if (dt == mcclFloat32) return op == mcclSum || op == mcclAvg;
+      if (dt == mcclFloat16 || dt == mcclBfloat16) return op == mcclSum || op == mcclAvg || op == mcclMax || op == mcclMin;
+      if (dt == mcclInt32 || dt == mcclUint32) return op == mcclSum || op == mcclMax || op == mcclMin || op == mcclAvg;
+      return false;
+    case mcclAlgoRing: case mcclAlgoTree:
+      return coll != mcclCollAllToAll;
+    case mcclAlgoTwoShot:
+      return coll == mcclCollAllReduce;
+    case mcclAlgoOneShot:
+      return true;   // "direct": every rank reads/writes every peer once
+    default: return false;
+  }
+}
+
+mcclResult_t tunerPick(const TunerModel& m, int coll, int n, size_t bytes, int dt, int op, const int enabled[mcclNumAlgos],
+                       bool cudaTransport, int* algo) {
+  if (algo == nullptr) MCCLFAIL(mcclInvalidArgument);
+  int best = -1;
+  float bestUs = INFINITY;
+  // Ties go to the lower-numbered algorithm (ring), as in the reference.
+  for (int a = 0; a < mcclNumAlgos; ++a) {
+    if (enabled != nullptr && !enabled[a]) continue;
+    if (!m.viable[a] || !algoSupports(a, coll, dt, op, cudaTransport)) continue;
+    if (a == mcclAlgoOneShot && coll == mcclCollAllReduce &&
+        (bytes > m.oneShotMaxBytes || n > m.oneShotMaxRanks)) continue;
+    if (!cudaTransport && a == mcclAlgoOneShot && (bytes > m.oneShotMaxBytes || n > m.oneShotMaxRanks)) continue;
+    float us;
+    tunerAlgoTime(m, a, coll, n, bytes, &us);
+    if (us < bestUs) { bestUs = us; best = a; }
+  }
+  if (best < 0) {
+    // The allow-list left nothing that can run this call: fall back to anything viable rather than fail.
+    for (int a = 0; a < mcclNumAlgos && best < 0; ++a)
+      if (m.viable[a] && algoSupports(a, coll, dt, op, cudaTransport) &&
+          !(a == mcclAlgoOneShot && coll == mcclCollAllReduce && bytes > m.oneShotMaxBytes && cudaTransport)) best = a;
+  }
+  if (best < 0) MCCLFAIL(mcclInternalError);
+  *algo = best;
+  return mcclSuccess;
+}
+
+mcclResult_t parseList(const char* str, const char* const names[], int n, int* enabled) {
+  if (str == nullptr || *str == '\0') { for (int i = 0; i < n; ++i) enabled[i] = 1; return mcclSuccess; }
+  const bool invert = str[0] == '^';
+  if (invert) ++str;
+  for (int i = 0; i < n; ++i) enabled[i] = invert ? 1 : 0;
+  std::string s(str);
+  size_t pos = 0;
+  while (pos <= s.size()) {
+    size_t comma = s.find(',', pos);
+    if (comma == std::string::npos) comma = s.size();
+    std::string tok = s.substr(pos, comma - pos);
+    pos = comma + 1;
+    if (tok.empty()) continue;
+    bool known = false;
+    for (int i = 0; i < n; ++i)
+      if (!strcasecmp(tok.c_str(), names[i])) { enabled[i] = invert ? 0 : 1; known = true; }
+    if (!known) {
+      MCCL_WARN("unknown name '%s' in list '%s'", tok.c_str(), str);
+      return mcclInvalidArgument;
+    }
+  }
+  return mcclSuccess;
+}
+
+mcclResult_t getEnabledAlgos(int enabled[mcclNumAlgos]) {
+  static const char* const names[] = {"ring", "tree", "oneshot", "twoshot", "nvls"};
+  mcclResult_t rc = parseList(envStr("MCCL_ALGO"), names, mcclNumAlgos, enabled);
+  if (rc != mcclSuccess) for (int i = 0; i < mcclNumAlgos; ++i) enabled[i] = 1;
+  return mcclSuccess;
+}
+
+}  // namespace mccl

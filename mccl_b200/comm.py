@@ -1,0 +1,299 @@
+"""Python face of the C API: Communicator and free functions over numpy arrays and torch tensors.
+
+Host buffers (numpy arrays, CPU tensors) go with the "tcp" transport, CUDA tensors with "cuda"; the
+pointer, element count and dtype are taken from the object and handed to libmccl unchanged.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from contextlib import contextmanager
+from typing import Optional
+
+import numpy as np
+
+from . import _lib as L
+
+try:  # torch is optional for the tcp transport
+    import torch
+except Exception:  # pragma: no cover
+    torch = None
+
+_NP_DTYPES = {
+    np.dtype(np.int8): L.INT8, np.dtype(np.uint8): L.UINT8, np.dtype(np.int32): L.INT32,
+    np.dtype(np.uint32): L.UINT32, np.dtype(np.int64): L.INT64, np.dtype(np.uint64): L.UINT64,
+    np.dtype(np.float16): L.FLOAT16, np.dtype(np.float32): L.FLOAT32, np.dtype(np.float64): L.FLOAT64,
+}
+
+
+def _torch_dtypes():
+    return {
+        torch.int8: L.INT8, torch.uint8: L.UINT8, torch.int32: L.INT32, torch.int64: L.INT64,
+        torch.float16: L.FLOAT16, torch.bfloat16: L.BFLOAT16, torch.float32: L.FLOAT32, torch.float64: L.FLOAT64,
+        **({torch.uint32: L.UINT32, torch.uint64: L.UINT64} if hasattr(torch, "uint32") else {}),
+    }
+
+
+def _describe(buf, dtype: Optional[int] = None):
+    """(pointer, element count, mccl dtype, is_cuda) of a numpy array or torch tensor."""
+    if buf is None:
+        return None, 0, dtype, False
+    if torch is not None and isinstance(buf, torch.Tensor):
+        if not buf.is_contiguous():
+            raise ValueError("mccl needs contiguous tensors")
+        dt = dtype if dtype is not None else _torch_dtypes()[buf.dtype]
+        return buf.data_ptr(), buf.numel(), dt, buf.is_cuda
+    a = buf
+    if not isinstance(a, np.ndarray):
+        raise TypeError(f"unsupported buffer type {type(buf)}")
+    if not a.flags["C_CONTIGUOUS"]:
+        raise ValueError("mccl needs C-contiguous arrays")
+    dt = dtype if dtype is not None else _NP_DTYPES[a.dtype]
+    return a.ctypes.data, a.size, dt, False
+
+
+def _stream_of(buf, stream):
+    if stream is not None:
+        return C.c_void_p(stream if isinstance(stream, int) else stream.cuda_stream)
+    if torch is not None and isinstance(buf, torch.Tensor) and buf.is_cuda:
+        return C.c_void_p(torch.cuda.current_stream(buf.device).cuda_stream)
+    return C.c_void_p(0)
+
+
+def get_unique_id() -> bytes:
+    uid = L.UniqueId()
+    L.check(L.load().mcclGetUniqueId(C.byref(uid)), "mcclGetUniqueId")
+    return bytes(uid.internal)
+
+
+def unique_id_from_env(ip: str, port: int) -> bytes:
+    """The shared-by-convention id every rank can build from (ip, port) without talking to anyone."""
+    raw = ip.encode().ljust(64, b"\0") + int(port).to_bytes(2, "little") + b"\0" * 6 + (0).to_bytes(8, "little")
+    return raw.ljust(128, b"\0")
+
+
+def set_forced_algo(algo) -> None:
+    a = L.ALGOS[algo] if isinstance(algo, str) else int(algo)
+    L.check(L.load().mcclSetForcedAlgo(a), "mcclSetForcedAlgo")
+
+
+@contextmanager
+def forced_algo(algo):
+    set_forced_algo(algo)
+    try:
+        yield
+    finally:
+        set_forced_algo("auto")
+
+
+@contextmanager
+def group():
+    lib = L.load()
+    L.check(lib.mcclGroupStart())
+    try:
+        yield
+    except BaseException:
+        lib.mcclGroupAbort()
+        raise
+    L.check(lib.mcclGroupEnd(), "mcclGroupEnd")
+
+
+class Communicator:
+    """One rank's handle on a communicator (wraps mcclComm_t)."""
+
+    def __init__(self, n_ranks: int, unique_id: bytes, rank: int, blocking: bool = True,
+                 transport: Optional[str] = None, _handle: Optional[int] = None):
+        self._lib = L.load()
+        self._h = C.c_void_p(_handle) if _handle is not None else C.c_void_p()
+        self._transport_keepalive = transport.encode() if transport else None
+        if _handle is None:
+            uid = L.UniqueId()
+            C.memmove(C.byref(uid), unique_id, 128)
+            cfg = L.Config(1 if blocking else 0, self._transport_keepalive)
+            L.check(self._lib.mcclCommInitRankConfig(C.byref(self._h), n_ranks, uid, rank, C.byref(cfg)),
+                    "mcclCommInitRankConfig")
+        self._sym = {}
+
+    # ---- queries
+    @property
+    def handle(self) -> int:
+        return self._h.value
+
+    def _q(self, fn) -> int:
+        v = C.c_int()
+        L.check(fn(self._h, C.byref(v)))
+        return v.value
+
+    @property
+    def rank(self) -> int:
+        return self._q(self._lib.mcclCommUserRank)
+
+    @property
+    def size(self) -> int:
+        return self._q(self._lib.mcclCommCount)
+
+    @property
+    def device(self) -> int:
+        return self._q(self._lib.mcclCommDevice)
+
+    @property
+    def transport(self) -> str:
+        return self._lib.mcclCommTransport(self._h).decode()
+
+    @property
+    def nvls(self) -> bool:
+        return bool(self._q(self._lib.mcclCommNvlsEnabled))
+
+    @property
+    def last_algo(self) -> str:
+        return L.ALGO_NAMES.get(self._q(self._lib.mcclCommLastAlgo), "none")
+
+    @property
+    def launch_count(self) -> int:
+        v = C.c_uint64()
+        L.check(self._lib.mcclCommLaunchCount(self._h, C.byref(v)))
+        return v.value
+
+    def async_error(self) -> int:
+        return self._q(self._lib.mcclCommGetAsyncError)
+
+    def pick_algo(self, coll: str, nbytes: int, dtype: int = L.FLOAT32, op: str = "sum") -> str:
+        a = C.c_int()
+        L.check(self._lib.mcclCommPickAlgo(self._h, L.COLLS[coll], nbytes, dtype, L.OPS[op], C.byref(a)))
+        return L.ALGO_NAMES[a.value]
+
+    def set_max_ctas(self, n: int) -> None:
+        L.check(self._lib.mcclCommSetMaxCtas(self._h, n))
+
+    def topo_xml(self) -> str:
+        p = C.c_void_p()
+        L.check(self._lib.mcclCommTopoXml(self._h, C.byref(p)))
+        s = C.string_at(p).decode()
+        self._lib.mcclFreeString(p)
+        return s
+
+    # ---- lifecycle
+    def split(self, color: int, key: int = 0, blocking: Optional[bool] = None) -> Optional["Communicator"]:
+        h = C.c_void_p()
+        cfg = None
+        if blocking is not None:
+            cfg = C.byref(L.Config(1 if blocking else 0, self._transport_keepalive or self.transport.encode()))
+        L.check(self._lib.mcclCommSplit(self._h, color, key, C.byref(h), cfg), "mcclCommSplit")
+        if not h.value:
+            return None
+        return Communicator(0, b"", 0, _handle=h.value)
+
+    def synchronize(self) -> None:
+        L.check(self._lib.mcclCommSynchronize(self._h), "mcclCommSynchronize")
+
+    def finalize(self) -> None:
+        L.check(self._lib.mcclCommFinalize(self._h), "mcclCommFinalize")
+
+    def abort(self) -> None:
+        L.check(self._lib.mcclCommAbort(self._h), "mcclCommAbort")
+
+    def destroy(self) -> None:
+        if self._h:
+            self._sym.clear()
+            self._lib.mcclCommDestroy(self._h)
+            self._h = C.c_void_p()
+
+    def host_barrier(self) -> None:
+        L.check(self._lib.mcclCommHostBarrier(self._h), "mcclCommHostBarrier")
+
+    def host_all_gather(self, payload: bytes) -> list:
+        n = self.size
+        out = C.create_string_buffer(len(payload) * n)
+        L.check(self._lib.mcclCommHostAllGather(self._h, payload, out, len(payload)), "mcclCommHostAllGather")
+        raw = out.raw
+        return [raw[i * len(payload):(i + 1) * len(payload)] for i in range(n)]
+
+    # ---- collectives
+    def all_reduce(self, send, recv=None, op: str = "sum", dtype: Optional[int] = None, stream=None) -> None:
+        recv = send if recv is None else recv
+        sp, cnt, dt, _ = _describe(send, dtype)
+        rp, _, _, _ = _describe(recv, dtype)
+        L.check(self._lib.mcclAllReduce(self._h, sp, rp, cnt, dt, L.OPS[op], _stream_of(send, stream)), "mcclAllReduce")
+
+    def all_gather(self, send, recv, dtype: Optional[int] = None, stream=None) -> None:
+        sp, cnt, dt, _ = _describe(send, dtype)
+        rp, _, _, _ = _describe(recv, dtype)
+        L.check(self._lib.mcclAllGather(self._h, sp, rp, cnt, dt, _stream_of(send, stream)), "mcclAllGather")
+
+    def reduce_scatter(self, send, recv, op: str = "sum", dtype: Optional[int] = None, stream=None) -> None:
+        sp, _, dt, _ = _describe(send, dtype)
+        rp, cnt, _, _ = _describe(recv, dtype)
+        L.check(self._lib.mcclReduceScatter(self._h, sp, rp, cnt, dt, L.OPS[op], _stream_of(send, stream)),
+                "mcclReduceScatter")
+
+    def broadcast(self, send, recv, root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
+        rp, cnt, dt, _ = _describe(recv, dtype)
+        sp = _describe(send, dtype)[0] if send is not None else None
+        L.check(self._lib.mcclBroadcast(self._h, sp, rp, cnt, dt, root, _stream_of(recv, stream)), "mcclBroadcast")
+
+    def reduce(self, send, recv, op: str = "sum", root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
+        sp, cnt, dt, _ = _describe(send, dtype)
+        rp = _describe(recv, dtype)[0] if recv is not None else None
+        L.check(self._lib.mcclReduce(self._h, sp, rp, cnt, dt, L.OPS[op], root, _stream_of(send, stream)), "mcclReduce")
+
+    def all_to_all(self, send, recv, dtype: Optional[int] = None, stream=None) -> None:
+        sp, cnt, dt, _ = _describe(send, dtype)
+        rp, _, _, _ = _describe(recv, dtype)
+        L.check(self._lib.mcclAllToAll(self._h, sp, rp, cnt // self.size, dt, _stream_of(send, stream)), "mcclAllToAll")
+
+    def send(self, buf, peer: int, dtype: Optional[int] = None, stream=None) -> None:
+        p, cnt, dt, _ = _describe(buf, dtype)
+        L.check(self._lib.mcclSend(self._h, p, cnt, dt, peer, _stream_of(buf, stream)), "mcclSend")
+
+    def recv(self, buf, peer: int, dtype: Optional[int] = None, stream=None) -> None:
+        p, cnt, dt, _ = _describe(buf, dtype)
+        L.check(self._lib.mcclRecv(self._h, p, cnt, dt, peer, _stream_of(buf, stream)), "mcclRecv")
+
+    def recv_any(self, buf, dtype: Optional[int] = None, stream=None) -> int:
+        p, cnt, dt, _ = _describe(buf, dtype)
+        src = C.c_int(-1)
+        L.check(self._lib.mcclRecvAny(self._h, p, cnt, dt, C.byref(src), _stream_of(buf, stream)), "mcclRecvAny")
+        return src.value
+
+    # ---- symmetric memory (cuda transport)
+    def alloc_raw(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        L.check(self._lib.mcclMemAlloc(self._h, nbytes, C.byref(p)), "mcclMemAlloc")
+        return p.value
+
+    def free_raw(self, ptr: int) -> None:
+        L.check(self._lib.mcclMemFree(self._h, C.c_void_p(ptr)), "mcclMemFree")
+
+    def empty(self, shape, dtype=None):
+        """A CUDA tensor in symmetric memory (collective: every rank calls with the same shape)."""
+        if torch is None:
+            raise RuntimeError("torch is required for symmetric tensors")
+        dtype = dtype or torch.float32
+        numel = int(np.prod(shape)) if not isinstance(shape, int) else int(shape)
+        nbytes = max(numel * torch.empty((), dtype=dtype).element_size(), 16)
+        ptr = self.alloc_raw(nbytes)
+        holder = _SymBlock(self, ptr, nbytes)
+        t = torch.as_tensor(holder, device=f"cuda:{self.device}").view(dtype)[:numel].view(shape)
+        self._sym[t.data_ptr()] = holder
+        return t
+
+    def peer_pointer(self, tensor_or_ptr, peer: int) -> int:
+        p = tensor_or_ptr.data_ptr() if hasattr(tensor_or_ptr, "data_ptr") else int(tensor_or_ptr)
+        out = C.c_void_p()
+        L.check(self._lib.mcclMemPeerPointer(self._h, C.c_void_p(p), peer, C.byref(out)))
+        return out.value or 0
+
+    def multicast_pointer(self, tensor_or_ptr) -> int:
+        p = tensor_or_ptr.data_ptr() if hasattr(tensor_or_ptr, "data_ptr") else int(tensor_or_ptr)
+        out = C.c_void_p()
+        L.check(self._lib.mcclMemMulticastPointer(self._h, C.c_void_p(p), C.byref(out)))
+        return out.value or 0
+
+
+class _SymBlock:
+    """Exposes a symmetric allocation through __cuda_array_interface__ so torch can wrap it without a copy."""
+
+    def __init__(self, comm: Communicator, ptr: int, nbytes: int):
+        self.comm, self.ptr, self.nbytes = comm, ptr, nbytes
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
+        }
