@@ -1,0 +1,744 @@
+// Host side of the collective kernels: resolves buffers to symmetric segments, stages what is not
+// symmetric, fills the kernel arguments for the chosen algorithm and launches on the caller's stream.
+// Role parity: the per-collective algorithm entry points of the reference (src/device/all_reduce.h,
+// all_gather.h, reduce_scatter.h, broadcast.h, reduce.h) and its launch step (src/coll/coll.cc:33-43).
+#include <algorithm>
+#include <cstring>
+#include <cuda_runtime.h>
+
+#include "../transport/cuda_mem.h"
+#include "kernels.cuh"
+
+namespace mccl {
+
+DEFINE_MCCL_PARAM(NChannels, "NCHANNELS", 0);
+
+namespace {
+
+struct View {
+  Segment* seg = nullptr;
+  size_t off = 0;
+  bool sym() const { return seg != nullptr; }
+  char* peer(int p) const { return seg->peer[p] + off; }
+  char* mc() const { return seg->mc ? seg->mc + off : nullptr; }
+};
+
+View viewOf(const CudaState* st, const void* ptr, size_t bytes) {
+  View v;
+  if (ptr == nullptr) return v;
+  v.seg = segmentFind(st, ptr, bytes);
+  if (v.seg) v.off = (size_t)(static_cast<const char*>(ptr) - v.seg->local);
+  return v;
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// CTAs for a kernel that moves `bytes` per rank.
+int pickCtas(const mcclComm* c, size_t bytes, int algo) {
+  int g;
+  if (bytes <= (64u << 10)) g = 2;
+  else if (bytes <= (512u << 10)) g = 8;
+  else if (bytes <= (8u << 20)) g = 16;
+  else if (bytes <= (64u << 20)) g = 32;
+  else g = 64;
+  if (algo == mcclAlgoOneShot) g = std::min(g, 8);
+  const int limit = c->graphs[algo >= 0 && algo < mcclNumAlgos ? algo : mcclAlgoTwoShot].nChannels;
+  if (limit > 0) g = std::min(g, std::max(limit, 1));
+  if (mcclParamNChannels() > 0) g = (int)mcclParamNChannels();
+  if (c->maxCtas > 0) g = std::min(g, c->maxCtas);
+  return std::max(1, std::min(g, MCCL_MAX_CTAS));
+}
+
+mcclResult_t launched(mcclComm* c, const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    MCCL_WARN("launch of %s failed: %s", what, cudaGetErrorString(e));
+    return mcclSystemError;
+  }
+  c->launches.fetch_add(1);
+  return mcclSuccess;
+}
+
+mcclResult_t launchCopy(mcclComm* c, const void* src, void* dst, uint64_t rows, uint64_t rowBytes, uint64_t srcPitch,
+                        uint64_t dstPitch, cudaStream_t s) {
+  if (rows == 0 || rowBytes == 0 || (src == dst && srcPitch == dstPitch)) return mcclSuccess;
+  const uint64_t total = rows * rowBytes;
+  int blocks = (int)std::min<uint64_t>((total / 16 + kThreads - 1) / kThreads + 1, 296);
+  copyKernel<<<blocks, kThreads, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), rows, rowBytes, srcPitch, dstPitch);
+  return launched(c, "copyKernel");
+}
+
+template <typename T>
+mcclResult_t launchPullT(mcclComm* c, const PullArgs& a, cudaStream_t s, bool fast) {
+  const int n = a.nSrcA;
+  if (fast && n == 2) pullKernel<T, 2><<<a.nCtas, kThreads, 0, s>>>(a);
+  else if (fast && n == 4) pullKernel<T, 4><<<a.nCtas, kThreads, 0, s>>>(a);
+  else if (fast && n == 8) pullKernel<T, 8><<<a.nCtas, kThreads, 0, s>>>(a);
+  else pullKernel<T, 0><<<a.nCtas, kThreads, 0, s>>>(a);
+  return launched(c, "pullKernel");
+}
+
+mcclResult_t launchPull(mcclComm* c, const PullArgs& a, mcclDataType_t dt, cudaStream_t s) {
+  switch (dt) {
+    case mcclFloat32:  return launchPullT<float>(c, a, s, true);
+    case mcclFloat16:  return launchPullT<__half>(c, a, s, true);
+    case mcclBfloat16: return launchPullT<__nv_bfloat16>(c, a, s, true);
+    case mcclInt32:    return launchPullT<int32_t>(c, a, s, true);
+    case mcclUint32:   return launchPullT<uint32_t>(c, a, s, false);
+    case mcclInt64:    return launchPullT<int64_t>(c, a, s, false);
+    case mcclUint64:   return launchPullT<uint64_t>(c, a, s, false);
+    case mcclFloat64:  return launchPullT<double>(c, a, s, false);
+    case mcclInt8:     return launchPullT<int8_t>(c, a, s, false);
+    case mcclUint8:    return launchPullT<uint8_t>(c, a, s, false);
+    default: return mcclInvalidArgument;
+  }
+}
+
+#define DISPATCH_ALL_TYPES(dt, KERNEL, grid, stream, args)                                   \
+  switch (dt) {                                                                              \
+    case mcclFloat32:  KERNEL<float><<<grid, kThreads, 0, stream>>>(args); break;             \
+    case mcclFloat16:  KERNEL<__half><<<grid, kThreads, 0, stream>>>(args); break;            \
+    case mcclBfloat16: KERNEL<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(args); break;     \
+    case mcclInt32:    KERNEL<int32_t><<<grid, kThreads, 0, stream>>>(args); break;           \
+    case mcclUint32:   KERNEL<uint32_t><<<grid, kThreads, 0, stream>>>(args); break;          \
+    case mcclInt64:    KERNEL<int64_t><<<grid, kThreads, 0, stream>>>(args); break;           \
+    case mcclUint64:   KERNEL<uint64_t><<<grid, kThreads, 0, stream>>>(args); break;          \
+    case mcclFloat64:  KERNEL<double><<<grid, kThreads, 0, stream>>>(args); break;            \
+    case mcclInt8:     KERNEL<int8_t><<<grid, kThreads, 0, stream>>>(args); break;            \
+    case mcclUint8:    KERNEL<uint8_t><<<grid, kThreads, 0, stream>>>(args); break;           \
+    default: return mcclInvalidArgument;                                                     \
+  }
+
+// Shard r of a message of `bytes` bytes cut into n shards on 16-byte boundaries; the last shard takes the tail.
+inline uint64_t shardOff(uint64_t bytes, int n, int r) { return (uint64_t)(((unsigned __int128)(bytes / 16) * (unsigned)r) / (unsigned)n) * 16; }
+inline uint64_t shardEnd(uint64_t bytes, int n, int r) { return r == n - 1 ? bytes : shardOff(bytes, n, r + 1); }
+
+struct Call {
+  mcclComm* c;
+  CudaState* st;
+  int n, r;
+  mcclDataType_t dt;
+  size_t es;
+  mcclRedOp_t op;
+  int divisor;
+  cudaStream_t s;
+  char* stageLocal() const { return st->ctrl->local + st->layout.stageOff; }
+  char* stagePeer(int p) const { return st->ctrl->peer[p] + st->layout.stageOff; }
+  char* stageMc() const { return st->ctrl->mc ? st->ctrl->mc + st->layout.stageOff : nullptr; }
+  size_t stageBytes() const { return (size_t)st->layout.stageBytes; }
+};
+
+PullArgs basePull(const Call& k, size_t bytesForCtas, int algo) {
+  PullArgs a;
+  memset(&a, 0, sizeof(a));
+  a.peers = k.st->peers;
+  a.nCtas = pickCtas(k.c, bytesForCtas, algo);
+  a.op = (k.op == mcclAvg) ? mcclSum : k.op;
+  a.divisor = k.divisor;
+  return a;
+}
+
+}  // namespace
+
+namespace {
+
+// ---- two-shot core: fold my shard from everyone's input, then collect the other shards -----------------------
+// in[p]  : rank p's input (as mapped here)      red[p] : rank p's peer-visible result area
+// out    : this rank's final destination (may equal red[r]); `collect` = run phase B on this rank
+mcclResult_t twoShot(const Call& k, char* const in[], char* const red[], char* out, size_t bytes, bool collect, int algoForCtas) {
+  PullArgs a = basePull(k, bytes, algoForCtas);
+  const int n = k.n, r = k.r;
+  const uint64_t o0 = shardOff(bytes, n, r), o1 = shardEnd(bytes, n, r);
+  a.nSrcA = n;
+  for (int p = 0; p < n; ++p) a.srcA[p] = in[p] + o0;
+  a.dstA = red[r] + o0;
+  a.dstA2 = (out != nullptr && out != red[r]) ? out + o0 : nullptr;
+  a.aBytes = o1 - o0;
+  a.nJobs = 0;
+  a.midBarrier = 1;
+  if (collect) {
+    char* dst = out ? out : red[r];
+    for (int p = 0; p < n; ++p) {
+      if (p == r) continue;
+      const uint64_t q0 = shardOff(bytes, n, p), q1 = shardEnd(bytes, n, p);
+      a.jobs[a.nJobs++] = CopyJob{red[p] + q0, dst + q0, q1 - q0};
+    }
+  }
+  return launchPull(k.c, a, k.dt, k.s);
+}
+
+size_t stageChunk(const Call& k, size_t rows) {
+  size_t per = k.stageBytes() / std::max<size_t>(rows, 1);
+  per = per / 256 * 256;
+  return per;
+}
+
+mcclResult_t arTwoShot(const Call& k, const void* send, void* recv, size_t bytes) {
+  const View sv = viewOf(k.st, send, bytes), rv = viewOf(k.st, recv, bytes);
+  char* in[MCCL_MAX_RANKS];
+  char* red[MCCL_MAX_RANKS];
+  if (sv.sym() && rv.sym()) {
+    for (int p = 0; p < k.n; ++p) { in[p] = sv.peer(p); red[p] = rv.peer(p); }
+    return twoShot(k, in, red, static_cast<char*>(recv), bytes, true, mcclAlgoTwoShot);
+  }
+  const size_t chunk = stageChunk(k, 1);
+  if (chunk == 0) return mcclInternalError;
+  for (int p = 0; p < k.n; ++p) in[p] = red[p] = k.stagePeer(p);
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+    MCCLCHECK(twoShot(k, in, red, static_cast<char*>(recv) + off, len, true, mcclAlgoTwoShot));
+  }
+  return mcclSuccess;
+}
+
+mcclResult_t arOneShot(const Call& k, const void* send, void* recv, size_t bytes) {
+  OneShotArgs a;
+  memset(&a, 0, sizeof(a));
+  a.peers = k.st->peers;
+  a.nCtas = pickCtas(k.c, bytes, mcclAlgoOneShot);
+  a.op = (k.op == mcclAvg) ? mcclSum : k.op;
+  a.divisor = k.divisor;
+  a.send = static_cast<const char*>(send);
+  a.recv = static_cast<char*>(recv);
+  a.bytes = bytes;
+  DISPATCH_ALL_TYPES(k.dt, oneShotKernel, a.nCtas, k.s, a);
+  return launched(k.c, "oneShotKernel");
+}
+
+bool nvlsType(mcclDataType_t dt, mcclRedOp_t op) {
+  if (dt == mcclFloat32) return op == mcclSum || op == mcclAvg;
+  if (dt == mcclFloat16 || dt == mcclBfloat16) return op == mcclSum || op == mcclAvg || op == mcclMin || op == mcclMax;
+  return false;
+}
+
+mcclResult_t launchNvls(const Call& k, const NvlsArgs& a, bool reducing) {
+  if (!reducing) { nvlsKernel<float><<<a.nCtas, kThreads, 0, k.s>>>(a); return launched(k.c, "nvlsKernel"); }
+  switch (k.dt) {
+    case mcclFloat32:  nvlsKernel<float><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
+    case mcclFloat16:  nvlsKernel<__half><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
+    case mcclBfloat16: nvlsKernel<__nv_bfloat16><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
+    default: return mcclInvalidArgument;
+  }
+  return launched(k.c, "nvlsKernel");
+}
+
+NvlsArgs baseNvls(const Call& k, size_t bytes) {
+  NvlsArgs a;
+  memset(&a, 0, sizeof(a));
+  a.peers = k.st->peers;
+  a.nCtas = pickCtas(k.c, bytes, mcclAlgoNvls);
+  a.op = (k.op == mcclAvg) ? mcclSum : k.op;
+  a.divisor = 1;
+  a.active = 1;
+  return a;
+}
+
+// NVLS all-reduce on multicast-mapped memory: the switch adds my shard across ranks and replicates the result.
+mcclResult_t arNvlsOn(const Call& k, char* mcIn, char* mcOut, size_t bytes) {
+  NvlsArgs a = baseNvls(k, bytes);
+  const uint64_t o0 = shardOff(bytes, k.n, k.r), o1 = shardEnd(bytes, k.n, k.r);
+  a.loadReduce = 1;
+  a.mcStore = 1;
+  a.mcSrc = mcIn + o0;
+  a.mcDst = mcOut + o0;
+  a.bytes = o1 - o0;
+  a.divisor = k.divisor;
+  return launchNvls(k, a, true);
+}
+
+mcclResult_t arNvls(const Call& k, const void* send, void* recv, size_t bytes) {
+  const View sv = viewOf(k.st, send, bytes), rv = viewOf(k.st, recv, bytes);
+  if (sv.sym() && rv.sym() && sv.mc() && rv.mc() && al16(send) && al16(recv))
+    return arNvlsOn(k, sv.mc(), rv.mc(), bytes);
+  const size_t chunk = stageChunk(k, 1);
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+    MCCLCHECK(arNvlsOn(k, k.stageMc(), k.stageMc(), len));
+    MCCLCHECK(launchCopy(k.c, k.stageLocal(), static_cast<char*>(recv) + off, 1, len, len, len, k.s));
+  }
+  return mcclSuccess;
+}
+
+mcclResult_t ringTreeOn(const Call& k, char* const buf[], size_t bytes, int algo) {
+  const Channel& ch = k.c->chan;
+  if (algo == mcclAlgoRing) {
+    RingArgs a;
+    memset(&a, 0, sizeof(a));
+    a.peers = k.st->peers;
+    a.nCtas = pickCtas(k.c, bytes, algo);
+    a.op = (k.op == mcclAvg) ? mcclSum : k.op;
+    a.divisor = k.divisor;
+    a.prev = ch.ring.prev;
+    a.next = ch.ring.next;
+    a.bytes = bytes;
+    for (int p = 0; p < k.n; ++p) a.buf[p] = buf[p];
+    DISPATCH_ALL_TYPES(k.dt, ringKernel, a.nCtas, k.s, a);
+    return launched(k.c, "ringKernel");
+  }
+  TreeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.peers = k.st->peers;
+  a.nCtas = pickCtas(k.c, bytes, algo);
+  a.op = (k.op == mcclAvg) ? mcclSum : k.op;
+  a.divisor = k.divisor;
+  a.bytes = bytes;
+  const TreeView* tv[2] = {&ch.tree, ch.dtree ? &ch.treeB : &ch.tree};
+  for (int t = 0; t < 2; ++t) {
+    a.up[t] = tv[t]->up;
+    a.down[t][0] = tv[t]->down.size() > 0 ? tv[t]->down[0] : -1;
+    a.down[t][1] = tv[t]->down.size() > 1 ? tv[t]->down[1] : -1;
+  }
+  for (int p = 0; p < k.n; ++p) a.buf[p] = buf[p];
+  DISPATCH_ALL_TYPES(k.dt, treeKernel, a.nCtas, k.s, a);
+  return launched(k.c, "treeKernel");
+}
+
+mcclResult_t arRingTree(const Call& k, const void* send, void* recv, size_t bytes, int algo) {
+  const View rv = viewOf(k.st, recv, bytes);
+  char* buf[MCCL_MAX_RANKS];
+  if (rv.sym() && al16(recv)) {
+    MCCLCHECK(launchCopy(k.c, send, recv, 1, bytes, bytes, bytes, k.s));
+    for (int p = 0; p < k.n; ++p) buf[p] = rv.peer(p);
+    return ringTreeOn(k, buf, bytes, algo);
+  }
+  // Chunks keep the 16-byte and n-way divisibility the kernels rely on.
+  size_t chunk = stageChunk(k, 1);
+  chunk = chunk / (16 * (size_t)k.n) * (16 * (size_t)k.n);
+  for (int p = 0; p < k.n; ++p) buf[p] = k.stagePeer(p);
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+    if (len % 16 == 0 && len / 16 >= (size_t)2 * k.n) {
+      MCCLCHECK(ringTreeOn(k, buf, len, algo));
+    } else {
+      char* in[MCCL_MAX_RANKS];
+      for (int p = 0; p < k.n; ++p) in[p] = k.stagePeer(p);
+      MCCLCHECK(twoShot(k, in, in, nullptr, len, true, mcclAlgoTwoShot));
+    }
+    MCCLCHECK(launchCopy(k.c, k.stageLocal(), static_cast<char*>(recv) + off, 1, len, len, len, k.s));
+  }
+  return mcclSuccess;
+}
+
+mcclResult_t allReduce(const Call& k, const void* send, void* recv, size_t count, int algo) {
+  const size_t bytes = count * k.es;
+  const bool vecOk = bytes % 16 == 0 && al16(send) && al16(recv);
+  if (algo == mcclAlgoOneShot && vecOk && bytes <= k.st->layout.oneShotSlotBytes) return arOneShot(k, send, recv, bytes);
+  if (algo == mcclAlgoNvls && k.st->nvls && nvlsType(k.dt, k.op) && bytes % 16 == 0 && bytes / 16 >= (size_t)k.n)
+    return arNvls(k, send, recv, bytes);
+  if ((algo == mcclAlgoRing || algo == mcclAlgoTree) && bytes % 16 == 0 && bytes / 16 >= (size_t)2 * k.n)
+    return arRingTree(k, send, recv, bytes, algo);
+  k.c->lastAlgo.store(mcclAlgoTwoShot);
+  return arTwoShot(k, send, recv, bytes);
+}
+
+}  // namespace
+
+namespace {
+
+// Type used to move opaque bytes through the fold path (single source, no arithmetic).
+mcclDataType_t carrierType(size_t bytes) { return bytes % 4 == 0 ? mcclInt32 : mcclUint8; }
+
+// ---- all-gather ----------------------------------------------------------------------------------------------
+mcclResult_t allGather(const Call& k, const void* send, void* recv, size_t sendcount, int algo) {
+  const size_t slot = sendcount * k.es;
+  char* out = static_cast<char*>(recv);
+  const bool inPlace = send == out + (size_t)k.r * slot;
+  const View rv = viewOf(k.st, recv, slot * k.n), sv = viewOf(k.st, send, slot);
+  if (algo == mcclAlgoNvls && k.st->nvls && rv.sym() && rv.mc() && slot % 16 == 0 && al16(send) && al16(recv)) {
+    NvlsArgs a = baseNvls(k, slot);
+    a.loadReduce = 0;
+    a.mcStore = 1;
+    a.src = static_cast<const char*>(send);
+    a.mcDst = rv.mc() + (size_t)k.r * slot;
+    a.bytes = slot;
+    return launchNvls(k, a, false);
+  }
+  k.c->lastAlgo.store(mcclAlgoOneShot);
+  if ((inPlace && rv.sym()) || sv.sym()) {
+    PullArgs a = basePull(k, slot * k.n, mcclAlgoTwoShot);
+    for (int p = 0; p < k.n; ++p) {
+      const char* src = (inPlace && rv.sym()) ? rv.peer(p) + (size_t)p * slot : sv.peer(p);
+      if (p == k.r) { if (!inPlace) a.jobs[a.nJobs++] = CopyJob{static_cast<const char*>(send), out + (size_t)p * slot, slot}; continue; }
+      a.jobs[a.nJobs++] = CopyJob{src, out + (size_t)p * slot, slot};
+    }
+    return launchPull(k.c, a, carrierType(slot), k.s);
+  }
+  const size_t chunk = stageChunk(k, 1);
+  for (size_t off = 0; off < slot; off += chunk) {
+    const size_t len = std::min(chunk, slot - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+    PullArgs a = basePull(k, len * k.n, mcclAlgoTwoShot);
+    for (int p = 0; p < k.n; ++p) {
+      if (p == k.r) { if (!inPlace) a.jobs[a.nJobs++] = CopyJob{static_cast<const char*>(send) + off, out + (size_t)p * slot + off, len}; continue; }
+      a.jobs[a.nJobs++] = CopyJob{k.stagePeer(p), out + (size_t)p * slot + off, len};
+    }
+    MCCLCHECK(launchPull(k.c, a, carrierType(len), k.s));
+  }
+  return mcclSuccess;
+}
+
+// ---- reduce-scatter ------------------------------------------------------------------------------------------
+mcclResult_t reduceScatter(const Call& k, const void* send, void* recv, size_t recvcount, int algo) {
+  const size_t blk = recvcount * k.es;
+  const View sv = viewOf(k.st, send, blk * k.n);
+  if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op) && blk % 16 == 0 && al16(send) && al16(recv)) {
+    NvlsArgs a = baseNvls(k, blk);
+    a.loadReduce = 1;
+    a.mcStore = 0;
+    a.mcSrc = sv.mc() + (size_t)k.r * blk;
+    a.dst = static_cast<char*>(recv);
+    a.bytes = blk;
+    a.divisor = k.divisor;
+    return launchNvls(k, a, true);
+  }
+  k.c->lastAlgo.store(mcclAlgoOneShot);
+  if (sv.sym()) {
+    PullArgs a = basePull(k, blk * k.n, mcclAlgoTwoShot);
+    a.nSrcA = k.n;
+    for (int p = 0; p < k.n; ++p) a.srcA[p] = sv.peer(p) + (size_t)k.r * blk;
+    a.dstA = static_cast<char*>(recv);
+    a.aBytes = blk;
+    return launchPull(k.c, a, k.dt, k.s);
+  }
+  size_t chunk = stageChunk(k, k.n);
+  chunk = std::max<size_t>(chunk / k.es * k.es, k.es);
+  for (size_t off = 0; off < blk; off += chunk) {
+    const size_t len = std::min(chunk, blk - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), k.n, len, blk, len, k.s));
+    PullArgs a = basePull(k, len * k.n, mcclAlgoTwoShot);
+    a.nSrcA = k.n;
+    for (int p = 0; p < k.n; ++p) a.srcA[p] = k.stagePeer(p) + (size_t)k.r * len;
+    a.dstA = static_cast<char*>(recv) + off;
+    a.aBytes = len;
+    MCCLCHECK(launchPull(k.c, a, k.dt, k.s));
+  }
+  return mcclSuccess;
+}
+
+// ---- broadcast -------------------------------------------------------------------------------------------------
+// Scatter + all-gather ("two-shot"): rank r fetches shard r from the root, then the shards are exchanged, so
+// the root's outbound traffic is one copy of the message instead of n-1.  `direct` makes every rank fetch
+// the whole message from the root (lowest latency for small messages).
+mcclResult_t bcastOn(const Call& k, char* const work[], char* out, size_t bytes, int root, bool direct) {
+  Call kk = k;
+  kk.op = mcclSum;
+  kk.divisor = 1;
+  PullArgs a = basePull(kk, bytes, mcclAlgoTwoShot);
+  const int r = k.r, n = k.n;
+  a.midBarrier = direct ? 0 : 1;
+  if (r != root) {
+    char* dst = out ? out : work[r];
+    if (direct) {
+      a.jobs[a.nJobs++] = CopyJob{work[root], dst, bytes};
+    } else {
+      const uint64_t o0 = shardOff(bytes, n, r), o1 = shardEnd(bytes, n, r);
+      a.nSrcA = 1;
+      a.srcA[0] = work[root] + o0;
+      a.dstA = work[r] + o0;
+      a.dstA2 = (out && out != work[r]) ? out + o0 : nullptr;
+      a.aBytes = o1 - o0;
+      for (int p = 0; p < n; ++p) {
+        if (p == r) continue;
+        const uint64_t q0 = shardOff(bytes, n, p), q1 = shardEnd(bytes, n, p);
+        a.jobs[a.nJobs++] = CopyJob{work[p] + q0, dst + q0, q1 - q0};   // the root's own copy is complete too
+      }
+    }
+  }
+  return launchPull(k.c, a, carrierType(bytes), k.s);
+}
+
+mcclResult_t broadcast(const Call& k, const void* send, void* recv, size_t count, int root, int algo) {
+  const size_t bytes = count * k.es;
+  const View rv = viewOf(k.st, recv, bytes);
+  const bool direct = algo == mcclAlgoOneShot;
+  if (algo == mcclAlgoNvls && k.st->nvls && rv.sym() && rv.mc() && bytes % 16 == 0 && al16(recv) && (k.r != root || al16(send))) {
+    NvlsArgs a = baseNvls(k, bytes);
+    a.loadReduce = 0;
+    a.mcStore = 1;
+    a.active = k.r == root;
+    a.src = static_cast<const char*>(send);
+    a.mcDst = rv.mc();
+    a.bytes = bytes;
+    return launchNvls(k, a, false);
+  }
+  k.c->lastAlgo.store(direct ? mcclAlgoOneShot : mcclAlgoTwoShot);
+  char* work[MCCL_MAX_RANKS];
+  if (rv.sym()) {
+    if (k.r == root) MCCLCHECK(launchCopy(k.c, send, recv, 1, bytes, bytes, bytes, k.s));
+    for (int p = 0; p < k.n; ++p) work[p] = rv.peer(p);
+    return bcastOn(k, work, static_cast<char*>(recv), bytes, root, direct);
+  }
+  const size_t chunk = stageChunk(k, 1);
+  for (int p = 0; p < k.n; ++p) work[p] = k.stagePeer(p);
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    if (k.r == root) {
+      MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+      MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, static_cast<char*>(recv) + off, 1, len, len, len, k.s));
+    }
+    MCCLCHECK(bcastOn(k, work, static_cast<char*>(recv) + off, len, root, direct));
+  }
+  return mcclSuccess;
+}
+
+// ---- reduce ----------------------------------------------------------------------------------------------------
+// Two-shot: every rank folds its shard, the root collects the shards.  Direct: the root folds everything.
+mcclResult_t reduceOn(const Call& k, char* const in[], char* const red[], char* recvAt, size_t bytes, int root, bool direct) {
+  const int n = k.n, r = k.r;
+  if (direct) {
+    PullArgs a = basePull(k, bytes, mcclAlgoTwoShot);
+    if (r == root) {
+      a.nSrcA = n;
+      for (int p = 0; p < n; ++p) a.srcA[p] = in[p];
+      a.dstA = recvAt;
+      a.aBytes = bytes;
+    }
+    return launchPull(k.c, a, k.dt, k.s);
+  }
+  return twoShot(k, in, red, r == root ? recvAt : nullptr, bytes, r == root, mcclAlgoTwoShot);
+}
+
+mcclResult_t reduce(const Call& k, const void* send, void* recv, size_t count, int root, int algo) {
+  const size_t bytes = count * k.es;
+  const View sv = viewOf(k.st, send, bytes);
+  const bool direct = algo == mcclAlgoOneShot;
+  if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op) && bytes % 16 == 0 && al16(send) &&
+      (k.r != root || al16(recv))) {
+    NvlsArgs a = baseNvls(k, bytes);
+    a.loadReduce = 1;
+    a.mcStore = 0;
+    a.active = k.r == root;
+    a.mcSrc = sv.mc();
+    a.dst = static_cast<char*>(recv);
+    a.bytes = bytes;
+    a.divisor = k.divisor;
+    return launchNvls(k, a, true);
+  }
+  k.c->lastAlgo.store(direct ? mcclAlgoOneShot : mcclAlgoTwoShot);
+  // The stage is cut in two: inputs that are not symmetric go to the first half, folded shards to the second.
+  size_t half = k.stageBytes() / 2 / 256 * 256;
+  half = std::max<size_t>(half / k.es * k.es, k.es);
+  char* in[MCCL_MAX_RANKS];
+  char* red[MCCL_MAX_RANKS];
+  for (size_t off = 0; off < bytes; off += half) {
+    const size_t len = std::min(half, bytes - off);
+    if (sv.sym()) {
+      for (int p = 0; p < k.n; ++p) in[p] = sv.peer(p) + off;
+    } else {
+      MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+      for (int p = 0; p < k.n; ++p) in[p] = k.stagePeer(p);
+    }
+    for (int p = 0; p < k.n; ++p) red[p] = k.stagePeer(p) + half;
+    MCCLCHECK(reduceOn(k, in, red, k.r == root ? static_cast<char*>(recv) + off : nullptr, len, root, direct));
+  }
+  return mcclSuccess;
+}
+
+// ---- all-to-all --------------------------------------------------------------------------------------------------
+mcclResult_t allToAll(const Call& k, const void* send, void* recv, size_t count) {
+  const size_t blk = count * k.es;
+  const View sv = viewOf(k.st, send, blk * k.n);
+  char* out = static_cast<char*>(recv);
+  if (sv.sym()) {
+    PullArgs a = basePull(k, blk * k.n, mcclAlgoTwoShot);
+    for (int p = 0; p < k.n; ++p) a.jobs[a.nJobs++] = CopyJob{sv.peer(p) + (size_t)k.r * blk, out + (size_t)p * blk, blk};
+    return launchPull(k.c, a, carrierType(blk), k.s);
+  }
+  const size_t chunk = stageChunk(k, k.n);
+  for (size_t off = 0; off < blk; off += chunk) {
+    const size_t len = std::min(chunk, blk - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), k.n, len, blk, len, k.s));
+    PullArgs a = basePull(k, len * k.n, mcclAlgoTwoShot);
+    for (int p = 0; p < k.n; ++p) a.jobs[a.nJobs++] = CopyJob{k.stagePeer(p) + (size_t)k.r * len, out + (size_t)p * blk + off, len};
+    MCCLCHECK(launchPull(k.c, a, carrierType(len), k.s));
+  }
+  return mcclSuccess;
+}
+
+}  // namespace
+
+// ---- entry points used by the runtime ------------------------------------------------------------------------------
+static mcclResult_t latchedError(mcclComm* c) {
+  const uint32_t code = c->cu->statusHost->code;
+  if (code == 0) return mcclSuccess;
+  return code == 3 ? mcclInvalidUsage : mcclRemoteError;
+}
+
+mcclResult_t cudaCollective(mcclComm* c, int coll, const void* send, void* recv, size_t count, mcclDataType_t dt,
+                            mcclRedOp_t op, int root, int algo, mcclStream_t stream) {
+  CudaState* st = c->cu;
+  if (st == nullptr) MCCLFAIL(mcclInternalError);
+  // A wait that gave up earlier leaves the flags of this communicator desynchronised: refuse further work.
+  MCCLCHECK(latchedError(c));
+  int dev = -1;
+  CUDACHECK(cudaGetDevice(&dev));
+  if (dev != c->device) CUDACHECK(cudaSetDevice(c->device));
+  Call k;
+  k.c = c; k.st = st; k.n = c->nRanks; k.r = c->rank; k.dt = dt; k.es = mcclDataSize(dt); k.op = op;
+  k.divisor = (op == mcclAvg) ? c->nRanks : 1;
+  k.s = reinterpret_cast<cudaStream_t>(stream);
+  mcclResult_t rc = mcclSuccess;
+  if (c->nRanks == 1) {
+    // Single rank: every collective is a local copy (avg over one rank is the identity).
+    if (recv != nullptr && send != nullptr) rc = launchCopy(c, send, recv, 1, count * k.es, count * k.es, count * k.es, k.s);
+  } else {
+    switch (coll) {
+      case mcclCollAllReduce:     rc = allReduce(k, send, recv, count, algo); break;
+      case mcclCollAllGather:     rc = allGather(k, send, recv, count, algo); break;
+      case mcclCollReduceScatter: rc = reduceScatter(k, send, recv, count, algo); break;
+      case mcclCollBroadcast:     rc = broadcast(k, send, recv, count, root, algo); break;
+      case mcclCollReduce:        rc = reduce(k, send, recv, count, root, algo); break;
+      case mcclCollAllToAll:      rc = allToAll(k, send, recv, count); break;
+      default: rc = mcclInvalidArgument;
+    }
+  }
+  if (dev != c->device) cudaSetDevice(dev);
+  return rc;
+}
+
+mcclResult_t cudaBarrier(mcclComm* c, mcclStream_t stream) {
+  CudaState* st = c->cu;
+  MCCLCHECK(latchedError(c));
+  CUDACHECK(cudaSetDevice(c->device));
+  cudaStream_t s = stream ? reinterpret_cast<cudaStream_t>(stream) : reinterpret_cast<cudaStream_t>(st->internalStream);
+  // Whatever the caller queued on any stream of this device comes first.
+  if (!stream) CUDACHECK(cudaDeviceSynchronize());
+  barrierKernel<<<1, kThreads, 0, s>>>(st->peers);
+  MCCLCHECK(launched(c, "barrierKernel"));
+  CUDACHECK(cudaStreamSynchronize(s));
+  return latchedError(c);
+}
+
+mcclResult_t cudaP2pBatch(mcclComm* c, const std::vector<P2pOp>& ops, mcclStream_t stream) {
+  CudaState* st = c->cu;
+  MCCLCHECK(latchedError(c));
+  CUDACHECK(cudaSetDevice(c->device));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // Sends to self pair with receives from self, in order.
+  std::vector<const P2pOp*> selfS, selfR;
+  for (const P2pOp& op : ops) if (op.peer == c->rank) (op.isSend ? selfS : selfR).push_back(&op);
+  if (selfS.size() != selfR.size()) MCCLFAIL(mcclInvalidUsage);
+  for (size_t i = 0; i < selfS.size(); ++i) {
+    if (selfS[i]->bytes != selfR[i]->bytes) MCCLFAIL(mcclInvalidUsage);
+    MCCLCHECK(launchCopy(c, selfS[i]->buf, selfR[i]->buf, 1, selfS[i]->bytes, selfS[i]->bytes, selfS[i]->bytes, s));
+  }
+  // One CTA per (peer, direction) flow; a batch holds at most MCCL_MAX_P2P_OPS operations per launch.
+  std::vector<const P2pOp*> rest;
+  for (const P2pOp& op : ops) if (op.peer != c->rank && op.bytes > 0) rest.push_back(&op);
+  size_t pos = 0;
+  while (pos < rest.size()) {
+    P2pArgs a;
+    memset(&a, 0, sizeof(a));
+    a.peers = st->peers;
+    int flowOf[MCCL_MAX_RANKS][2];
+    for (auto& f : flowOf) f[0] = f[1] = -1;
+    int flows = 0;
+    while (pos < rest.size() && a.nOps < MCCL_MAX_P2P_OPS) {
+      const P2pOp* op = rest[pos++];
+      int& f = flowOf[op->peer][op->isSend ? 1 : 0];
+      if (f < 0) f = flows++;
+      P2pDesc& d = a.ops[a.nOps++];
+      d.isSend = (f << 1) | (op->isSend ? 1 : 0);
+      d.peer = op->peer;
+      d.buf = static_cast<char*>(op->buf);
+      d.bytes = op->bytes;
+    }
+    p2pKernel<<<flows, kThreads, 0, s>>>(a);
+    MCCLCHECK(launched(c, "p2pKernel"));
+  }
+  return mcclSuccess;
+}
+
+mcclResult_t cudaRecvAny(mcclComm* c, void* buf, size_t bytes, int* src, mcclStream_t stream) {
+  CudaState* st = c->cu;
+  MCCLCHECK(latchedError(c));
+  CUDACHECK(cudaSetDevice(c->device));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int* host = static_cast<int*>(st->probeHost);
+  int* dev = nullptr;
+  CUDACHECK(cudaHostGetDevicePointer((void**)&dev, host, 0));
+  *host = -2;
+  recvAnyProbeKernel<<<1, 32, 0, s>>>(st->peers, dev);
+  MCCLCHECK(launched(c, "recvAnyProbeKernel"));
+  CUDACHECK(cudaStreamSynchronize(s));
+  if (*host < 0) {
+    MCCL_WARN("RecvAny: no sender within the device time budget");
+    return c->aborted.load() ? mcclInvalidUsage : mcclRemoteError;
+  }
+  *src = *host;
+  std::vector<P2pOp> one{P2pOp{c, false, *src, buf, bytes, stream}};
+  return cudaP2pBatch(c, one, stream);
+}
+
+// Measure what the cost model assumes: per-pair pull bandwidth and the latency of an empty collective,
+// then refine the tuner's constants (maximum over ranks, so every rank ends with the same table).
+// Role parity: mcclCalibrateTbLinks (src/init.cc:164-204) of the reference, with a timed pull kernel in
+// place of a one-second TCP stream.
+mcclResult_t cudaCalibrate(mcclComm* c) {
+  CudaState* st = c->cu;
+  if (c->nRanks < 2 || st->layout.stageBytes < (8u << 20)) return mcclSuccess;
+  CUDACHECK(cudaSetDevice(c->device));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(st->internalStream);
+  cudaEvent_t e0, e1;
+  CUDACHECK(cudaEventCreate(&e0));
+  CUDACHECK(cudaEventCreate(&e1));
+  Call k;
+  k.c = c; k.st = st; k.n = c->nRanks; k.r = c->rank; k.dt = mcclFloat32; k.es = 4; k.op = mcclSum; k.divisor = 1; k.s = s;
+  std::vector<float> bw(c->nRanks, 0.f);
+  const size_t probe = std::min<size_t>(st->layout.stageBytes / 2, 32u << 20);
+  char* scratch = k.stageLocal() + st->layout.stageBytes / 2;
+  float latencyUs = 0.f;
+  // Latency: empty pull kernels (three barriers each); bandwidth: pull `probe` bytes from one peer at a time.
+  for (int round = -1; round < c->nRanks; ++round) {
+    const int peer = round;
+    if (peer == c->rank) continue;
+    const int iters = peer < 0 ? 20 : 4;
+    for (int it = -1; it < iters; ++it) {     // first pass warms up
+      if (it == 0) CUDACHECK(cudaEventRecord(e0, s));
+      PullArgs a = basePull(k, probe, mcclAlgoTwoShot);
+      if (peer >= 0) a.jobs[a.nJobs++] = CopyJob{k.stagePeer(peer), scratch, probe};
+      MCCLCHECK(launchPull(c, a, mcclInt32, s));
+    }
+    CUDACHECK(cudaEventRecord(e1, s));
+    CUDACHECK(cudaStreamSynchronize(s));
+    float ms = 0.f;
+    CUDACHECK(cudaEventElapsedTime(&ms, e0, e1));
+    if (peer < 0) latencyUs = ms * 1000.f / iters;
+    else bw[peer] = (float)((double)probe * iters / (ms * 1e-3) / 1e9);
+    MCCLCHECK(latchedError(c));
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  struct Row { float bw[MCCL_MAX_RANKS]; float lat; };
+  Row mine;
+  memset(&mine, 0, sizeof(mine));
+  for (int p = 0; p < c->nRanks; ++p) mine.bw[p] = bw[p];
+  mine.lat = latencyUs;
+  std::vector<Row> all(c->nRanks);
+  MCCLCHECK(bootstrapAllGather(c->bs, &mine, all.data(), sizeof(Row)));
+  float minBw = 1e9f, maxLat = 0.f;
+  for (int a = 0; a < c->nRanks; ++a) {
+    maxLat = std::max(maxLat, all[a].lat);
+    for (TopoLink& l : c->system.nodes[a].links) {
+      l.measured = all[a].bw[l.remote];
+      l.latencyUs = all[a].lat / 3.f;
+      if (l.measured > 0.f) { l.bw = l.measured; minBw = std::min(minBw, l.measured); }
+    }
+  }
+  if (minBw < 1e9f) {
+    // One peer at a time cannot saturate the port; pulls from all peers at once reach more, so the
+    // single-pair figure is a floor for the all-pairs algorithms, not a replacement for the table.
+    for (int a = 0; a < mcclNumAlgos; ++a) c->tuner.stepUs[a] = maxLat / 3.f;
+    c->tuner.alphaUs[mcclAlgoTwoShot] = c->tuner.alphaUs[mcclAlgoNvls] = maxLat;
+    c->tuner.alphaUs[mcclAlgoOneShot] = maxLat * 0.6f;
+  }
+  MCCL_INFO("calibration: empty collective %.1f us, slowest pair %.1f GB/s", maxLat, minBw);
+  const char* cache = envStr("MCCL_TUNER_CACHE");
+  if (cache && c->rank == 0) tunerSaveCache(c->tuner, cache);
+  return mcclSuccess;
+}
+
+}  // namespace mccl

@@ -1,0 +1,154 @@
+// Structures shared by host and device code of the cuda transport.
+//
+// Every communicator owns a *control block* in symmetric memory (same layout on every rank, every rank
+// maps every peer's copy).  It holds the flags through which the kernels of different GPUs synchronise,
+// the one-shot exchange slots and the Send/Recv FIFOs.  All flags are monotonically increasing 64-bit
+// counters, never reset, so back-to-back collectives cannot confuse one call's signal with the next.
+#pragma once
+
+#include <stdint.h>
+
+#define MCCL_MAX_RANKS 16      // ranks of one NVSwitch domain a kernel can address
+#define MCCL_MAX_CTAS 128      // upper bound on CTAs ("channels") of one collective kernel
+#define MCCL_COLL_THREADS 512
+
+namespace mccl {
+
+// Device status word (pinned host memory, one per communicator).  A wait that runs out of time records
+// where it gave up and the kernel returns normally; nothing traps.
+struct DevStatus {
+  volatile uint32_t code;     // 0 = fine, 1 = timeout in a barrier, 2 = timeout in a step wait, 3 = aborted by host
+  volatile uint32_t peer;     // rank that did not answer
+  volatile uint32_t cta;
+  volatile uint32_t step;
+  volatile uint32_t abort;    // host sets it to make every wait give up at once
+  uint32_t pad[3];
+};
+
+struct CtrlFlags {
+  // bar[cta][src]: written by rank `src`'s CTA `cta`: "I have reached barrier number N".
+  uint64_t bar[MCCL_MAX_CTAS][MCCL_MAX_RANKS];
+  // sig[cta][src]: step signals of the ring / tree kernels, written by rank `src`.
+  uint64_t sig[MCCL_MAX_CTAS][MCCL_MAX_RANKS];
+  // epoch[cta]: barriers this rank's CTA has passed so far (local bookkeeping, read at kernel entry).
+  uint64_t epoch[MCCL_MAX_CTAS];
+  // one-shot: ready[cta][src] = number of one-shot calls whose data from `src` has fully arrived.
+  uint64_t oneShotReady[MCCL_MAX_CTAS][MCCL_MAX_RANKS];
+  uint64_t oneShotCalls[MCCL_MAX_CTAS];
+  // Send/Recv FIFOs: head[src] = chunks rank `src` has written into my slot; tail[dst] = chunks rank
+  // `dst` has drained from its slot for me.  sent/recvd are this rank's own running totals.
+  uint64_t p2pHead[MCCL_MAX_RANKS];
+  uint64_t p2pTail[MCCL_MAX_RANKS];
+  uint64_t p2pSent[MCCL_MAX_RANKS];
+  uint64_t p2pRecvd[MCCL_MAX_RANKS];
+  // RecvAny: pending[src] = messages announced by `src` and not yet consumed.
+  uint64_t canary;            // 0x6d63636c63616e61, checked by tests after every run
+};
+
+constexpr uint64_t kCanary = 0x6d63636c63616e61ull;
+
+// Layout of the control segment: flags, then the one-shot slots, then the Send/Recv slots.
+struct CtrlLayout {
+  uint64_t flagsOff;
+  uint64_t oneShotOff;      // 2 buffers x n ranks x oneShotSlotBytes
+  uint64_t oneShotSlotBytes;
+  uint64_t p2pOff;          // n ranks x p2pSlotBytes (two halves each)
+  uint64_t p2pSlotBytes;
+  uint64_t stageOff;        // staging area for buffers that are not symmetric
+  uint64_t stageBytes;
+  uint64_t totalBytes;
+};
+
+struct DevPeers {
+  int rank, n;
+  char* ctrl[MCCL_MAX_RANKS];     // every rank's control segment as mapped here (ctrl[rank] = local)
+  char* ctrlMc;                   // multicast alias of the control segment, or null
+  CtrlLayout layout;
+  DevStatus* status;              // device alias of the pinned status word
+  uint64_t timeoutNs;
+};
+
+struct CopyJob {
+  const char* src;
+  char* dst;
+  uint64_t bytes;
+};
+
+// Arguments of the pull kernel (two-shot all-reduce and every "direct" collective).
+struct PullArgs {
+  DevPeers peers;
+  int nCtas;
+  int op;                      // mcclRedOp_t
+  // phase A: fold `nSrcA` sources over [aBytes) into dstA (and dstA2 if set)
+  int nSrcA;
+  const char* srcA[MCCL_MAX_RANKS];
+  char* dstA;
+  char* dstA2;
+  uint64_t aBytes;
+  // phase B: plain copies, each sliced over the CTAs
+  int nJobs;
+  CopyJob jobs[MCCL_MAX_RANKS + 1];
+  int divisor;                 // avg: number of ranks, else 1
+  int midBarrier;              // barrier between the phases (same value on every rank of a call)
+};
+
+struct OneShotArgs {
+  DevPeers peers;
+  int nCtas;
+  int op;
+  const char* send;
+  char* recv;
+  uint64_t bytes;
+  int divisor;
+};
+
+struct NvlsArgs {
+  DevPeers peers;
+  int nCtas;
+  int op;
+  int loadReduce;              // 1: read through multimem.ld_reduce from mcSrc; 0: read local src
+  int mcStore;                 // 1: write through multimem.st to mcDst; 0: write local dst
+  int active;                  // 0: this rank only takes part in the barriers
+  const char* src;             // local source (loadReduce == 0)
+  const char* mcSrc;
+  char* dst;
+  char* mcDst;
+  uint64_t bytes;
+  int divisor;
+};
+
+struct RingArgs {
+  DevPeers peers;
+  int nCtas;
+  int op;
+  int prev, next;
+  char* buf[MCCL_MAX_RANKS];   // every rank's work buffer (peer-visible), in place
+  uint64_t bytes;
+  int divisor;
+};
+
+struct TreeArgs {
+  DevPeers peers;
+  int nCtas;
+  int op;
+  int up[2];
+  int down[2][2];
+  char* buf[MCCL_MAX_RANKS];
+  uint64_t bytes;
+  int divisor;
+};
+
+struct P2pDesc {
+  int isSend;
+  int peer;
+  char* buf;
+  uint64_t bytes;
+};
+#define MCCL_MAX_P2P_OPS 32
+struct P2pArgs {
+  DevPeers peers;
+  int nOps;
+  P2pDesc ops[MCCL_MAX_P2P_OPS];
+};
+
+}  // namespace mccl

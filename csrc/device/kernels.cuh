@@ -1,0 +1,466 @@
+// The collective kernels of the cuda transport.  One CTA index = one "channel": CTA b of every rank works
+// on slice b of every region, and all cross-GPU ordering happens between the CTAs that share an index, so
+// no CTA ever waits for another CTA of its own GPU.
+//
+//   pullKernel    two-shot all-reduce and every direct collective: phase A folds a shard read from all
+//                 peers into local memory, phase B copies shards from peers; barriers in between.
+//   oneShotKernel small all-reduce: push the input into every peer's slot, one flag wait, fold locally.
+//   nvlsKernel    NVSwitch-reduced / -replicated variants through multimem.ld_reduce / multimem.st.
+//   ringKernel    ring all-reduce (reduce-scatter steps then all-gather steps) with per-step signals.
+//   treeKernel    double-binary-tree all-reduce, even CTAs on tree 0 / first half, odd CTAs on tree 1.
+//   p2pKernel     Send/Recv batch through per-peer FIFO slots.
+//   copyKernel    local 2-D copy used for staging.
+//
+// Algorithm parity with the reference: direct fold order src/device/all_reduce.h:44-58, ring steps
+// :63-101, tree :148-225; fused here: the fold, the dtype widening, the 1/world scale and the
+// out-of-place copy happen in the same pass that moves the bytes over NVLink.
+#pragma once
+
+#include "common.cuh"
+
+namespace mccl {
+
+constexpr int kThreads = MCCL_COLL_THREADS;
+
+// ---- element-granular helpers (tails and misaligned buffers) -----------------------------------------------
+template <typename T> __device__ __forceinline__ T ldElem(const void* p) {
+  if constexpr (sizeof(T) == 1) { uint8_t v = *reinterpret_cast<const volatile uint8_t*>(p); return *reinterpret_cast<T*>(&v); }
+  else if constexpr (sizeof(T) == 2) { uint16_t v = *reinterpret_cast<const volatile uint16_t*>(p); return *reinterpret_cast<T*>(&v); }
+  else if constexpr (sizeof(T) == 4) { uint32_t v = *reinterpret_cast<const volatile uint32_t*>(p); return *reinterpret_cast<T*>(&v); }
+  else { uint64_t v = *reinterpret_cast<const volatile uint64_t*>(p); return *reinterpret_cast<T*>(&v); }
+}
+
+template <typename T>
+__device__ __forceinline__ void foldElems(const PullArgs& a, uint64_t byteLo, uint64_t byteHi, int tid, int nthreads) {
+  using A = typename Acc<T>::type;
+  for (uint64_t off = byteLo + (uint64_t)tid * sizeof(T); off < byteHi; off += (uint64_t)nthreads * sizeof(T)) {
+    A acc = widen<T>(ldElem<T>(a.srcA[0] + off));
+    for (int p = 1; p < a.nSrcA; ++p) acc = foldOp<A>(acc, widen<T>(ldElem<T>(a.srcA[p] + off)), a.op);
+    const T out = finish<T>(acc, a.divisor);
+    *reinterpret_cast<T*>(a.dstA + off) = out;
+    if (a.dstA2) *reinterpret_cast<T*>(a.dstA2 + off) = out;
+  }
+}
+
+__device__ __forceinline__ void copyBytes(const char* src, char* dst, uint64_t lo, uint64_t hi, int tid, int nthreads) {
+  for (uint64_t off = lo + tid; off < hi; off += nthreads) dst[off] = *reinterpret_cast<const volatile char*>(src + off);
+}
+
+// Copy vectors [lo, hi) (16-byte units) from src to dst, eight loads in flight per thread.
+__device__ __forceinline__ void copyVecs(const char* src, char* dst, uint64_t lo, uint64_t hi, int tid, int nthreads) {
+  constexpr int U = 8;
+  uint64_t i = lo + tid;
+  for (; i + (uint64_t)(U - 1) * nthreads < hi; i += (uint64_t)U * nthreads) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ldSys128(src + (i + (uint64_t)u * nthreads) * 16);
+#pragma unroll
+    for (int u = 0; u < U; ++u) stLocal128(dst + (i + (uint64_t)u * nthreads) * 16, v[u]);
+  }
+  for (; i < hi; i += nthreads) stLocal128(dst + i * 16, ldSys128(src + i * 16));
+}
+
+// Fold vectors [lo, hi) of NR sources (NR = 0: run-time count) into dstA / dstA2.
+template <typename T, int NR>
+__device__ __forceinline__ void foldVecs(const PullArgs& a, uint64_t lo, uint64_t hi, int tid, int nthreads) {
+  using A = typename Acc<T>::type;
+  constexpr int N = Pack<T>::N;
+  if constexpr (NR > 0) {
+    constexpr int U = (NR <= 2) ? 4 : (NR <= 4 ? 2 : 1);
+    for (uint64_t i = lo + tid; i < hi; i += (uint64_t)U * nthreads) {
+      uint4 v[U][NR];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t idx = i + (uint64_t)u * nthreads;
+        if (idx < hi) {
+#pragma unroll
+          for (int p = 0; p < NR; ++p) v[u][p] = ldSys128(a.srcA[p] + idx * 16);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t idx = i + (uint64_t)u * nthreads;
+        if (idx < hi) {
+          A acc[N];
+          accInit<T>(acc, v[u][0]);
+#pragma unroll
+          for (int p = 1; p < NR; ++p) accFold<T>(acc, v[u][p], a.op);
+          const uint4 out = accFinish<T>(acc, a.divisor);
+          stLocal128(a.dstA + idx * 16, out);
+          if (a.dstA2) stLocal128(a.dstA2 + idx * 16, out);
+        }
+      }
+    }
+  } else {
+    for (uint64_t i = lo + tid; i < hi; i += nthreads) {
+      A acc[N];
+      accInit<T>(acc, ldSys128(a.srcA[0] + i * 16));
+      for (int p = 1; p < a.nSrcA; ++p) accFold<T>(acc, ldSys128(a.srcA[p] + i * 16), a.op);
+      const uint4 out = accFinish<T>(acc, a.divisor);
+      stLocal128(a.dstA + i * 16, out);
+      if (a.dstA2) stLocal128(a.dstA2 + i * 16, out);
+    }
+  }
+}
+
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T, int NR>
+__global__ void __launch_bounds__(kThreads, 1) pullKernel(const __grid_constant__ PullArgs a) {
+  __shared__ int sFail;
+  const DevPeers& P = a.peers;
+  const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
+  if (tid == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, P.rank);
+  uint64_t epoch = mine->epoch[cta];
+  bool ok = true;
+  const bool multi = P.n > 1;
+  if (multi) ok = ctaBarrier(P, epoch, &sFail);          // every peer's inputs are ready, its outputs are free
+
+  // The split over CTAs depends on sizes only (16-byte units, the tail to the last CTA), never on alignment,
+  // so CTA b of every rank always covers the same byte range of a region; inside its range a CTA takes the
+  // 128-bit path when the pointers allow it.
+  if (ok && a.nSrcA > 0 && a.aBytes > 0) {
+    bool vec = aligned16(a.dstA) && (a.dstA2 == nullptr || aligned16(a.dstA2));
+    for (int p = 0; p < a.nSrcA; ++p) vec = vec && aligned16(a.srcA[p]);
+    const uint64_t V = a.aBytes / 16;
+    const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
+    if (vec) foldVecs<T, NR>(a, lo, hi, tid, kThreads);
+    else foldElems<T>(a, lo * 16, hi * 16, tid, kThreads);
+    if (cta == G - 1 && V * 16 < a.aBytes) foldElems<T>(a, V * 16, a.aBytes, tid, kThreads);
+  }
+  if (multi && ok && a.midBarrier) ok = ctaBarrier(P, epoch, &sFail);   // every shard is folded
+
+  if (ok) {
+    for (int j = 0; j < a.nJobs; ++j) {
+      const CopyJob job = a.jobs[j];
+      if (job.bytes == 0) continue;
+      const uint64_t V = job.bytes / 16;
+      const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
+      if (aligned16(job.src) && aligned16(job.dst)) copyVecs(job.src, job.dst, lo, hi, tid, kThreads);
+      else copyBytes(job.src, job.dst, lo * 16, hi * 16, tid, kThreads);
+      if (cta == G - 1 && V * 16 < job.bytes) copyBytes(job.src, job.dst, V * 16, job.bytes, tid, kThreads);
+    }
+  }
+  if (multi && ok) ok = ctaBarrier(P, epoch, &sFail);    // nobody still reads this rank's memory
+  if (tid == 0) mine->epoch[cta] = epoch;
+}
+
+// ---- one-shot ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) oneShotKernel(const __grid_constant__ OneShotArgs a) {
+  __shared__ int sFail;
+  using A = typename Acc<T>::type;
+  constexpr int N = Pack<T>::N;
+  const DevPeers& P = a.peers;
+  const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x, n = P.n, me = P.rank;
+  if (tid == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, me);
+  const uint64_t call = mine->oneShotCalls[cta] + 1;
+  const uint64_t parity = call & 1;
+  const uint64_t slot = P.layout.oneShotSlotBytes;
+  const uint64_t V = a.bytes / 16;                           // the launcher guarantees bytes % 16 == 0
+  const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
+  // push my slice into slot[parity][me] of every peer
+  for (uint64_t i = lo + tid; i < hi; i += kThreads) {
+    const uint4 v = ldLocal128(a.send + i * 16);
+    for (int p = 0; p < n; ++p) {
+      if (p == me) continue;
+      stSys128(P.ctrl[p] + P.layout.oneShotOff + (parity * n + me) * slot + i * 16, v);
+    }
+  }
+  __syncthreads();
+  if (tid < n && tid != me) {
+    __threadfence_system();
+    stReleaseSys(&flagsOf(P, tid)->oneShotReady[cta][me], call);
+    if (!waitFlag(&mine->oneShotReady[cta][tid], call, P, 2u, tid, 0)) sFail = 1;
+  }
+  __syncthreads();
+  if (sFail == 0) {
+    const char* base = P.ctrl[me] + P.layout.oneShotOff + parity * n * slot;
+    for (uint64_t i = lo + tid; i < hi; i += kThreads) {
+      A acc[N];
+      // ascending rank order on every rank: identical bytes everywhere
+      for (int p = 0; p < n; ++p) {
+        const uint4 v = (p == me) ? ldLocal128(a.send + i * 16) : ldSys128(base + (uint64_t)p * slot + i * 16);
+        if (p == 0) accInit<T>(acc, v); else accFold<T>(acc, v, a.op);
+      }
+      stLocal128(a.recv + i * 16, accFinish<T>(acc, a.divisor));
+    }
+  }
+  if (tid == 0) mine->oneShotCalls[cta] = call;
+}
+
+// ---- NVLS ---------------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ uint4 mmLdReduce(const void* mc, int op);
+template <> __device__ __forceinline__ uint4 mmLdReduce<float>(const void* mc, int) { return mmLdReduceAddF32(mc); }
+template <> __device__ __forceinline__ uint4 mmLdReduce<__nv_bfloat16>(const void* mc, int op) {
+  return op == mcclMin ? mmLdReduceMinBf16(mc) : (op == mcclMax ? mmLdReduceMaxBf16(mc) : mmLdReduceAddBf16(mc));
+}
+template <> __device__ __forceinline__ uint4 mmLdReduce<__half>(const void* mc, int op) {
+  return op == mcclMin ? mmLdReduceMinF16(mc) : (op == mcclMax ? mmLdReduceMaxF16(mc) : mmLdReduceAddF16(mc));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) nvlsKernel(const __grid_constant__ NvlsArgs a) {
+  __shared__ int sFail;
+  using A = typename Acc<T>::type;
+  constexpr int N = Pack<T>::N;
+  const DevPeers& P = a.peers;
+  const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
+  if (tid == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, P.rank);
+  uint64_t epoch = mine->epoch[cta];
+  bool ok = ctaBarrier(P, epoch, &sFail);
+  if (ok && a.active) {
+    const uint64_t V = a.bytes / 16;
+    const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
+    constexpr int U = 4;
+    for (uint64_t i = lo + tid; i < hi; i += (uint64_t)U * kThreads) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t idx = i + (uint64_t)u * kThreads;
+        if (idx < hi) v[u] = a.loadReduce ? mmLdReduce<T>(a.mcSrc + idx * 16, a.op) : ldLocal128(a.src + idx * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t idx = i + (uint64_t)u * kThreads;
+        if (idx < hi) {
+          uint4 out = v[u];
+          if (a.divisor > 1) {
+            A acc[N];
+            accInit<T>(acc, out);
+            out = accFinish<T>(acc, a.divisor);
+          }
+          if (a.mcStore) mmStore128(a.mcDst + idx * 16, out); else stLocal128(a.dst + idx * 16, out);
+        }
+      }
+    }
+  }
+  if (ok) ok = ctaBarrier(P, epoch, &sFail);
+  if (tid == 0) mine->epoch[cta] = epoch;
+}
+
+// ---- ring -----------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) ringKernel(const __grid_constant__ RingArgs a) {
+  __shared__ int sFail;
+  using A = typename Acc<T>::type;
+  constexpr int N = Pack<T>::N;
+  const DevPeers& P = a.peers;
+  const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x, n = P.n, r = P.rank;
+  if (tid == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, r);
+  uint64_t epoch = mine->epoch[cta];
+  bool ok = ctaBarrier(P, epoch, &sFail);
+  const uint64_t tag = epoch << 10;                 // step signals of this call: tag + steps completed
+  const uint64_t V = a.bytes / 16;
+  char* own = a.buf[r];
+  const char* prevBuf = a.buf[a.prev];
+  uint64_t* nextSig = &flagsOf(P, a.next)->sig[cta][r];
+  const uint64_t* prevSig = &mine->sig[cta][a.prev];
+  int done = 0;
+  for (int step = 0; ok && step < 2 * (n - 1); ++step) {
+    const bool reducing = step < n - 1;
+    const int i = reducing ? step : step - (n - 1);
+    const int chunk = reducing ? ((r - (i + 1)) % n + n) % n : ((r - i) % n + n) % n;
+    if (step > 0) {
+      if (tid == 0 && !waitFlag(prevSig, tag + step, P, 2u, a.prev, step)) sFail = 1;
+      __syncthreads();
+      if (sFail) { ok = false; break; }
+    }
+    const uint64_t c0 = sliceLo(V, n, chunk), c1 = sliceLo(V, n, chunk + 1);
+    const uint64_t lo = c0 + sliceLo(c1 - c0, G, cta), hi = c0 + sliceLo(c1 - c0, G, cta + 1);
+    if (reducing) {
+      const int divisor = (i == n - 2) ? a.divisor : 1;    // the last fold completes the chunk
+      for (uint64_t k = lo + tid; k < hi; k += kThreads) {
+        A acc[N];
+        accInit<T>(acc, ldSys128(prevBuf + k * 16));
+        accFold<T>(acc, ldLocal128(own + k * 16), a.op);
+        stLocal128(own + k * 16, accFinish<T>(acc, divisor));
+      }
+    } else {
+      copyVecs(prevBuf, own, lo, hi, tid, kThreads);
+    }
+    __syncthreads();
+    ++done;
+    if (tid == 0) { __threadfence_system(); stReleaseSys(nextSig, tag + done); }
+  }
+  if (ok) ok = ctaBarrier(P, epoch, &sFail);
+  if (tid == 0) mine->epoch[cta] = epoch;
+}
+
+// ---- double-binary tree ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) treeKernel(const __grid_constant__ TreeArgs a) {
+  __shared__ int sFail;
+  using A = typename Acc<T>::type;
+  constexpr int N = Pack<T>::N;
+  const DevPeers& P = a.peers;
+  const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x, r = P.rank;
+  if (tid == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, r);
+  uint64_t epoch = mine->epoch[cta];
+  bool ok = ctaBarrier(P, epoch, &sFail);
+  const uint64_t tag = epoch << 10;
+  // Even CTAs run tree 0 on the first half, odd CTAs tree 1 on the second half (one CTA: both, in turn).
+  const uint64_t V = a.bytes / 16, half = V / 2;
+  for (int t = 0; ok && t < 2; ++t) {
+    if (G > 1 && (cta & 1) != t) continue;
+    const int lanes = G > 1 ? (G + 1 - t) / 2 : 1;          // CTAs working on this tree
+    const int lane = G > 1 ? cta / 2 : 0;
+    const uint64_t h0 = t == 0 ? 0 : half, h1 = t == 0 ? half : V;
+    const uint64_t lo = h0 + sliceLo(h1 - h0, lanes, lane), hi = h0 + sliceLo(h1 - h0, lanes, lane + 1);
+    const int up = a.up[t], d0 = a.down[t][0], d1 = a.down[t][1];
+    // A peer can be my child in one tree and my parent in the other and signals through one slot, so the
+    // two trees use disjoint, increasing values.
+    const uint64_t upTag = tag + 4 * t + 1, downTag = tag + 4 * t + 2;
+    char* own = a.buf[r];
+    // up: fold the children's partial sums into mine
+    if (tid == 0) {
+      if (d0 >= 0 && !waitFlag(&mine->sig[cta][d0], upTag, P, 2u, d0, 1)) sFail = 1;
+      if (d1 >= 0 && !sFail && !waitFlag(&mine->sig[cta][d1], upTag, P, 2u, d1, 1)) sFail = 1;
+    }
+    __syncthreads();
+    if (sFail) { ok = false; break; }
+    const int divisor = up < 0 ? a.divisor : 1;               // the root finishes the sum
+    if (d0 >= 0 || d1 >= 0 || divisor > 1) {
+      for (uint64_t k = lo + tid; k < hi; k += kThreads) {
+        A acc[N];
+        accInit<T>(acc, ldLocal128(own + k * 16));
+        if (d0 >= 0) accFold<T>(acc, ldSys128(a.buf[d0] + k * 16), a.op);
+        if (d1 >= 0) accFold<T>(acc, ldSys128(a.buf[d1] + k * 16), a.op);
+        stLocal128(own + k * 16, accFinish<T>(acc, divisor));
+      }
+    }
+    __syncthreads();
+    if (up >= 0) {
+      if (tid == 0) {
+        __threadfence_system();
+        stReleaseSys(&flagsOf(P, up)->sig[cta][r], upTag);
+        if (!waitFlag(&mine->sig[cta][up], downTag, P, 2u, up, 2)) sFail = 1;   // down: parent holds the result
+      }
+      __syncthreads();
+      if (sFail) { ok = false; break; }
+      copyVecs(a.buf[up], own, lo, hi, tid, kThreads);
+      __syncthreads();
+    }
+    if (tid == 0) {
+      __threadfence_system();
+      if (d0 >= 0) stReleaseSys(&flagsOf(P, d0)->sig[cta][r], downTag);
+      if (d1 >= 0) stReleaseSys(&flagsOf(P, d1)->sig[cta][r], downTag);
+    }
+  }
+  if (ok) ok = ctaBarrier(P, epoch, &sFail);
+  if (tid == 0) mine->epoch[cta] = epoch;
+}
+
+// ---- Send / Recv -------------------------------------------------------------------------------------------------
+// One CTA per flow (peer, direction); ops of a flow run in order.  The sender writes chunks into the
+// receiver's slot (two halves) and publishes a running chunk count; the receiver drains and acknowledges.
+__global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_constant__ P2pArgs a) {
+  __shared__ int sFail;
+  const DevPeers& P = a.peers;
+  const int tid = threadIdx.x, me = P.rank;
+  if (tid == 0) sFail = 0;
+  __syncthreads();
+  CtrlFlags* mine = flagsOf(P, me);
+  // flow = blockIdx.x; ops carry their flow in the upper bits of isSend
+  for (int k = 0; k < a.nOps && sFail == 0; ++k) {
+    const P2pDesc op = a.ops[k];
+    if ((op.isSend >> 1) != (int)blockIdx.x) continue;
+    const bool isSend = op.isSend & 1;
+    const int peer = op.peer;
+    const uint64_t half = P.layout.p2pSlotBytes / 2;
+    const uint64_t nChunks = (op.bytes + half - 1) / half;
+    if (isSend) {
+      uint64_t sent = mine->p2pSent[peer];
+      char* slot = P.ctrl[peer] + P.layout.p2pOff + (uint64_t)me * P.layout.p2pSlotBytes;
+      for (uint64_t c = 0; c < nChunks && sFail == 0; ++c) {
+        const uint64_t seq = sent + c + 1;
+        if (tid == 0 && seq > 2 && !waitFlag(&mine->p2pTail[peer], seq - 2, P, 2u, peer, (int)c)) sFail = 1;
+        __syncthreads();
+        if (sFail) break;
+        const uint64_t off = c * half, len = min(half, op.bytes - off);
+        char* dst = slot + (seq & 1) * half;
+        const char* src = op.buf + off;
+        if (aligned16(src) && (len & 15) == 0) {
+          for (uint64_t i = tid; i < len / 16; i += kThreads) stSys128(dst + i * 16, ldLocal128(src + i * 16));
+        } else {
+          for (uint64_t i = tid; i < len; i += kThreads) dst[i] = src[i];
+        }
+        __syncthreads();
+        if (tid == 0) { __threadfence_system(); stReleaseSys(&flagsOf(P, peer)->p2pHead[me], seq); }
+      }
+      if (tid == 0) mine->p2pSent[peer] = sent + nChunks;
+    } else {
+      uint64_t got = mine->p2pRecvd[peer];
+      const char* slot = P.ctrl[me] + P.layout.p2pOff + (uint64_t)peer * P.layout.p2pSlotBytes;
+      for (uint64_t c = 0; c < nChunks && sFail == 0; ++c) {
+        const uint64_t seq = got + c + 1;
+        if (tid == 0 && !waitFlag(&mine->p2pHead[peer], seq, P, 2u, peer, (int)c)) sFail = 1;
+        __syncthreads();
+        if (sFail) break;
+        const uint64_t off = c * half, len = min(half, op.bytes - off);
+        const char* src = slot + (seq & 1) * half;
+        char* dst = op.buf + off;
+        if (aligned16(dst) && (len & 15) == 0) {
+          for (uint64_t i = tid; i < len / 16; i += kThreads) stLocal128(dst + i * 16, ldSys128(src + i * 16));
+        } else {
+          copyBytes(src, dst, 0, len, tid, kThreads);
+        }
+        __syncthreads();
+        if (tid == 0) { __threadfence_system(); stReleaseSys(&flagsOf(P, peer)->p2pTail[me], seq); }
+      }
+      if (tid == 0) mine->p2pRecvd[peer] = got + nChunks;
+    }
+    __syncthreads();
+  }
+}
+
+// Wait until any peer has announced a chunk this rank has not drained yet; writes the peer into *out
+// (pinned host memory), or -1 after the time budget.
+__global__ void recvAnyProbeKernel(DevPeers P, int* out) {
+  if (threadIdx.x != 0) return;
+  CtrlFlags* mine = flagsOf(P, P.rank);
+  const uint64_t t0 = globalTimerNs();
+  for (;;) {
+    for (int p = 0; p < P.n; ++p) {
+      if (p == P.rank) continue;
+      if (ldAcquireSys(&mine->p2pHead[p]) > mine->p2pRecvd[p]) { *out = p; __threadfence_system(); return; }
+    }
+    if (P.status->abort != 0 || globalTimerNs() - t0 > P.timeoutNs) { *out = -1; __threadfence_system(); return; }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) barrierKernel(DevPeers P) {
+  __shared__ int sFail;
+  if (threadIdx.x == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, P.rank);
+  uint64_t epoch = mine->epoch[blockIdx.x];
+  ctaBarrier(P, epoch, &sFail);
+  if (threadIdx.x == 0) mine->epoch[blockIdx.x] = epoch;
+}
+
+// rows x rowBytes, each row at its own pitch.
+__global__ void __launch_bounds__(kThreads) copyKernel(const char* src, char* dst, uint64_t rows, uint64_t rowBytes,
+                                                       uint64_t srcPitch, uint64_t dstPitch) {
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (uint64_t)gridDim.x * blockDim.x;
+  const bool vec = aligned16(src) && aligned16(dst) && (rowBytes & 15) == 0 && (srcPitch & 15) == 0 && (dstPitch & 15) == 0;
+  if (vec) {
+    const uint64_t perRow = rowBytes / 16, total = perRow * rows;
+    for (uint64_t i = tid; i < total; i += nth) {
+      const uint64_t row = i / perRow, col = i - row * perRow;
+      stLocal128(dst + row * dstPitch + col * 16, ldLocal128(src + row * srcPitch + col * 16));
+    }
+  } else {
+    const uint64_t total = rowBytes * rows;
+    for (uint64_t i = tid; i < total; i += nth) {
+      const uint64_t row = i / rowBytes, col = i - row * rowBytes;
+      dst[row * dstPitch + col] = src[row * srcPitch + col];
+    }
+  }
+}
+
+}  // namespace mccl
