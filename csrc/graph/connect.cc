@@ -8,7 +8,6 @@
 
 namespace mccl {
 
-DEFINE_MCCL_PARAM(Dtree, "DTREE", 0);
 DEFINE_MCCL_PARAM(DtreeMinRanks, "DTREE_MIN_RANKS", 8);
 
 mcclResult_t topoConnect(const TopoSystem& sys, const TopoGraph& ring, const TopoGraph& tree, int rank, Channel* out) {
@@ -30,7 +29,7 @@ mcclResult_t topoConnect(const TopoSystem& sys, const TopoGraph& ring, const Top
   // ---- tree
   if ((int)tree.order.size() != n) MCCLFAIL(mcclInternalError);
   const bool nvlMesh = topoNvlAllToAll(sys);
-  const bool wantDtree = n > 2 && (mcclParamDtree() != 0 || nvlMesh || n > mcclParamDtreeMinRanks());
+  const bool wantDtree = n > 2 && (envInt("MCCL_DTREE", 0) != 0 || nvlMesh || n > mcclParamDtreeMinRanks());
   out->treeParent.assign(n, -1);
   if (wantDtree) {
     out->dtree = true;

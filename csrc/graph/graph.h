@@ -124,7 +124,6 @@ struct Channel {
   bool flatTree = false;          // depth-1 star
   bool dtree = false;             // tree + treeB are a double-binary tree
 };
-MCCL_PARAM(Dtree);
 MCCL_PARAM(DtreeMinRanks);
 
 mcclResult_t topoConnect(const TopoSystem& sys, const TopoGraph& ring, const TopoGraph& tree, int rank, Channel* out);

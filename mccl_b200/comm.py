@@ -62,7 +62,7 @@ def _stream_of(buf, stream):
 def get_unique_id() -> bytes:
     uid = L.UniqueId()
     L.check(L.load().mcclGetUniqueId(C.byref(uid)), "mcclGetUniqueId")
-    return bytes(uid.internal)
+    return C.string_at(C.byref(uid), 128)      # the raw 128 bytes (a c_char array would stop at the first NUL)
 
 
 def unique_id_from_env(ip: str, port: int) -> bytes:
@@ -107,7 +107,7 @@ class Communicator:
         self._transport_keepalive = transport.encode() if transport else None
         if _handle is None:
             uid = L.UniqueId()
-            C.memmove(C.byref(uid), unique_id, 128)
+            C.memmove(C.byref(uid), bytes(unique_id).ljust(128, b"\0")[:128], 128)
             cfg = L.Config(1 if blocking else 0, self._transport_keepalive)
             L.check(self._lib.mcclCommInitRankConfig(C.byref(self._h), n_ranks, uid, rank, C.byref(cfg)),
                     "mcclCommInitRankConfig")
@@ -261,6 +261,7 @@ class Communicator:
         return p.value
 
     def free_raw(self, ptr: int) -> None:
+        self._sym.pop(ptr, None)
         L.check(self._lib.mcclMemFree(self._h, C.c_void_p(ptr)), "mcclMemFree")
 
     def empty(self, shape, dtype=None):

@@ -1,0 +1,221 @@
+"""One rank of a multi-GPU test of the cuda transport (one process per GPU).  Scenario in argv[1]."""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+
+import torch
+
+import mccl_b200 as mccl
+from mccl_b200 import _lib as L
+
+RANK = int(os.environ["MCCL_TEST_RANK"])
+WORLD = int(os.environ["MCCL_TEST_WORLD"])
+PORT = int(os.environ["MCCL_TEST_PORT"])
+ARGS = json.loads(os.environ.get("MCCL_TEST_ARGS", "{}"))
+torch.cuda.set_device(RANK)
+DEV = torch.device("cuda", RANK)
+
+
+def make_comm():
+    return mccl.Communicator(WORLD, mccl.unique_id_from_env("127.0.0.1", PORT), RANK, transport="cuda")
+
+
+def gen(r, n, dtype):
+    g = torch.Generator(device="cuda").manual_seed(1000 + r)
+    if not dtype.is_floating_point:
+        return torch.randint(-1000, 1000, (n,), generator=g, device="cuda", dtype=torch.int64).to(dtype)
+    return (torch.rand(n, generator=g, device="cuda") * 2 - 1).to(dtype)
+
+
+def oracle(n, dtype, op, seed_shift=0):
+    """fp64 (or exact integer) restatement of the reduction over every rank's input."""
+    xs = [gen(r + seed_shift, n, dtype) for r in range(WORLD)]
+    st = torch.stack([x.double() for x in xs]) if dtype.is_floating_point else torch.stack([x.long() for x in xs])
+    if op in ("sum", "avg"):
+        o = st.sum(0)
+        if op == "avg":
+            o = o / WORLD if dtype.is_floating_point else torch.div(o.to(dtype), WORLD, rounding_mode="trunc")
+    elif op == "prod":
+        o = st.prod(0)
+    elif op == "max":
+        o = st.max(0).values
+    else:
+        o = st.min(0).values
+    return o
+
+
+def check(what, got, ref, dtype):
+    if dtype.is_floating_point:
+        tol = {torch.float32: 1e-5, torch.float64: 1e-12, torch.float16: 4e-3, torch.bfloat16: 3e-2}[dtype]
+        err = ((got.double() - ref.double()).abs() / (ref.double().abs() + 1.0)).max().item()
+        assert err <= tol, (what, err)
+    else:
+        assert torch.equal(got, ref.to(got.dtype)), what          # integers are bit exact
+
+
+def canary_ok(comm):
+    return comm.async_error() == L.SUCCESS
+
+
+def matrix():
+    comm = make_comm()
+    quick = ARGS.get("quick", False)
+    sizes = [4, 1024 + 3, (1 << 20) + 8] if quick else [1, 4, 1027, 65536, (1 << 20) + 8, 6 << 20]
+    algos = ["oneshot", "twoshot", "ring", "tree"] + (["nvls"] if comm.nvls else [])
+    dtypes = [torch.float32, torch.bfloat16, torch.float16, torch.int32] + ([] if quick else [torch.int64, torch.float64, torch.uint8])
+    for dtype in dtypes:
+        for n in sizes:
+            for sym in (False, True):
+                for algo in algos:
+                    ops = ("sum", "avg") if algo == "nvls" else (("sum", "avg", "max", "min", "prod") if n <= 1027 else ("sum", "avg"))
+                    for op in ops:
+                        if dtype == torch.uint8 and op in ("avg", "prod"):
+                            continue
+                        x = gen(RANK, n, dtype)
+                        if op == "prod":          # keep products representable: factors in {-1, 1} or near 1
+                            x = torch.sign(x) + (x == 0).to(dtype) if not dtype.is_floating_point else (1 + x / 64).to(dtype)
+                        buf = comm.empty(n, dtype) if sym else torch.empty(n, device=DEV, dtype=dtype)
+                        buf.copy_(x)
+                        with mccl.forced_algo(algo):
+                            comm.all_reduce(buf, op=op)
+                        torch.cuda.synchronize()
+                        assert canary_ok(comm), ("async error", dtype, n, sym, algo, op)
+                        if op == "prod":
+                            xs = []
+                            for r in range(WORLD):
+                                y = gen(r, n, dtype)
+                                xs.append((torch.sign(y) + (y == 0).to(dtype)).long() if not dtype.is_floating_point else (1 + y / 64).to(dtype).double())
+                            ref = torch.stack(xs).prod(0)
+                        else:
+                            ref = oracle(n, dtype, op)
+                        if dtype == torch.uint8:
+                            ref = ref % 256 if op == "sum" else ref
+                        check(("allreduce", dtype, n, sym, algo, comm.last_algo, op), buf, ref, dtype)
+                        if sym:
+                            comm.free_raw(buf.data_ptr())
+    # out of place, sources untouched
+    x = gen(RANK, 70001, torch.float32); keep = x.clone(); y = torch.empty_like(x)
+    comm.all_reduce(x, y, op="sum"); torch.cuda.synchronize()
+    assert torch.equal(x, keep)
+    check("out-of-place", y, oracle(70001, torch.float32, "sum"), torch.float32)
+    comm.finalize(); comm.destroy()
+
+
+def collectives():
+    comm = make_comm()
+    for dtype in (torch.float32, torch.bfloat16, torch.int32):
+        for n in (5, 1024 + 3, 1 << 18):
+            for sym in (False, True):
+                mk = (lambda m: comm.empty(m, dtype)) if sym else (lambda m: torch.empty(m, device=DEV, dtype=dtype))
+                for algo in ["auto", "oneshot", "twoshot"] + (["nvls"] if comm.nvls else []):
+                    with mccl.forced_algo(algo):
+                        x = gen(RANK, n, dtype)
+                        s = mk(n); s.copy_(x); g = mk(n * WORLD)
+                        comm.all_gather(s, g); torch.cuda.synchronize()
+                        assert torch.equal(g, torch.cat([gen(r, n, dtype) for r in range(WORLD)])), ("allgather", dtype, n, sym, algo)
+                        g2 = mk(n * WORLD); g2[RANK * n:(RANK + 1) * n].copy_(x)
+                        comm.all_gather(g2[RANK * n:(RANK + 1) * n], g2); torch.cuda.synchronize()        # in place
+                        assert torch.equal(g2, g), ("allgather in place", dtype, n, sym, algo)
+                        s2 = mk(n * WORLD); s2.copy_(gen(RANK + 50, n * WORLD, dtype)); o2 = mk(n)
+                        comm.reduce_scatter(s2, o2, op="sum"); torch.cuda.synchronize()
+                        check(("reducescatter", dtype, n, sym, algo), o2, oracle(n * WORLD, dtype, "sum", 50)[RANK * n:(RANK + 1) * n], dtype)
+                        for root in {0, WORLD - 1}:
+                            b = mk(n); b.zero_()
+                            if RANK == root:
+                                b.copy_(x)
+                            comm.broadcast(b if RANK == root else None, b, root=root); torch.cuda.synchronize()
+                            assert torch.equal(b, gen(root, n, dtype)), ("broadcast", dtype, n, sym, algo, root)
+                            s3 = mk(n); s3.copy_(x); o3 = mk(n)
+                            comm.reduce(s3, o3, op="avg" if dtype.is_floating_point else "sum", root=root); torch.cuda.synchronize()
+                            if RANK == root:
+                                check(("reduce", dtype, n, sym, algo, root), o3, oracle(n, dtype, "avg" if dtype.is_floating_point else "sum"), dtype)
+                        for t in (s, g, g2, s2, o2):
+                            if sym:
+                                comm.free_raw(t.data_ptr())
+                blk = max(n // WORLD, 1)
+                s4 = mk(blk * WORLD); s4.copy_(gen(RANK, blk * WORLD, dtype)); o4 = mk(blk * WORLD)
+                comm.all_to_all(s4, o4); torch.cuda.synchronize()
+                ref = torch.cat([gen(p, blk * WORLD, dtype)[RANK * blk:(RANK + 1) * blk] for p in range(WORLD)])
+                assert torch.equal(o4, ref), ("alltoall", dtype, n, sym)
+        assert canary_ok(comm)
+    # Send/Recv ring inside a group (both directions at once), odd size
+    x = gen(RANK, 3_000_001, torch.float32); y = torch.empty_like(x); z = torch.empty_like(x)
+    with mccl.group():
+        comm.send(x, (RANK + 1) % WORLD); comm.recv(y, (RANK - 1) % WORLD)
+        comm.send(x, (RANK - 1) % WORLD); comm.recv(z, (RANK + 1) % WORLD)
+    torch.cuda.synchronize()
+    assert torch.equal(y, gen((RANK - 1) % WORLD, 3_000_001, torch.float32))
+    assert torch.equal(z, gen((RANK + 1) % WORLD, 3_000_001, torch.float32))
+    if RANK == 0:
+        seen = set()
+        for _ in range(WORLD - 1):
+            buf = torch.empty(256, device=DEV)
+            src = comm.recv_any(buf); torch.cuda.synchronize()
+            assert torch.all(buf == float(src)); seen.add(src)
+        assert seen == set(range(1, WORLD))
+    else:
+        comm.send(torch.full((256,), float(RANK), device=DEV), 0)
+    torch.cuda.synchronize()
+    comm.finalize(); comm.destroy()
+
+
+def split_and_ddp():
+    from mccl_b200.models.gpt2 import GPT2, GPT2Config
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    comm = make_comm()
+    sub = comm.split(RANK % 2, RANK)
+    members = [r for r in range(WORLD) if r % 2 == RANK % 2]
+    y = torch.full((1000,), RANK + 1.0, device=DEV)
+    sub.all_reduce(y); torch.cuda.synchronize()
+    assert torch.all(y == sum(r + 1.0 for r in members))
+    sub.finalize(); sub.destroy()
+    torch.manual_seed(0)
+    cfg = GPT2Config.tiny()
+    model = GPT2(cfg).to(device=DEV, dtype=torch.bfloat16)
+    ddp = DistributedDataParallel(model, comm, bucket_mb=0.25)
+    g = torch.Generator().manual_seed(7 + RANK)
+    tokens = torch.randint(0, cfg.vocab_size, (4, cfg.seq_len + 1), generator=g).to(DEV)
+    losses = []
+    for _ in range(5):
+        loss = ddp(tokens[:, :-1], tokens[:, 1:]); loss.backward(); ddp.step(lr=3e-3)
+        losses.append(loss.item())
+    assert losses[-1] < losses[0], losses
+    # replicas stay bit-identical: same averaged gradients, same optimizer arithmetic
+    flat = torch.cat([b.param.float() for b in ddp.buckets])
+    gathered = torch.empty(flat.numel() * WORLD, device=DEV)
+    comm.all_gather(flat, gathered); torch.cuda.synchronize()
+    for r in range(WORLD):
+        assert torch.equal(gathered[r * flat.numel():(r + 1) * flat.numel()], flat), f"replica {r} diverged"
+    comm.finalize(); comm.destroy()
+
+
+def device_timeout():
+    """Rank 1 sits out one collective (between steps, nothing of its own in flight).  The others' kernels
+    give up after the device time budget, record why in the status word and return; the host reads it."""
+    comm = make_comm()
+    x = torch.ones(1 << 16, device=DEV)
+    comm.all_reduce(x); torch.cuda.synchronize()
+    assert comm.async_error() == L.SUCCESS
+    comm.host_barrier()
+    if RANK == 1:
+        time.sleep(4.0)                     # takes no part in the next collective
+    else:
+        t0 = time.time()
+        comm.all_reduce(x); torch.cuda.synchronize()          # returns: the wait is bounded
+        assert time.time() - t0 < 10
+        assert comm.async_error() == L.REMOTE_ERROR
+        try:
+            comm.all_reduce(x)
+            raise SystemExit("a poisoned communicator accepted more work")
+        except mccl.MCCLError as e:
+            assert e.code == L.REMOTE_ERROR
+        y = torch.ones(8, device=DEV) * 3              # the CUDA context is intact
+        assert y.sum().item() == 24
+    comm.abort(); comm.destroy()
+
+
+if __name__ == "__main__":
+    globals()[sys.argv[1]]()

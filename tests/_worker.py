@@ -1,0 +1,349 @@
+"""One rank of a multi-process CPU test (tcp transport).  Scenario name in argv[1]; rank/world/port/args in
+the environment (see tests/_mp.py).  Exit code 0 = the rank's checks passed."""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+import mccl_b200 as mccl
+from mccl_b200 import _lib as L
+
+RANK = int(os.environ["MCCL_TEST_RANK"])
+WORLD = int(os.environ["MCCL_TEST_WORLD"])
+PORT = int(os.environ["MCCL_TEST_PORT"])
+ARGS = json.loads(os.environ.get("MCCL_TEST_ARGS", "{}"))
+
+
+def make_comm(blocking=True):
+    return mccl.Communicator(WORLD, mccl.unique_id_from_env("127.0.0.1", PORT), RANK, blocking=blocking, transport="tcp")
+
+
+def data(rank, n, dtype=np.float32):
+    rng = np.random.default_rng(rank)
+    if np.issubdtype(dtype, np.integer):
+        lo, hi = (-100, 100) if np.issubdtype(dtype, np.signedinteger) else (0, 100)
+        return rng.integers(lo, hi, n).astype(dtype)
+    return rng.uniform(-1, 1, n).astype(dtype)
+
+
+def ref_reduce(arrs, op):
+    acc = arrs[0].astype(np.float64) if arrs[0].dtype.kind == "f" else arrs[0].copy()
+    for a in arrs[1:]:
+        b = a.astype(np.float64) if a.dtype.kind == "f" else a
+        if op in ("sum", "avg"):
+            acc = acc + b
+        elif op == "prod":
+            acc = acc * b
+        elif op == "max":
+            acc = np.maximum(acc, b)
+        else:
+            acc = np.minimum(acc, b)
+    if op == "avg":
+        acc = acc / len(arrs) if arrs[0].dtype.kind == "f" else (np.trunc(acc / len(arrs))).astype(arrs[0].dtype)
+    return acc
+
+
+def close(got, ref, dtype):
+    if np.dtype(dtype).kind != "f":
+        return np.array_equal(got, ref.astype(dtype))
+    tol = {2: 2e-2, 4: 1e-5, 8: 1e-12}[np.dtype(dtype).itemsize]
+    return np.max(np.abs(got.astype(np.float64) - ref) / (np.abs(ref) + 1.0)) <= tol * WORLD
+
+
+# ---- scenarios ---------------------------------------------------------------------------------------------
+def baseline_config():
+    """BASELINE config 1: 1 Mi fp32 per rank ~U[-1,1] seeded by rank; five collectives against numpy; split."""
+    comm = make_comm()
+    n = 1 << 20
+    xs = [data(r, n) for r in range(WORLD)]
+    x = xs[RANK]
+    ref = ref_reduce(xs, "sum")
+    out = np.empty_like(x)
+    comm.all_reduce(x, out)
+    assert np.max(np.abs(out - ref) / (np.abs(ref) + 1.0)) < 1e-6
+    g = np.empty(n * WORLD, np.float32)
+    comm.all_gather(x, g)
+    assert np.array_equal(g, np.concatenate(xs))
+    blk = n // WORLD
+    rs = np.empty(blk, np.float32)
+    comm.reduce_scatter(x[: blk * WORLD], rs)
+    assert np.max(np.abs(rs - ref[RANK * blk:(RANK + 1) * blk]) / (np.abs(ref[RANK * blk:(RANK + 1) * blk]) + 1.0)) < 1e-6
+    b = x.copy() if RANK == 0 else np.zeros_like(x)
+    comm.broadcast(b if RANK == 0 else None, b, root=0)
+    assert np.array_equal(b, xs[0])
+    root = 1 % WORLD
+    rd = np.empty_like(x) if RANK == root else None
+    comm.reduce(x, rd, root=root)
+    if RANK == root:
+        assert np.max(np.abs(rd - ref) / (np.abs(ref) + 1.0)) < 1e-6
+    sub = comm.split(RANK, 0)             # {0}, {1}, ...: every rank alone
+    assert sub.size == 1 and sub.rank == 0
+    y = np.full(16, RANK + 1.0, np.float32)
+    sub.all_reduce(y)
+    assert np.all(y == RANK + 1.0)
+    sub.finalize(); sub.destroy()
+    comm.finalize(); comm.destroy()
+
+
+def matrix():
+    """Every collective x forced algorithm x a few dtypes/ops/counts (odd counts, in place)."""
+    comm = make_comm()
+    algos = ARGS.get("algos", ["auto", "ring", "tree", "oneshot"])
+    dtypes = [np.dtype(d) for d in ARGS.get("dtypes", ["float32", "int32", "float16", "float64", "uint8", "int64"])]
+    counts = ARGS.get("counts", [1, 7, 1000, 4099, 300001])
+    for algo in algos:
+        with mccl.forced_algo(algo):
+            for dt in dtypes:
+                for n in counts:
+                    xs = [data(r, n, dt) for r in range(WORLD)]
+                    for op in ("sum", "max", "avg") if dt.kind == "f" else ("sum", "min", "prod"):
+                        if dt.kind != "f" and op == "prod":
+                            xs2 = [np.sign(a).astype(dt) if dt.kind == "i" else (a % 2).astype(dt) for a in xs]
+                        else:
+                            xs2 = xs
+                        buf = xs2[RANK].copy()
+                        comm.all_reduce(buf, op=op)       # in place
+                        assert close(buf, ref_reduce(xs2, op), dt), ("allreduce", algo, dt, n, op)
+                    g = np.empty(n * WORLD, dt)
+                    g[RANK * n:(RANK + 1) * n] = xs[RANK]
+                    comm.all_gather(g[RANK * n:(RANK + 1) * n], g)     # in place slot
+                    assert np.array_equal(g, np.concatenate(xs)), ("allgather", algo, dt, n)
+                    full = [data(r + 100, n * WORLD, dt) for r in range(WORLD)]
+                    o = np.empty(n, dt)
+                    comm.reduce_scatter(full[RANK], o, op="sum")
+                    assert close(o, ref_reduce(full, "sum")[RANK * n:(RANK + 1) * n], dt), ("reducescatter", algo, dt, n)
+                    for root in {0, WORLD - 1}:
+                        b = xs[root].copy() if RANK == root else np.zeros(n, dt)
+                        comm.broadcast(b if RANK == root else None, b, root=root)
+                        assert np.array_equal(b, xs[root]), ("broadcast", algo, dt, n, root)
+                        rd = np.empty(n, dt) if RANK == root else None
+                        comm.reduce(xs[RANK], rd, op="sum", root=root)
+                        if RANK == root:
+                            assert close(rd, ref_reduce(xs, "sum"), dt), ("reduce", algo, dt, n, root)
+    comm.finalize(); comm.destroy()
+
+
+def bf16():
+    import torch
+    comm = make_comm()
+    n = 5003
+    xs = [torch.from_numpy(data(r, n)).to(torch.bfloat16) for r in range(WORLD)]
+    for algo in ("ring", "tree", "oneshot"):
+        with mccl.forced_algo(algo):
+            buf = xs[RANK].clone()
+            comm.all_reduce(buf, op="avg")
+            ref = torch.stack([x.double() for x in xs]).sum(0) / WORLD
+            assert ((buf.double() - ref).abs() / (ref.abs() + 1)).max() < 3e-2 * WORLD, algo
+    comm.finalize(); comm.destroy()
+
+
+def p2p_group():
+    comm = make_comm()
+    n = 100003
+    x = data(RANK, n)
+    y = np.empty_like(x)
+    nxt, prv = (RANK + 1) % WORLD, (RANK - 1) % WORLD
+    with mccl.group():
+        comm.send(x, nxt)
+        comm.recv(y, prv)
+    assert np.array_equal(y, data(prv, n))
+    # all-to-all with provenance tags: value = src * WORLD + dst
+    blk = 513
+    s = np.repeat(np.arange(WORLD, dtype=np.float32) + RANK * WORLD, blk)
+    r = np.empty_like(s)
+    comm.all_to_all(s, r)
+    exp = np.repeat(np.arange(WORLD, dtype=np.float32) * WORLD + RANK, blk)
+    assert np.array_equal(r, exp)
+    # RecvAny: every rank but 0 sends one message to rank 0, which collects them in arrival order
+    if RANK == 0:
+        seen = set()
+        for _ in range(WORLD - 1):
+            buf = np.empty(64, np.float32)
+            src = comm.recv_any(buf)
+            assert np.all(buf == float(src)), (src, buf[:4])
+            seen.add(src)
+        assert seen == set(range(1, WORLD))
+    else:
+        comm.send(np.full(64, float(RANK), np.float32), 0)
+    # a collective recorded inside a group runs at GroupEnd
+    z = np.full(8, 1.0, np.float32)
+    with mccl.group():
+        comm.all_reduce(z)
+    assert np.all(z == WORLD)
+    comm.finalize(); comm.destroy()
+
+
+def nonblocking():
+    comm = make_comm(blocking=False)
+    n = 1 << 18
+    bufs = [data(RANK + 10 * i, n) for i in range(4)]
+    outs = [np.empty(n, np.float32) for _ in range(4)]
+    for b, o in zip(bufs, outs):
+        comm.all_reduce(b, o)                 # returns at once, work runs on the communicator's thread
+    saw_progress = comm.async_error() in (L.SUCCESS, L.IN_PROGRESS)
+    comm.synchronize()
+    assert saw_progress and comm.async_error() == L.SUCCESS
+    for i, o in enumerate(outs):
+        ref = ref_reduce([data(r + 10 * i, n) for r in range(WORLD)], "sum")
+        assert close(o, ref, np.float32)
+    comm.finalize(); comm.destroy()
+
+
+def split_groups():
+    comm = make_comm()
+    color = RANK % 2
+    sub = comm.split(color, key=-RANK)        # reversed order inside each group
+    members = [r for r in range(WORLD) if r % 2 == color]
+    assert sub.size == len(members)
+    assert sub.rank == sorted(members, key=lambda r: -r).index(RANK)
+    y = np.full(32, RANK + 1.0, np.float32)
+    sub.all_reduce(y)
+    assert np.all(y == sum(r + 1.0 for r in members))
+    none = comm.split(mccl.SPLIT_NOCOLOR if RANK == 0 else 5, 0)
+    assert (none is None) == (RANK == 0)
+    if none is not None:
+        assert none.size == WORLD - 1
+        none.finalize(); none.destroy()
+    sub.finalize(); sub.destroy()
+    comm.finalize(); comm.destroy()
+
+
+def usage_errors():
+    comm = make_comm()
+    lib = L.load()
+    x = np.zeros(8, np.float32)
+    import ctypes as C
+    h = C.c_void_p(comm.handle)
+    assert lib.mcclAllReduce(h, None, x.ctypes.data, 8, L.FLOAT32, L.SUM, None) == L.INVALID_ARGUMENT
+    assert lib.mcclAllReduce(h, x.ctypes.data, x.ctypes.data, 8, 99, L.SUM, None) == L.INVALID_ARGUMENT
+    assert lib.mcclAllReduce(h, x.ctypes.data, x.ctypes.data, 8, L.FLOAT32, 17, None) == L.INVALID_ARGUMENT
+    assert lib.mcclAllReduce(h, None, None, 0, L.FLOAT32, L.SUM, None) == L.SUCCESS        # count 0: no-op
+    assert lib.mcclBroadcast(h, x.ctypes.data, x.ctypes.data, 8, L.FLOAT32, WORLD, None) == L.INVALID_ARGUMENT
+    assert lib.mcclSend(h, x.ctypes.data, 8, L.FLOAT32, WORLD + 3, None) == L.INVALID_ARGUMENT
+    assert lib.mcclGroupEnd() == L.INVALID_USAGE
+    # usage errors do not poison the communicator
+    comm.all_reduce(x)
+    assert comm.async_error() == L.SUCCESS
+    comm.finalize(); comm.destroy()
+
+
+def abort_unblocks():
+    """Rank 0 parks in a receive nobody will satisfy; a second thread aborts; the call returns an error."""
+    comm = make_comm()
+    comm.host_barrier()
+    if RANK == 0:
+        err = {}
+
+        def park():
+            try:
+                comm.recv(np.empty(1 << 16, np.float32), 1 % WORLD)
+                err["rc"] = "returned"
+            except mccl.MCCLError as e:
+                err["rc"] = e.code
+        t = threading.Thread(target=park)
+        t.start()
+        time.sleep(0.5)
+        comm.abort()
+        t.join(timeout=20)
+        assert not t.is_alive(), "abort did not unblock the receive"
+        assert err.get("rc") not in (None, "returned"), err
+        assert comm.async_error() == L.INVALID_USAGE
+    else:
+        time.sleep(1.5)
+        comm.abort()
+    # aborted communicators are destroyed without a finalize barrier
+    comm.destroy()
+
+
+def peer_dies():
+    """Rank 1 exits before the collective; the others get an error (not a hang) and the error is sticky."""
+    comm = make_comm()
+    comm.host_barrier()
+    if RANK == 1:
+        os._exit(0)
+    time.sleep(0.3)
+    x = np.ones(1 << 20, np.float32)
+    try:
+        comm.all_reduce(x)
+        raise SystemExit("all_reduce with a dead peer returned success")
+    except mccl.MCCLError as e:
+        assert e.code in (L.SYSTEM_ERROR, L.REMOTE_ERROR), e.code
+    assert comm.async_error() in (L.SYSTEM_ERROR, L.REMOTE_ERROR)
+    try:
+        comm.all_reduce(x)
+        raise SystemExit("second call on a failed communicator returned success")
+    except mccl.MCCLError as e:
+        assert e.code in (L.SYSTEM_ERROR, L.REMOTE_ERROR)
+    comm.abort(); comm.destroy()
+
+
+def never_joins():
+    """Rank WORLD-1 never calls init: everyone else fails the rendezvous within the deadline."""
+    if RANK == WORLD - 1:
+        return
+    t0 = time.time()
+    try:
+        make_comm()
+        raise SystemExit("init succeeded without the last rank")
+    except mccl.MCCLError as e:
+        assert e.code in (L.SYSTEM_ERROR, L.REMOTE_ERROR), e.code
+    assert time.time() - t0 < 30
+
+
+def inject_socket_fault():
+    """MCCL_FAULT_INJECT=send:N on rank 0 makes its Nth socket send fail: the collective reports a fatal error."""
+    comm = make_comm()
+    x = np.ones(1 << 16, np.float32)
+    failed = False
+    for _ in range(6):
+        try:
+            comm.all_reduce(x.copy())
+        except mccl.MCCLError as e:
+            assert e.code in (L.SYSTEM_ERROR, L.REMOTE_ERROR)
+            failed = True
+            break
+    assert failed, "the injected fault never surfaced"
+    comm.abort(); comm.destroy()
+
+
+def ddp_cpu():
+    """Two-process DDP on the tcp transport equals single-process training on the concatenated batch."""
+    import torch
+    from mccl_b200.models.gpt2 import GPT2, GPT2Config
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    comm = make_comm()
+    torch.manual_seed(0)
+    cfg = GPT2Config.tiny()
+    model = GPT2(cfg)
+    ddp = DistributedDataParallel(model, comm, bucket_mb=0.25)
+    assert len(ddp.buckets) > 2
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, cfg.vocab_size, (2 * WORLD, cfg.seq_len + 1), generator=g)
+    mine = tokens[2 * RANK: 2 * RANK + 2]
+    torch.manual_seed(0)
+    single = GPT2(cfg)
+    ref = DistributedDataParallel(single, None, bucket_mb=0.25)
+    # gradients of the first step: the bucket all-reduce (avg) must reproduce the global-batch gradient
+    loss = ddp(mine[:, :-1], mine[:, 1:]); loss.backward(); ddp.finish_backward()
+    l2 = ref(tokens[:, :-1], tokens[:, 1:]); l2.backward()
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), single.named_parameters()):
+        assert torch.allclose(p1.grad, p2.grad, atol=1e-6, rtol=1e-4), (n1, (p1.grad - p2.grad).abs().max().item())
+    ddp.step(lr=1e-3); ref.step(lr=1e-3)
+    for _ in range(2):
+        loss = ddp(mine[:, :-1], mine[:, 1:]); loss.backward(); ddp.step(lr=1e-3)
+        l2 = ref(tokens[:, :-1], tokens[:, 1:]); l2.backward(); ref.step(lr=1e-3)
+    # Adam divides by sqrt(v): elements with near-zero gradients amplify rounding, so the bound is a
+    # fraction of the total possible movement (3 steps x lr).
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), single.named_parameters()):
+        assert (p1 - p2).abs().max().item() < 1.5e-3, (n1, (p1 - p2).abs().max().item())
+        assert (p1 - p2).abs().mean().item() < 5e-5, (n1, (p1 - p2).abs().mean().item())
+    comm.finalize(); comm.destroy()
+
+
+if __name__ == "__main__":
+    globals()[sys.argv[1]]()

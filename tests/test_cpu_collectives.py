@@ -1,0 +1,55 @@
+"""Multi-process tests of the tcp transport on loopback (no GPU): the reference's MCCL_COLL_MAIN,
+MCCL_BOOTSTRAP_MAIN and MCCL_COMM_MAIN probes (src/coll/coll.cc:110-237, src/bootstrap.cc:88-109,
+src/comm.cc:360-389) grown into a matrix."""
+import pytest
+
+from _mp import assert_all_ok, run_ranks
+
+
+def test_baseline_config_two_ranks():
+    assert_all_ok(run_ranks(2, "baseline_config"))
+
+
+@pytest.mark.parametrize("world", [2, 3, 5])
+def test_matrix(world):
+    args = {"counts": [1, 7, 4099, 70001]} if world != 3 else {"counts": [1000, 300001], "dtypes": ["float32", "int32"]}
+    assert_all_ok(run_ranks(world, "matrix", args=args, timeout=300))
+
+
+def test_matrix_double_binary_tree():
+    assert_all_ok(run_ranks(6, "matrix", env={"MCCL_DTREE": "1"},
+                            args={"algos": ["tree"], "dtypes": ["float32"], "counts": [3, 5000]}))
+
+
+def test_matrix_single_ring_no_direct():
+    assert_all_ok(run_ranks(4, "matrix", env={"MCCL_DUAL_RINGS": "0", "MCCL_DIRECT_MAX_BYTES": "0", "MCCL_NSOCKS": "1"},
+                            args={"algos": ["auto", "ring"], "dtypes": ["float32"], "counts": [9, 400001]}))
+
+
+def test_matrix_striped_dual_ring_large():
+    assert_all_ok(run_ranks(3, "matrix", env={"MCCL_NSOCKS": "4", "MCCL_PIPELINE_CHUNKS": "3"},
+                            args={"algos": ["ring", "tree"], "dtypes": ["float32"], "counts": [1 << 20]}))
+
+
+def test_bf16():
+    assert_all_ok(run_ranks(3, "bf16"))
+
+
+def test_p2p_group_alltoall_recvany():
+    assert_all_ok(run_ranks(4, "p2p_group"))
+
+
+def test_nonblocking_worker():
+    assert_all_ok(run_ranks(2, "nonblocking"))
+
+
+def test_split():
+    assert_all_ok(run_ranks(5, "split_groups"))
+
+
+def test_usage_errors_do_not_latch():
+    assert_all_ok(run_ranks(2, "usage_errors"))
+
+
+def test_ddp_matches_single_process():
+    assert_all_ok(run_ranks(2, "ddp_cpu"))

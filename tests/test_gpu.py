@@ -1,0 +1,107 @@
+"""GPU tests (marker `gpu`).  Single-GPU tests run the native kernels that need no peer; multi-GPU tests
+start one process per GPU and compare every collective kernel with an fp64 / exact-integer PyTorch oracle."""
+import pytest
+import torch
+
+from _mp import assert_all_ok, run_ranks
+
+pytestmark = pytest.mark.gpu
+
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+need2 = pytest.mark.skipif(NGPU < 2, reason="needs two GPUs")
+
+
+def _require_cuda():
+    if NGPU < 1:
+        pytest.fail("GPU tests need a CUDA device (run the CPU tier with -m 'not gpu')")
+
+
+def test_fused_adamw_matches_fp32_reference():
+    _require_cuda()
+    from mccl_b200.ops.optim import adamw_reference, fused_adamw_
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    for n in (8, 1000, 1003, (1 << 20) + 5):
+        master = torch.randn(n, device=dev)
+        param = master.to(torch.bfloat16)
+        m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        rm, rma, rv = master.clone(), m.clone(), v.clone()
+        for step in (1, 2, 3):
+            grad = (torch.randn(n, device=dev) * 0.1).to(torch.bfloat16)
+            g2 = grad.clone()
+            fused_adamw_(param, master, m, v, grad, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, grad_scale=0.5, step=step)
+            ref_p = adamw_reference(rm, rma, rv, g2, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, grad_scale=0.5, step=step)
+            torch.cuda.synchronize()
+            assert torch.allclose(master, rm, rtol=1e-5, atol=1e-6)
+            assert torch.allclose(m, rma, rtol=1e-5, atol=1e-7) and torch.allclose(v, rv, rtol=1e-5, atol=1e-9)
+            assert torch.equal(param, ref_p) or (param.float() - ref_p.float()).abs().max() <= 2 ** -7 * ref_p.float().abs().max()
+            assert torch.count_nonzero(grad) == 0              # the kernel clears the gradient for the next step
+
+
+def test_single_rank_cuda_communicator():
+    _require_cuda()
+    import mccl_b200 as mccl
+    torch.cuda.set_device(0)
+    comm = mccl.Communicator(1, mccl.get_unique_id(), 0, transport="cuda")
+    assert comm.transport == "cuda" and comm.size == 1 and comm.device == 0
+    x = torch.randn(100003, device="cuda")
+    y = torch.empty_like(x)
+    comm.all_reduce(x, y, op="avg")
+    g = torch.empty_like(x)
+    comm.all_gather(x, g)
+    s = comm.empty(4096, torch.bfloat16)
+    s.fill_(2.0)
+    comm.all_reduce(s, op="sum")
+    torch.cuda.synchronize()
+    assert torch.equal(x, y) and torch.equal(x, g) and torch.all(s == 2.0)
+    assert comm.peer_pointer(s, 0) == s.data_ptr()
+    assert comm.launch_count >= 2 and comm.async_error() == 0
+    assert "gpu" in comm.topo_xml()
+    comm.finalize(); comm.destroy()
+
+
+def test_graft_smoke():
+    _require_cuda()
+    import __graft_entry__ as entry
+    entry.smoke()
+
+
+@need2
+def test_all_reduce_matrix_two_gpus():
+    assert_all_ok(run_ranks(2, "matrix", worker="_gpu_worker.py", timeout=900))
+
+
+@need2
+def test_collectives_two_gpus():
+    assert_all_ok(run_ranks(2, "collectives", worker="_gpu_worker.py", timeout=900))
+
+
+@need2
+def test_staging_with_small_stage_and_ipc_heap():
+    # A 1 MB stage forces the chunked staging loops; IPC mode exercises the cudaMalloc + cudaIpc fallback.
+    env = {"MCCL_STAGE_MB": "1", "MCCL_HEAP_MODE_IPC": "1"}
+    assert_all_ok(run_ranks(2, "matrix", worker="_gpu_worker.py", env=env, args={"quick": True}, timeout=900))
+
+
+@pytest.mark.skipif(NGPU < 4, reason="needs four GPUs")
+def test_matrix_and_collectives_all_gpus():
+    n = 8 if NGPU >= 8 else 4
+    assert_all_ok(run_ranks(n, "matrix", worker="_gpu_worker.py", args={"quick": True}, timeout=1200))
+    assert_all_ok(run_ranks(n, "collectives", worker="_gpu_worker.py", timeout=1200))
+
+
+@pytest.mark.skipif(NGPU < 3, reason="needs three GPUs")
+def test_odd_world_size():
+    assert_all_ok(run_ranks(3, "matrix", worker="_gpu_worker.py", args={"quick": True}, timeout=900))
+
+
+@need2
+def test_split_and_ddp():
+    assert_all_ok(run_ranks(min(NGPU, 4), "split_and_ddp", worker="_gpu_worker.py", timeout=600))
+
+
+@need2
+def test_device_wait_times_out_cleanly():
+    # Bounded device waits, NVLS off, plain peer loads: a rank that sits out is reported, nothing hangs or traps.
+    env = {"MCCL_DEVICE_TIMEOUT_MS": "1000", "MCCL_NVLS_ENABLE": "0"}
+    assert_all_ok(run_ranks(2, "device_timeout", worker="_gpu_worker.py", env=env, timeout=120))

@@ -1,0 +1,259 @@
+"""Single-process unit tests of the host-side subsystems on synthetic inputs (the role of the reference's
+MCCL_TREES_MAIN, MCCL_CONNECT_MAIN, MCCL_XML_MAIN and MCCL_ALLOC_MAIN probes)."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+import mccl_b200 as mccl
+from mccl_b200 import _lib as L
+
+
+def test_version_and_strings(lib):
+    v = C.c_int()
+    assert lib.mcclGetVersion(C.byref(v)) == 0 and v.value == 100
+    assert lib.mcclResultStr(L.REMOTE_ERROR) == b"remote error"
+    assert lib.mcclDataTypeStr(L.BFLOAT16) == b"bfloat16"
+    assert lib.mcclRedOpStr(L.AVG) == b"avg"
+    assert [lib.mcclAlgoStr(i) for i in range(5)] == [b"ring", b"tree", b"oneshot", b"twoshot", b"nvls"]
+    assert [lib.mcclDataSize(i) for i in range(10)] == [1, 1, 4, 4, 8, 8, 2, 2, 4, 8]
+    assert lib.mcclDataSize(42) == 0
+
+
+def test_param_parsing(lib, monkeypatch):
+    monkeypatch.setenv("MCCL_UNIT_X", "0x20")
+    assert lib.mcclDbgParam(b"MCCL_UNIT_X", 5) == 32
+    monkeypatch.setenv("MCCL_UNIT_X", "junk")
+    assert lib.mcclDbgParam(b"MCCL_UNIT_X", 5) == 5
+    monkeypatch.delenv("MCCL_UNIT_X")
+    assert lib.mcclDbgParam(b"MCCL_UNIT_X", -7) == -7
+
+
+def test_algo_list_parsing(lib):
+    en = (C.c_int * 5)()
+    assert lib.mcclDbgParseList(b"ring,tree", en) == 0 and list(en) == [1, 1, 0, 0, 0]
+    assert lib.mcclDbgParseList(b"^ring", en) == 0 and list(en) == [0, 1, 1, 1, 1]
+    assert lib.mcclDbgParseList(b"NVLS", en) == 0 and list(en) == [0, 0, 0, 0, 1]
+    assert lib.mcclDbgParseList(b"", en) == 0 and list(en) == [1] * 5
+    assert lib.mcclDbgParseList(b"bogus", en) == L.INVALID_ARGUMENT
+
+
+NP_TYPES = {L.INT8: np.int8, L.UINT8: np.uint8, L.INT32: np.int32, L.UINT32: np.uint32, L.INT64: np.int64,
+            L.UINT64: np.uint64, L.FLOAT16: np.float16, L.FLOAT32: np.float32, L.FLOAT64: np.float64}
+
+
+@pytest.mark.parametrize("dt", sorted(NP_TYPES))
+@pytest.mark.parametrize("op", ["sum", "prod", "max", "min"])
+def test_host_reduce_all_types(lib, dt, op):
+    npdt = NP_TYPES[dt]
+    rng = np.random.default_rng(dt * 7 + len(op))
+    n = 4099 if dt != L.FLOAT32 else (1 << 21) + 3      # the large one takes the parallel path
+    if np.dtype(npdt).kind == "f":
+        a, b = rng.uniform(-2, 2, n).astype(npdt), rng.uniform(-2, 2, n).astype(npdt)
+    else:
+        a, b = rng.integers(0, 11, n).astype(npdt), rng.integers(0, 11, n).astype(npdt)
+    ref = {"sum": a + b, "prod": a * b, "max": np.maximum(a, b), "min": np.minimum(a, b)}[op]
+    dst = a.copy()
+    assert lib.mcclDbgHostReduce(dst.ctypes.data, b.ctypes.data, n, dt, L.OPS[op]) == 0
+    if npdt == np.float16:
+        assert np.allclose(dst.astype(np.float32), ref.astype(np.float32), rtol=2e-3, atol=2e-3)
+    else:
+        assert np.array_equal(dst, ref)
+
+
+def test_host_reduce_bf16_and_scale(lib):
+    import torch
+    a = torch.randn(5001).to(torch.bfloat16)
+    b = torch.randn(5001).to(torch.bfloat16)
+    dst = a.clone()
+    assert lib.mcclDbgHostReduce(dst.data_ptr(), b.data_ptr(), 5001, L.BFLOAT16, L.SUM) == 0
+    assert torch.equal(dst, (a.float() + b.float()).to(torch.bfloat16))       # widen, add, round to nearest even
+    nan = torch.tensor([float("nan"), 1.0]).to(torch.bfloat16)
+    one = torch.ones(2).to(torch.bfloat16)
+    lib.mcclDbgHostReduce(nan.data_ptr(), one.data_ptr(), 2, L.BFLOAT16, L.SUM)
+    assert torch.isnan(nan[0]) and nan[1] == 2
+    x = np.arange(-8, 8, dtype=np.int32)
+    y = x.copy()
+    assert lib.mcclDbgHostScale(y.ctypes.data, y.size, L.INT32, 3) == 0
+    assert np.array_equal(y, np.trunc(x / 3).astype(np.int32))               # integer avg truncates
+    f = np.linspace(-1, 1, 1001, dtype=np.float32)
+    g = f.copy()
+    lib.mcclDbgHostScale(g.ctypes.data, g.size, L.FLOAT32, 4)
+    assert np.allclose(g, f / 4)
+
+
+def _dtree(lib, n, r):
+    out = (C.c_int * 6)()
+    lib.mcclDbgDtree(n, r, out)
+    return list(out)
+
+
+@pytest.mark.parametrize("n", list(range(1, 66)) + [100, 127, 128, 129, 255, 256])
+def test_double_binary_tree_invariants(lib, n):
+    trees = [_dtree(lib, n, r) for r in range(n)]
+    for t in (0, 1):
+        ups = [trees[r][3 * t] for r in range(n)]
+        kids = [[c for c in trees[r][3 * t + 1:3 * t + 3] if c >= 0] for r in range(n)]
+        roots = [r for r in range(n) if ups[r] < 0]
+        assert len(roots) == 1
+        for r in range(n):
+            for c in kids[r]:
+                assert 0 <= c < n and ups[c] == r                       # parent/child agree
+            if ups[r] >= 0:
+                assert r in kids[ups[r]]
+        seen, stack = set(), [roots[0]]                                  # every rank reachable from the root
+        while stack:
+            v = stack.pop()
+            assert v not in seen
+            seen.add(v)
+            stack.extend(kids[v])
+        assert seen == set(range(n))
+    if n > 2:
+        leaf0 = {r for r in range(n) if trees[r][1] < 0 and trees[r][2] < 0}
+        leaf1 = {r for r in range(n) if trees[r][4] < 0 and trees[r][5] < 0}
+        assert not (leaf0 & leaf1)                                       # nobody is a leaf in both trees
+        r0 = [r for r in range(n) if trees[r][0] < 0][0]
+        r1 = [r for r in range(n) if trees[r][3] < 0][0]
+        assert r0 != r1
+
+
+def _channel(lib, n, r, cuda, dtree=0, cap=8):
+    out = (C.c_int * (4 + 2 * (2 + cap)))()
+    assert lib.mcclDbgSyntheticChannel(n, r, cuda, dtree, out, cap) == 0
+    v = list(out)
+    a, b = v[4:6 + cap], v[6 + cap:]
+    return {"prev": v[0], "next": v[1], "flat": v[2], "dtree": v[3], "upA": a[0], "downA": [c for c in a[2:2 + a[1]]],
+            "upB": b[0], "downB": [c for c in b[2:2 + b[1]]]}
+
+
+@pytest.mark.parametrize("n,cuda", [(2, 0), (4, 0), (16, 0), (2, 1), (8, 1), (5, 1)])
+def test_channel_connect(lib, n, cuda):
+    chans = [_channel(lib, n, r, cuda, cap=16) for r in range(n)]
+    for r, ch in enumerate(chans):                                       # ring: rank order, mutual neighbours
+        assert ch["next"] == (r + 1) % n and ch["prev"] == (r - 1) % n
+    roots = [r for r in range(n) if chans[r]["upA"] < 0]
+    assert len(roots) == 1
+    for r, ch in enumerate(chans):
+        for c in ch["downA"]:
+            assert chans[c]["upA"] == r
+    if cuda and n > 2:
+        assert all(ch["dtree"] for ch in chans)                          # NVSwitch: every pair has its own path
+    if not cuda and n <= 8:
+        assert all(ch["flat"] for ch in chans)                           # uniform LAN: depth-1 star
+        assert sum(len(ch["downA"]) for ch in chans) == n - 1
+    if not cuda and n > 8:
+        assert all(ch["dtree"] for ch in chans)                          # above MCCL_DTREE_MIN_RANKS
+
+
+def test_forced_dtree_on_tcp(lib):
+    chans = [_channel(lib, 6, r, 0, dtree=1) for r in range(6)]
+    assert all(ch["dtree"] for ch in chans)
+    assert len([1 for ch in chans if ch["upB"] < 0]) == 1
+
+
+def _xml(lib, n, cuda, bw=0.0, nvls=0):
+    p = C.c_void_p()
+    assert lib.mcclDbgSyntheticTopoXml(n, cuda, C.c_float(bw), nvls, C.byref(p)) == 0
+    s = C.string_at(p).decode()
+    lib.mcclFreeString(p)
+    return s
+
+
+def test_topology_xml_and_round_trip(lib):
+    import xml.etree.ElementTree as ET
+    s = _xml(lib, 8, 1, 0.0, 1)
+    root = ET.fromstring(s)
+    assert root.tag == "system" and root.get("ranks") == "8" and root.get("nvls") == "1"
+    gpus = root.findall("gpu")
+    assert len(gpus) == 8 and all(len(g.findall("link")) == 7 for g in gpus)
+    assert all(l.get("type") == "NVL" and float(l.get("bw")) == 900.0 for g in gpus for l in g.findall("link"))
+    algos = {a.get("name"): a for a in root.findall("algo")}
+    assert set(algos) == {"ring", "tree", "oneshot", "twoshot", "nvls"} and all(a.get("viable") == "1" for a in algos.values())
+    out = C.c_void_p()
+    assert lib.mcclDbgXmlRoundTrip(s.encode(), C.byref(out)) == 0
+    again = C.string_at(out).decode()
+    lib.mcclFreeString(out)
+    assert ET.tostring(ET.fromstring(again)) == ET.tostring(root)
+    tcp = ET.fromstring(_xml(lib, 3, 0, 2.5))
+    assert len(tcp.findall("host")) == 3
+    assert {a.get("name"): a.get("viable") for a in tcp.findall("algo")}["nvls"] == "0"
+    assert all(float(l.get("bw")) == 2.5 for h in tcp.findall("host") for l in h.findall("link"))
+
+
+def test_paths_detect_missing_peer_link(lib):
+    n = 4
+    types = (C.c_int * (n * n))()
+    hops = (C.c_int * (n * n))()
+    types[0] = 2                                   # sever NVLink between GPUs 1 and 2
+    assert lib.mcclDbgPaths(n, 1, types, hops) == 0
+    t = np.array(list(types)).reshape(n, n)
+    h = np.array(list(hops)).reshape(n, n)
+    assert t[0, 0] == 0 and h[0, 0] == 0                                 # LOC
+    assert t[0, 1] == 1 and h[0, 1] == 1                                 # one NVLink hop
+    assert t[1, 2] == 2 and h[1, 2] == 2                                 # relayed over another GPU
+    assert t[2, 1] == 2
+
+
+def _pick(lib, n, cuda, nvls, nbytes, coll="allreduce", dt=L.FLOAT32, op=L.SUM, algos=b""):
+    a = C.c_int()
+    times = (C.c_float * 5)()
+    rc = lib.mcclDbgTunerPick(n, cuda, nvls, nbytes, L.COLLS[coll], dt | (op << 8), algos, C.byref(a), times)
+    assert rc == 0
+    return L.ALGO_NAMES[a.value], list(times)
+
+
+def test_tuner_choices(lib):
+    assert _pick(lib, 8, 1, 1, 4096)[0] == "oneshot"                     # latency bound
+    assert _pick(lib, 8, 1, 1, 1 << 30)[0] == "nvls"                     # the switch reduces: least traffic
+    assert _pick(lib, 8, 1, 0, 1 << 30)[0] == "twoshot"
+    assert _pick(lib, 8, 1, 1, 1 << 30, op=L.PROD)[0] == "twoshot"       # multimem has no product
+    assert _pick(lib, 8, 1, 1, 1 << 30, algos=b"ring,tree")[0] == "ring"
+    assert _pick(lib, 8, 1, 1, 1 << 30, algos=b"^nvls,twoshot")[0] in ("ring", "tree")
+    name, t = _pick(lib, 8, 1, 1, 1 << 30)
+    assert t[L.ALGO_NVLS] < t[L.ALGO_TWOSHOT] < t[L.ALGO_RING] < t[L.ALGO_TREE] < t[L.ALGO_ONESHOT]
+    assert _pick(lib, 4, 0, 0, 1 << 10)[0] == "oneshot"                  # tcp: direct path below 2 MiB
+    assert _pick(lib, 4, 0, 0, 64 << 20)[0] == "ring"
+    assert _pick(lib, 4, 0, 0, 1 << 10, coll="broadcast")[0] in ("ring", "tree")
+
+
+def test_mem_pool(lib):
+    pool = C.c_void_p()
+    assert lib.mcclMemPoolCreate(1 << 16, 2, C.byref(pool)) == 0
+    bufs = [L.Buf() for _ in range(3)]
+    for b in bufs:
+        assert lib.mcclMemPoolAlloc(pool, C.byref(b)) == 0               # third allocation grows the pool
+        assert b.host % os.sysconf("SC_PAGESIZE") == 0 and b.size == 1 << 16
+    assert len({b.host for b in bufs}) == 3
+    total, free = C.c_int(), C.c_int()
+    lib.mcclMemPoolStats(pool, C.byref(total), C.byref(free))
+    assert (total.value, free.value) == (3, 0)
+    assert lib.mcclMemPoolFree(pool, C.byref(bufs[1])) == 0
+    assert lib.mcclMemPoolFree(pool, C.byref(bufs[1])) == L.INVALID_USAGE  # double free
+    again = L.Buf()
+    assert lib.mcclMemPoolAlloc(pool, C.byref(again)) == 0 and again.host == bufs[1].host   # reuse
+    assert lib.mcclMemPoolDestroy(pool) == 0
+
+
+def test_single_rank_tcp_comm():
+    comm = mccl.Communicator(1, mccl.get_unique_id(), 0, transport="tcp")
+    x = np.arange(10, dtype=np.float32)
+    y = np.zeros_like(x)
+    comm.all_reduce(x, y, op="avg")
+    assert np.array_equal(x, y)
+    comm.all_gather(x, y)
+    assert np.array_equal(x, y)
+    assert comm.transport == "tcp" and comm.size == 1 and not comm.nvls
+    assert "<system" in comm.topo_xml()
+    comm.finalize(); comm.destroy()
+
+
+def test_unknown_transport_is_refused():
+    with pytest.raises(mccl.MCCLError) as e:
+        mccl.Communicator(1, mccl.get_unique_id(), 0, transport="carrier-pigeon")
+    assert e.value.code == L.INVALID_ARGUMENT
+
+
+def test_unique_ids_differ():
+    a, b = mccl.get_unique_id(), mccl.get_unique_id()
+    assert a != b
