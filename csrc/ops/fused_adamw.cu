@@ -21,9 +21,15 @@ struct AdamArgs {
   uint64_t n;
   float lr, beta1, beta2, eps, weightDecay, gradScale, biasCorr1, biasCorr2Sqrt;
   int zeroGrad;              // clear the gradient after use, ready for the next accumulation
+  const float* normSq;       // optional device scalar: squared global gradient norm (for clipping)
+  float maxNorm;             // clip threshold; used only when normSq is set
 };
 
 __global__ void __launch_bounds__(256) adamwKernel(AdamArgs a) {
+  if (a.normSq != nullptr) {   // global-norm clipping: scale = min(1, maxNorm / ||g||), read on the device (no host sync)
+    const float norm = sqrtf(*a.normSq) * a.gradScale;
+    if (norm > a.maxNorm) a.gradScale *= a.maxNorm / (norm + 1e-6f);
+  }
   const uint64_t nVec = a.n / 8;
   const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (uint64_t)gridDim.x * blockDim.x;
   for (uint64_t i = tid; i < nVec; i += nth) {
@@ -70,7 +76,8 @@ __global__ void __launch_bounds__(256) adamwKernel(AdamArgs a) {
 
 extern "C" mcclResult_t mcclFusedAdamW(void* param, float* master, float* expAvg, float* expAvgSq, const void* grad,
                                        uint64_t n, float lr, float beta1, float beta2, float eps, float weightDecay,
-                                       float gradScale, int step, int zeroGrad, mcclStream_t stream) {
+                                       float gradScale, int step, int zeroGrad, const float* normSq, float maxNorm,
+                                       mcclStream_t stream) {
   if (param == nullptr || master == nullptr || expAvg == nullptr || expAvgSq == nullptr || grad == nullptr || step < 1)
     return mcclInvalidArgument;
   if (n == 0) return mcclSuccess;
@@ -86,6 +93,8 @@ extern "C" mcclResult_t mcclFusedAdamW(void* param, float* master, float* expAvg
   a.biasCorr1 = 1.f - powf(beta1, (float)step);
   a.biasCorr2Sqrt = sqrtf(1.f - powf(beta2, (float)step));
   a.zeroGrad = zeroGrad;
+  a.normSq = normSq;
+  a.maxNorm = maxNorm;
   const uint64_t vec = (n + 7) / 8;
   int blocks = (int)((vec + 255) / 256);
   if (blocks > 148 * 8) blocks = 148 * 8;

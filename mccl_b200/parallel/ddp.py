@@ -23,7 +23,7 @@ import torch
 import torch.nn as nn
 
 from ..comm import Communicator
-from ..ops.optim import fused_adamw_
+from ..ops.optim import fused_adamw_, scratch_floats, sum_squares_
 
 
 class _Bucket:
@@ -54,7 +54,8 @@ class DistributedDataParallel(nn.Module):
         self.overlap = overlap
         self.betas, self.eps = betas, eps
         self.step_count = 0
-        self.exposed_comm_ms = 0.0
+        self._norm_sq = None
+        self._norm_scratch = None
         params = [p for p in module.parameters() if p.requires_grad]
         if not params:
             raise ValueError("module has no trainable parameters")
@@ -150,9 +151,25 @@ class DistributedDataParallel(nn.Module):
             if b.done_event is not None and cur is not None:
                 cur.wait_event(b.done_event)
 
-    def step(self, lr: float = 3e-4) -> None:
-        """Wait for the gradient buckets, then one fused AdamW kernel per bucket (it also clears the gradients)."""
+    def step(self, lr: float = 3e-4, max_grad_norm: Optional[float] = None) -> None:
+        """Wait for the gradient buckets, then one fused AdamW kernel per bucket (it also clears the gradients).
+        With `max_grad_norm` the global gradient norm is accumulated bucket by bucket on the device and the
+        optimizer kernels clip by it without a host round trip."""
         self.step_count += 1
+        norm_sq = None
+        if max_grad_norm is not None and self.device.type == "cuda":
+            if self._norm_sq is None:
+                self._norm_sq = torch.zeros(1, device=self.device, dtype=torch.float32)
+                self._norm_scratch = torch.zeros(scratch_floats(max(b.numel for b in self.buckets)), device=self.device,
+                                                 dtype=torch.float32)
+            norm_sq = self._norm_sq
+            cur0 = torch.cuda.current_stream(self.device)
+            for i, b in enumerate(self.buckets):
+                if not b.launched:
+                    self._launch(b)
+                if b.done_event is not None:
+                    cur0.wait_event(b.done_event)
+                sum_squares_(b.grad, norm_sq, self._norm_scratch, accumulate=i > 0)
         for b in self.buckets:
             if not b.launched:
                 self._launch(b)
@@ -162,7 +179,8 @@ class DistributedDataParallel(nn.Module):
                 cur.wait_event(b.done_event)
             if self.device.type == "cuda":
                 fused_adamw_(b.param, b.master, b.exp_avg, b.exp_avg_sq, b.grad, lr=lr, betas=self.betas, eps=self.eps,
-                             weight_decay=b.weight_decay, step=self.step_count, zero_grad=True)
+                             weight_decay=b.weight_decay, step=self.step_count, zero_grad=True, norm_sq=norm_sq,
+                             max_norm=max_grad_norm or 0.0)
             else:  # CPU stand-in for tests of the bucket logic
                 from ..ops.optim import adamw_reference
                 new = adamw_reference(b.master, b.exp_avg, b.exp_avg_sq, b.grad, lr=lr, betas=self.betas, eps=self.eps,

@@ -105,3 +105,33 @@ def test_device_wait_times_out_cleanly():
     # Bounded device waits, NVLS off, plain peer loads: a rank that sits out is reported, nothing hangs or traps.
     env = {"MCCL_DEVICE_TIMEOUT_MS": "1000", "MCCL_NVLS_ENABLE": "0"}
     assert_all_ok(run_ranks(2, "device_timeout", worker="_gpu_worker.py", env=env, timeout=120))
+
+
+def test_sum_squares_and_clipped_step():
+    _require_cuda()
+    from mccl_b200.ops.optim import adamw_reference, fused_adamw_, scratch_floats, sum_squares_
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(1)
+    out = torch.zeros(1, device=dev)
+    for n in (1, 9, 65536, 65537, 3_000_001):
+        x = torch.randn(n + 1, device=dev).to(torch.bfloat16)
+        scratch = torch.zeros(scratch_floats(n), device=dev)
+        for view in (x[:n], x[1:]):                        # the second view is not 16-byte aligned
+            sum_squares_(view, out, scratch)
+            ref = view.float().pow(2).sum()
+            assert torch.allclose(out[0], ref, rtol=2e-5), (n, out.item(), ref.item())
+            sum_squares_(view, out, scratch, accumulate=True)
+            assert torch.allclose(out[0], 2 * ref, rtol=2e-5)
+    # clipping inside the optimizer kernel equals scaling the gradient by min(1, max_norm/||g||)
+    n = 4099
+    master = torch.randn(n, device=dev); param = master.to(torch.bfloat16)
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    rm, rma, rv = master.clone(), m.clone(), v.clone()
+    grad = torch.randn(n, device=dev).to(torch.bfloat16)
+    g2 = grad.clone()
+    sum_squares_(grad, out, torch.zeros(scratch_floats(n), device=dev))
+    fused_adamw_(param, master, m, v, grad, lr=1e-2, weight_decay=0.0, step=1, norm_sq=out, max_norm=1.0)
+    scale = min(1.0, 1.0 / (g2.float().norm().item() + 1e-6))
+    adamw_reference(rm, rma, rv, g2, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, grad_scale=scale, step=1)
+    torch.cuda.synchronize()
+    assert torch.allclose(master, rm, rtol=1e-4, atol=1e-5)
