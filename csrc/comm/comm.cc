@@ -373,6 +373,11 @@ mcclResult_t mcclCommSetMaxCtas(mcclComm_t comm, int maxCtas) {
   comm->maxCtas = maxCtas;
   return mcclSuccess;
 }
+mcclResult_t mcclCommSetCtas(mcclComm_t comm, int ctas) {
+  if (comm == nullptr || ctas < 0) MCCLFAIL(mcclInvalidArgument);
+  comm->forcedCtas = ctas;
+  return mcclSuccess;
+}
 mcclResult_t mcclCommTopoXml(mcclComm_t comm, char** xml) {
   if (comm == nullptr || xml == nullptr) MCCLFAIL(mcclInvalidArgument);
   XmlNode* root = topoToXml(comm->system, comm->graphs, mcclNumAlgos, &comm->tuner);

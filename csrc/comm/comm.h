@@ -48,6 +48,7 @@ struct mcclComm {
   std::atomic<int> lastAlgo{-1};
   std::atomic<uint64_t> launches{0};
   int maxCtas = 0;
+  int forcedCtas = 0;                // exact CTA count for every collective kernel (tuning aid), 0 = planner's choice
   uint32_t splitSeq = 0;
 };
 

@@ -36,15 +36,18 @@ inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) 
 // CTAs for a kernel that moves `bytes` per rank.
 int pickCtas(const mcclComm* c, size_t bytes, int algo) {
   int g;
+  // From sweeps on 8 B200: NVLS saturates with 16-32 CTAs at every size; the load/store algorithms keep
+  // gaining up to 64.
   if (bytes <= (64u << 10)) g = 2;
   else if (bytes <= (512u << 10)) g = 8;
-  else if (bytes <= (8u << 20)) g = 16;
-  else if (bytes <= (64u << 20)) g = 32;
+  else if (bytes <= (1u << 20)) g = 16;
+  else if (bytes <= (64u << 20) || algo == mcclAlgoNvls) g = 32;
   else g = 64;
   if (algo == mcclAlgoOneShot) g = std::min(g, 8);
   const int limit = c->graphs[algo >= 0 && algo < mcclNumAlgos ? algo : mcclAlgoTwoShot].nChannels;
   if (limit > 0) g = std::min(g, std::max(limit, 1));
   if (mcclParamNChannels() > 0) g = (int)mcclParamNChannels();
+  if (c->forcedCtas > 0) g = c->forcedCtas;
   if (c->maxCtas > 0) g = std::min(g, c->maxCtas);
   return std::max(1, std::min(g, MCCL_MAX_CTAS));
 }
@@ -158,8 +161,10 @@ mcclResult_t twoShot(const Call& k, char* const in[], char* const red[], char* o
   a.midBarrier = 1;
   if (collect) {
     char* dst = out ? out : red[r];
-    for (int p = 0; p < n; ++p) {
-      if (p == r) continue;
+    // Rank r starts with peer r+1: at any moment every peer is being read by a different rank, instead
+    // of all ranks draining peer 0 first, then peer 1, ...
+    for (int i = 1; i < n; ++i) {
+      const int p = (r + i) % n;
       const uint64_t q0 = shardOff(bytes, n, p), q1 = shardEnd(bytes, n, p);
       a.jobs[a.nJobs++] = CopyJob{red[p] + q0, dst + q0, q1 - q0};
     }
@@ -212,15 +217,23 @@ bool nvlsType(mcclDataType_t dt, mcclRedOp_t op) {
   return false;
 }
 
-mcclResult_t launchNvls(const Call& k, const NvlsArgs& a, bool reducing) {
-  if (!reducing) { nvlsKernel<float><<<a.nCtas, kThreads, 0, k.s>>>(a); return launched(k.c, "nvlsKernel"); }
+template <int U>
+mcclResult_t launchNvlsU(const Call& k, const NvlsArgs& a, bool reducing) {
+  if (!reducing) { nvlsKernel<float, U><<<a.nCtas, kThreads, 0, k.s>>>(a); return launched(k.c, "nvlsKernel"); }
   switch (k.dt) {
-    case mcclFloat32:  nvlsKernel<float><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
-    case mcclFloat16:  nvlsKernel<__half><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
-    case mcclBfloat16: nvlsKernel<__nv_bfloat16><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
+    case mcclFloat32:  nvlsKernel<float, U><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
+    case mcclFloat16:  nvlsKernel<__half, U><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
+    case mcclBfloat16: nvlsKernel<__nv_bfloat16, U><<<a.nCtas, kThreads, 0, k.s>>>(a); break;
     default: return mcclInvalidArgument;
   }
   return launched(k.c, "nvlsKernel");
+}
+
+mcclResult_t launchNvls(const Call& k, const NvlsArgs& a, bool reducing) {
+  static const int unroll = (int)envInt("MCCL_NVLS_UNROLL", 4);
+  if (unroll >= 8) return launchNvlsU<8>(k, a, reducing);
+  if (unroll <= 2) return launchNvlsU<2>(k, a, reducing);
+  return launchNvlsU<4>(k, a, reducing);
 }
 
 NvlsArgs baseNvls(const Call& k, size_t bytes) {
@@ -359,7 +372,8 @@ mcclResult_t allGather(const Call& k, const void* send, void* recv, size_t sendc
   k.c->lastAlgo.store(mcclAlgoOneShot);
   if ((inPlace && rv.sym()) || sv.sym()) {
     PullArgs a = basePull(k, slot * k.n, mcclAlgoTwoShot);
-    for (int p = 0; p < k.n; ++p) {
+    for (int i = 0; i < k.n; ++i) {
+      const int p = (k.r + i) % k.n;          // rotated start, see twoShot
       const char* src = (inPlace && rv.sym()) ? rv.peer(p) + (size_t)p * slot : sv.peer(p);
       if (p == k.r) { if (!inPlace) a.jobs[a.nJobs++] = CopyJob{static_cast<const char*>(send), out + (size_t)p * slot, slot}; continue; }
       a.jobs[a.nJobs++] = CopyJob{src, out + (size_t)p * slot, slot};
@@ -371,7 +385,8 @@ mcclResult_t allGather(const Call& k, const void* send, void* recv, size_t sendc
     const size_t len = std::min(chunk, slot - off);
     MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
     PullArgs a = basePull(k, len * k.n, mcclAlgoTwoShot);
-    for (int p = 0; p < k.n; ++p) {
+    for (int i = 0; i < k.n; ++i) {
+      const int p = (k.r + i) % k.n;
       if (p == k.r) { if (!inPlace) a.jobs[a.nJobs++] = CopyJob{static_cast<const char*>(send) + off, out + (size_t)p * slot + off, len}; continue; }
       a.jobs[a.nJobs++] = CopyJob{k.stagePeer(p), out + (size_t)p * slot + off, len};
     }
@@ -440,8 +455,8 @@ mcclResult_t bcastOn(const Call& k, char* const work[], char* out, size_t bytes,
       a.dstA = work[r] + o0;
       a.dstA2 = (out && out != work[r]) ? out + o0 : nullptr;
       a.aBytes = o1 - o0;
-      for (int p = 0; p < n; ++p) {
-        if (p == r) continue;
+      for (int i = 1; i < n; ++i) {
+        const int p = (r + i) % n;
         const uint64_t q0 = shardOff(bytes, n, p), q1 = shardEnd(bytes, n, p);
         a.jobs[a.nJobs++] = CopyJob{work[p] + q0, dst + q0, q1 - q0};   // the root's own copy is complete too
       }
@@ -544,7 +559,10 @@ mcclResult_t allToAll(const Call& k, const void* send, void* recv, size_t count)
   char* out = static_cast<char*>(recv);
   if (sv.sym()) {
     PullArgs a = basePull(k, blk * k.n, mcclAlgoTwoShot);
-    for (int p = 0; p < k.n; ++p) a.jobs[a.nJobs++] = CopyJob{sv.peer(p) + (size_t)k.r * blk, out + (size_t)p * blk, blk};
+    for (int i = 0; i < k.n; ++i) {
+      const int p = (k.r + i) % k.n;
+      a.jobs[a.nJobs++] = CopyJob{sv.peer(p) + (size_t)k.r * blk, out + (size_t)p * blk, blk};
+    }
     return launchPull(k.c, a, carrierType(blk), k.s);
   }
   const size_t chunk = stageChunk(k, k.n);
@@ -552,7 +570,10 @@ mcclResult_t allToAll(const Call& k, const void* send, void* recv, size_t count)
     const size_t len = std::min(chunk, blk - off);
     MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), k.n, len, blk, len, k.s));
     PullArgs a = basePull(k, len * k.n, mcclAlgoTwoShot);
-    for (int p = 0; p < k.n; ++p) a.jobs[a.nJobs++] = CopyJob{k.stagePeer(p) + (size_t)k.r * len, out + (size_t)p * blk + off, len};
+    for (int i = 0; i < k.n; ++i) {
+      const int p = (k.r + i) % k.n;
+      a.jobs[a.nJobs++] = CopyJob{k.stagePeer(p) + (size_t)k.r * len, out + (size_t)p * blk + off, len};
+    }
     MCCLCHECK(launchPull(k.c, a, carrierType(len), k.s));
   }
   return mcclSuccess;

@@ -66,7 +66,7 @@ __device__ __forceinline__ void foldVecs(const PullArgs& a, uint64_t lo, uint64_
   using A = typename Acc<T>::type;
   constexpr int N = Pack<T>::N;
   if constexpr (NR > 0) {
-    constexpr int U = (NR <= 2) ? 4 : (NR <= 4 ? 2 : 1);
+    constexpr int U = (NR <= 2) ? 4 : 2;
     for (uint64_t i = lo + tid; i < hi; i += (uint64_t)U * nthreads) {
       uint4 v[U][NR];
 #pragma unroll
@@ -201,7 +201,7 @@ template <> __device__ __forceinline__ uint4 mmLdReduce<__half>(const void* mc, 
   return op == mcclMin ? mmLdReduceMinF16(mc) : (op == mcclMax ? mmLdReduceMaxF16(mc) : mmLdReduceAddF16(mc));
 }
 
-template <typename T>
+template <typename T, int U>
 __global__ void __launch_bounds__(kThreads, 1) nvlsKernel(const __grid_constant__ NvlsArgs a) {
   __shared__ int sFail;
   using A = typename Acc<T>::type;
@@ -215,7 +215,6 @@ __global__ void __launch_bounds__(kThreads, 1) nvlsKernel(const __grid_constant_
   if (ok && a.active) {
     const uint64_t V = a.bytes / 16;
     const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
-    constexpr int U = 4;
     for (uint64_t i = lo + tid; i < hi; i += (uint64_t)U * kThreads) {
       uint4 v[U];
 #pragma unroll

@@ -78,20 +78,24 @@ mcclResult_t tunerInit(const TopoSystem& sys, const TopoGraph graphs[mcclNumAlgo
     out->alphaUs[a] = 0.f;
   }
   if (cudaTransport) {
-    // Fixed per-launch costs in microseconds (kernel launch + entry/exit barriers), defaults from B200
-    // measurements of this library; the per-step term adds the dependent flag crossings.
-    out->alphaUs[mcclAlgoOneShot] = 4.f;
-    out->alphaUs[mcclAlgoTwoShot] = 6.f;
-    out->alphaUs[mcclAlgoNvls] = 6.f;
-    out->alphaUs[mcclAlgoRing] = 6.f;
-    out->alphaUs[mcclAlgoTree] = 6.f;
-    // Achievable fractions of the port rate: loads/stores over NVLink carry packet headers; NVLS moves
-    // each byte once through the switch and sustains more of it.
-    out->bw[mcclAlgoTwoShot] *= 0.78f;
-    out->bw[mcclAlgoOneShot] *= 0.70f;
-    out->bw[mcclAlgoRing] *= 0.60f;
-    out->bw[mcclAlgoTree] *= 0.45f;
-    out->bw[mcclAlgoNvls] *= 0.85f;
+    // Defaults fitted to this library's kernels on B200 (2 and 8 GPUs, bf16 sum, back-to-back launches):
+    // alpha grows with the number of peers a CTA signals and waits for; the bandwidth fractions are what
+    // each algorithm sustains of the 900 GB/s port at 1 GiB once its traffic factor is taken out.
+    // MCCL_CALIBRATE=1 or MCCL_TUNER_CACHE replace them with values measured on the machine at hand.
+    const float n = (float)sys.nodes.size();
+    out->alphaUs[mcclAlgoOneShot] = 8.f + 2.1f * n;
+    out->alphaUs[mcclAlgoNvls] = 15.f + 1.3f * n;
+    out->alphaUs[mcclAlgoTwoShot] = 17.f + 4.2f * n;
+    out->alphaUs[mcclAlgoRing] = 12.f;
+    out->alphaUs[mcclAlgoTree] = 12.f;
+    out->stepUs[mcclAlgoOneShot] = out->stepUs[mcclAlgoNvls] = out->stepUs[mcclAlgoTwoShot] = 0.f;
+    out->stepUs[mcclAlgoRing] = 9.6f;
+    out->stepUs[mcclAlgoTree] = 9.0f;
+    out->bw[mcclAlgoTwoShot] *= 0.60f;
+    out->bw[mcclAlgoOneShot] *= 0.145f;
+    out->bw[mcclAlgoRing] *= 0.23f;
+    out->bw[mcclAlgoTree] *= 0.047f;
+    out->bw[mcclAlgoNvls] *= 0.60f;
     out->oneShotMaxBytes = (size_t)envInt("MCCL_DIRECT_MAX_BYTES", 2 << 20);
     out->oneShotMaxRanks = (int)envInt("MCCL_DIRECT_MAX_RANKS", 16);
   } else {

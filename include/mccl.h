@@ -196,6 +196,8 @@ mcclResult_t mcclCommLastAlgo(mcclComm_t comm, int* algo);
 mcclResult_t mcclCommLaunchCount(mcclComm_t comm, uint64_t* launches);
 /* Limit the CTAs per collective kernel (0 = tuner default); used to leave SMs to overlapped compute. */
 mcclResult_t mcclCommSetMaxCtas(mcclComm_t comm, int maxCtas);
+/* Use exactly `ctas` CTAs for every collective kernel (0 = planner's choice); a tuning aid. */
+mcclResult_t mcclCommSetCtas(mcclComm_t comm, int ctas);
 /* Topology of the communicator as XML (caller frees with mcclFreeString). */
 mcclResult_t mcclCommTopoXml(mcclComm_t comm, char** xml);
 void         mcclFreeString(char* s);

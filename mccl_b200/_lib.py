@@ -108,6 +108,7 @@ def _declare(lib: C.CDLL) -> None:
     fn("mcclSetForcedAlgo", i, i)
     fn("mcclCommLaunchCount", i, vp, P(u64))
     fn("mcclCommSetMaxCtas", i, vp, i)
+    fn("mcclCommSetCtas", i, vp, i)
     fn("mcclCommTopoXml", i, vp, P(C.c_void_p))
     fn("mcclFreeString", None, vp)
     # debug / test hooks (csrc/graph/debug.cc)

@@ -164,6 +164,9 @@ class Communicator:
     def set_max_ctas(self, n: int) -> None:
         L.check(self._lib.mcclCommSetMaxCtas(self._h, n))
 
+    def set_ctas(self, n: int) -> None:
+        L.check(self._lib.mcclCommSetCtas(self._h, n))
+
     def topo_xml(self) -> str:
         p = C.c_void_p()
         L.check(self._lib.mcclCommTopoXml(self._h, C.byref(p)))
