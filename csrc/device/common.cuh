@@ -180,6 +180,20 @@ __device__ __forceinline__ void mmStore128(void* mc, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" :: "l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// Copy vectors [lo, hi) (16-byte units) from src to dst, eight loads in flight per thread.
+__device__ __forceinline__ void copyVecs(const char* src, char* dst, uint64_t lo, uint64_t hi, int tid, int nthreads) {
+  constexpr int U = 8;
+  uint64_t i = lo + tid;
+  for (; i + (uint64_t)(U - 1) * nthreads < hi; i += (uint64_t)U * nthreads) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ldSys128(src + (i + (uint64_t)u * nthreads) * 16);
+#pragma unroll
+    for (int u = 0; u < U; ++u) stLocal128(dst + (i + (uint64_t)u * nthreads) * 16, v[u]);
+  }
+  for (; i < hi; i += nthreads) stLocal128(dst + i * 16, ldSys128(src + i * 16));
+}
+
 // Slice [lo, hi) of `total` units for part `i` of `parts`.
 __device__ __forceinline__ uint64_t sliceLo(uint64_t total, int parts, int i) {
   return (uint64_t)(((unsigned __int128)total * (unsigned)i) / (unsigned)parts);

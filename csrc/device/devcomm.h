@@ -9,7 +9,7 @@
 #include <stdint.h>
 
 #define MCCL_MAX_RANKS 16      // ranks of one NVSwitch domain a kernel can address
-#define MCCL_MAX_CTAS 128      // upper bound on CTAs ("channels") of one collective kernel
+#define MCCL_MAX_CTAS 160      // upper bound on CTAs ("channels") of one collective kernel
 #define MCCL_COLL_THREADS 512
 
 namespace mccl {

@@ -1,0 +1,255 @@
+// Host side of the tcgen05 GEMM and its fused tensor-parallel forms: tensor-map encoding, shape checks,
+// argument set-up and launch.  C ABI so the Python layer can call it with raw pointers.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <mutex>
+
+#include "../../comm/comm.h"
+#include "../../transport/cuda_mem.h"
+#include "gemm_core.cuh"
+
+using namespace mccl;
+using namespace mccl::gemm;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+    cudaGetLastError();
+  });
+  return fn;
+}
+
+// Row-major [rows, cols] bf16 matrix, box = 64 columns (128 bytes, the swizzle width) x boxRows rows.
+mcclResult_t makeMap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t boxRows) {
+  EncodeTiledFn fn = encodeTiled();
+  if (fn == nullptr) MCCLFAIL(mcclSystemError);
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, boxRows};
+  const cuuint32_t elemStrides[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elemStrides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    MCCL_WARN("cuTensorMapEncodeTiled failed with %d (base %p rows %llu cols %llu box %u)", (int)r, base,
+              (unsigned long long)rows, (unsigned long long)cols, boxRows);
+    return mcclInvalidArgument;
+  }
+  return mcclSuccess;
+}
+
+// Widest tile width that divides N and fills the machine's last wave best.
+int pickBN(int M, int N, int sms) {
+  const int cand[] = {256, 224, 192, 160, 128, 96, 64};
+  int best = 0;
+  double bestEff = -1.0;
+  for (int bn : cand) {
+    if (N % bn) continue;
+    const long tiles = (long)(M / BM) * (N / bn);
+    const long waves = (tiles + sms - 1) / sms;
+    // Fraction of issued tile slots doing work, discounted for narrow tiles (less reuse of the A tile).
+    const double eff = (double)tiles / (double)(waves * sms) * (bn >= 192 ? 1.0 : (bn >= 128 ? 0.92 : 0.75));
+    if (eff > bestEff + 1e-9) { bestEff = eff; best = bn; }
+  }
+  return best;
+}
+
+int* errFlagFor(int device) {
+  static std::mutex mu;
+  static int* flags[64] = {nullptr};
+  std::lock_guard<std::mutex> lk(mu);
+  if (device < 0 || device >= 64) return nullptr;
+  if (flags[device] == nullptr) {
+    int* host = nullptr;
+    if (cudaHostAlloc((void**)&host, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    *host = 0;
+    flags[device] = host;
+  }
+  return flags[device];
+}
+
+template <int MODE>
+mcclResult_t launchMode(const GemmArgs& a, int bn, int grid, cudaStream_t s) {
+#define MCCL_GEMM_CASE(BN_)                                                                                          \
+  case BN_: {                                                                                                        \
+    auto kern = tpGemmKernel<BN_, MODE>;                                                                             \
+    static bool attr[64] = {false};                                                                                  \
+    int dev = 0; cudaGetDevice(&dev);                                                                                \
+    if (!attr[dev & 63]) {                                                                                           \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<BN_>::TOTAL) != cudaSuccess) {  \
+        cudaGetLastError(); return mcclSystemError; }                                                                \
+      attr[dev & 63] = true;                                                                                         \
+    }                                                                                                                \
+    kern<<<grid, kThreadsGemm, Smem<BN_>::TOTAL, s>>>(a);                                                             \
+    break;                                                                                                           \
+  }
+  switch (bn) {
+    MCCL_GEMM_CASE(256) MCCL_GEMM_CASE(224) MCCL_GEMM_CASE(192) MCCL_GEMM_CASE(160) MCCL_GEMM_CASE(128) MCCL_GEMM_CASE(96)
+    MCCL_GEMM_CASE(64)
+    default: return mcclInvalidArgument;
+  }
+#undef MCCL_GEMM_CASE
+  return cudaGetLastError() == cudaSuccess ? mcclSuccess : mcclSystemError;
+}
+
+mcclResult_t checkShapes(int M, int N, int K, int nRanks) {
+  if (M <= 0 || N <= 0 || K <= 0 || M % (BM * nRanks) || K % BK || N % 64) {
+    MCCL_WARN("tcgen05 GEMM needs M %% %d == 0, N %% 64 == 0, K %% 64 == 0 (got %d x %d x %d)", BM * nRanks, M, N, K);
+    return mcclInvalidArgument;
+  }
+  return mcclSuccess;
+}
+
+int smCount() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Last error code recorded by a GEMM kernel on the current device (0 = none); reading clears it.
+int mcclTpGemmLastError(void) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* f = errFlagFor(dev);
+  if (f == nullptr) return -1;
+  const int v = *f;
+  *f = 0;
+  return v;
+}
+
+// C[M,N] = act(A[M,K] * B[N,K]^T), bf16 in and out, on the current device.
+mcclResult_t mcclTpGemm(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int maxCtas, mcclStream_t stream) {
+  if (A == nullptr || B == nullptr || C == nullptr) return mcclInvalidArgument;
+  MCCLCHECK(checkShapes(M, N, K, 1));
+  const int sms = maxCtas > 0 ? maxCtas : smCount();
+  const int bn = pickBN(M, N, sms);
+  if (bn == 0) return mcclInvalidArgument;
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  MCCLCHECK(makeMap(&a.mapA, A, M, K, BM));
+  MCCLCHECK(makeMap(&a.mapB, B, N, K, bn));
+  a.M = M; a.N = N; a.K = K;
+  a.C = static_cast<__nv_bfloat16*>(C);
+  a.epilogue = epilogue;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* hostFlag = errFlagFor(dev);
+  if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
+  a.budgetNs = 2000000000ull;
+  const int tiles = (M / BM) * (N / bn);
+  return launchMode<MODE_PLAIN>(a, bn, tiles < sms ? tiles : sms, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Fused all-gather -> GEMM -> activation.  xShard: this rank's [M/n, K] activations in symmetric memory;
+// xFull: local [M, K] workspace; W: [N, K] local weight shard; out: [M, N]; flags: >= 16 uint64 of device
+// memory (zeroed by this call).  Collective over `comm`.
+mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFull, const void* W, void* out, void* flags,
+                                 int M, int N, int K, int epilogue, mcclStream_t stream) {
+  if (comm == nullptr || !comm->cuda || comm->cu == nullptr || xShard == nullptr || xFull == nullptr || W == nullptr ||
+      out == nullptr || flags == nullptr) return mcclInvalidArgument;
+  const int n = comm->nRanks;
+  MCCLCHECK(checkShapes(M, N, K, n));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  CUDACHECK(cudaSetDevice(comm->device));
+  const size_t shardBytes = (size_t)(M / n) * K * 2;
+  Segment* seg = segmentFind(comm->cu, xShard, shardBytes);
+  if (seg == nullptr) {
+    MCCL_WARN("mcclTpAllGatherGemm: the activation shard must live in symmetric memory (mcclMemAlloc)");
+    return mcclInvalidArgument;
+  }
+  const int sms = std::min(smCount(), MCCL_MAX_CTAS);
+  const int bn = pickBN(M, N, sms);
+  if (bn == 0) return mcclInvalidArgument;
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  MCCLCHECK(makeMap(&a.mapA, xFull, M, K, BM));
+  MCCLCHECK(makeMap(&a.mapB, W, N, K, bn));
+  a.M = M; a.N = N; a.K = K;
+  a.C = static_cast<__nv_bfloat16*>(out);
+  a.epilogue = epilogue;
+  int* hostFlag = errFlagFor(comm->device);
+  if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
+  a.peers = comm->cu->peers;
+  a.budgetNs = 2 * a.peers.timeoutNs;
+  a.callIndex = 1;
+  a.shardReady = static_cast<uint64_t*>(flags);
+  const size_t off = (size_t)(static_cast<const char*>(xShard) - seg->local);
+  for (int p = 0; p < n; ++p) a.xPeer[p] = seg->peer[p] + off;
+  a.xFull = static_cast<char*>(xFull);
+  CUDACHECK(cudaMemsetAsync(flags, 0, MCCL_MAX_RANKS * sizeof(uint64_t), s));
+  const int tiles = (M / BM) * (N / bn);
+  // Every CTA's communication warps take part in the copy and in the cross-GPU barriers, so the grid is
+  // the same on every rank and never larger than what is resident at once.
+  const int grid = tiles < sms ? tiles : sms;
+  mcclResult_t rc = launchMode<MODE_AG>(a, bn, grid, s);
+  if (rc == mcclSuccess) comm->launches.fetch_add(1);
+  return rc;
+}
+
+// Fused GEMM -> reduce-scatter over the row (token) dimension.  H: [M, K] local activations; W: [N, K] local
+// weight shard; partial: [M, N] staging in symmetric memory; flags: symmetric memory of at least
+// (16 + M/128 + n * M/(128 n)) uint64, zeroed once at allocation; out: [M/n, N] reduced rows of this rank's
+// block.  callIndex counts the calls made with this flags buffer (1, 2, ...).  Collective over `comm`.
+mcclResult_t mcclTpGemmReduceScatter(mcclComm_t comm, const void* H, const void* W, void* partial, void* flags, void* out,
+                                     int M, int N, int K, uint64_t callIndex, mcclStream_t stream) {
+  if (comm == nullptr || !comm->cuda || comm->cu == nullptr || H == nullptr || W == nullptr || partial == nullptr ||
+      flags == nullptr || out == nullptr || callIndex == 0) return mcclInvalidArgument;
+  const int n = comm->nRanks;
+  MCCLCHECK(checkShapes(M, N, K, n));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  CUDACHECK(cudaSetDevice(comm->device));
+  const int stripes = M / BM, stripesPerBlock = stripes / n;
+  const size_t flagWords = 16 + (size_t)stripes + (size_t)n * stripesPerBlock;
+  Segment* pseg = segmentFind(comm->cu, partial, (size_t)M * N * 2);
+  Segment* fseg = segmentFind(comm->cu, flags, flagWords * 8);
+  if (pseg == nullptr || fseg == nullptr) {
+    MCCL_WARN("mcclTpGemmReduceScatter: staging and flags must live in symmetric memory (mcclMemAlloc)");
+    return mcclInvalidArgument;
+  }
+  const int sms = std::min(smCount(), MCCL_MAX_CTAS);
+  const int bn = pickBN(M, N, sms);
+  if (bn == 0) return mcclInvalidArgument;
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  MCCLCHECK(makeMap(&a.mapA, H, M, K, BM));
+  MCCLCHECK(makeMap(&a.mapB, W, N, K, bn));
+  a.M = M; a.N = N; a.K = K;
+  a.C = static_cast<__nv_bfloat16*>(partial);
+  a.epilogue = EPI_NONE;
+  int* hostFlag = errFlagFor(comm->device);
+  if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
+  a.peers = comm->cu->peers;
+  a.budgetNs = 2 * a.peers.timeoutNs;
+  a.callIndex = callIndex;
+  const size_t poff = (size_t)(static_cast<char*>(partial) - pseg->local), foff = (size_t)(static_cast<char*>(flags) - fseg->local);
+  uint64_t* localFlags = static_cast<uint64_t*>(flags);
+  a.stripeCount = localFlags + 16;
+  for (int p = 0; p < n; ++p) {
+    a.partialPeer[p] = pseg->peer[p] + poff;
+    a.tileReadyPeer[p] = reinterpret_cast<uint64_t*>(fseg->peer[p] + foff) + 16 + stripes;
+  }
+  a.out = static_cast<__nv_bfloat16*>(out);
+  CUDACHECK(cudaMemsetAsync(a.stripeCount, 0, (size_t)stripes * sizeof(uint64_t), s));   // local counters only
+  const int tiles = (M / BM) * (N / bn);
+  const int grid = tiles < sms ? tiles : sms;
+  mcclResult_t rc = launchMode<MODE_RS>(a, bn, grid, s);
+  if (rc == mcclSuccess) comm->launches.fetch_add(1);
+  return rc;
+}
+
+}  // extern "C"

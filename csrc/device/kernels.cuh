@@ -46,20 +46,6 @@ __device__ __forceinline__ void copyBytes(const char* src, char* dst, uint64_t l
   for (uint64_t off = lo + tid; off < hi; off += nthreads) dst[off] = *reinterpret_cast<const volatile char*>(src + off);
 }
 
-// Copy vectors [lo, hi) (16-byte units) from src to dst, eight loads in flight per thread.
-__device__ __forceinline__ void copyVecs(const char* src, char* dst, uint64_t lo, uint64_t hi, int tid, int nthreads) {
-  constexpr int U = 8;
-  uint64_t i = lo + tid;
-  for (; i + (uint64_t)(U - 1) * nthreads < hi; i += (uint64_t)U * nthreads) {
-    uint4 v[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) v[u] = ldSys128(src + (i + (uint64_t)u * nthreads) * 16);
-#pragma unroll
-    for (int u = 0; u < U; ++u) stLocal128(dst + (i + (uint64_t)u * nthreads) * 16, v[u]);
-  }
-  for (; i < hi; i += nthreads) stLocal128(dst + i * 16, ldSys128(src + i * 16));
-}
-
 // Fold vectors [lo, hi) of NR sources (NR = 0: run-time count) into dstA / dstA2.
 template <typename T, int NR>
 __device__ __forceinline__ void foldVecs(const PullArgs& a, uint64_t lo, uint64_t hi, int tid, int nthreads) {
