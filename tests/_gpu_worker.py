@@ -217,5 +217,35 @@ def device_timeout():
     comm.abort(); comm.destroy()
 
 
+def tp_ffn():
+    """Fused all-gather->GEMM->SiLU and GEMM->reduce-scatter against an fp32 PyTorch restatement."""
+    from mccl_b200.parallel.tp import TensorParallelFFN
+    comm = make_comm()
+    tokens, hidden, ffn = ARGS.get("tokens", 128 * WORLD * 2), ARGS.get("hidden", 512), ARGS.get("ffn", 256 * WORLD)
+    def mk(seed, shape, scale):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        return (torch.randn(shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+    xs = [mk(10 + r, (tokens // WORLD, hidden), 1.0) for r in range(WORLD)]
+    wus = [mk(100 + r, (ffn // WORLD, hidden), 0.05) for r in range(WORLD)]
+    wds = [mk(200 + r, (hidden, ffn // WORLD), 0.05) for r in range(WORLD)]
+    layer = TensorParallelFFN(comm, tokens, hidden, ffn, wus[RANK].contiguous(), wds[RANK].contiguous())
+    ref = layer.reference(xs, wus, wds)
+    from mccl_b200.ops import gemm as G
+    for it in range(3):                       # repeated calls reuse flags and staging
+        out = layer.forward(xs[RANK])
+        torch.cuda.synchronize()
+        assert G.last_error() == 0 and comm.async_error() == L.SUCCESS, (G.last_error(), comm.async_error())
+        x_all = torch.cat(xs)
+        assert torch.equal(layer.x_full, x_all), "gathered activations differ"
+        href = torch.nn.functional.silu(x_all.float() @ wus[RANK].float().t())
+        eh = ((layer.h.float() - href).abs() / (href.abs() + 1.0)).max().item()
+        assert eh < 2e-2, ("up projection", it, eh)
+        # Partial sums cross NVLink as bf16, so an output can be off by one bf16 step of a partial (which is
+        # larger than the output where partials cancel): the bound is relative to the largest output.
+        err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
+        assert err < 1e-2, ("ffn output", it, err)
+    comm.finalize(); comm.destroy()
+
+
 if __name__ == "__main__":
     globals()[sys.argv[1]]()

@@ -135,3 +135,37 @@ def test_sum_squares_and_clipped_step():
     adamw_reference(rm, rma, rv, g2, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, grad_scale=scale, step=1)
     torch.cuda.synchronize()
     assert torch.allclose(master, rm, rtol=1e-4, atol=1e-5)
+
+
+def test_tcgen05_gemm_matches_fp32_reference():
+    _require_cuda()
+    from mccl_b200.ops import gemm as G
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    for (M, N, K) in [(128, 64, 64), (256, 448, 192), (1024, 3584, 1024), (384, 8192, 3584)]:
+        x = (torch.randn(M, K, device=dev) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+        for epi in ("none", "silu"):
+            y = G.gemm(x, w, epilogue=epi)
+            torch.cuda.synchronize()
+            assert G.last_error() == 0
+            ref = x.float() @ w.float().t()
+            if epi == "silu":
+                ref = torch.nn.functional.silu(ref)
+            err = ((y.float() - ref).abs() / (ref.abs() + 1.0)).max().item()
+            assert err < 1e-2, (M, N, K, epi, err)
+    with pytest.raises(ValueError):
+        G.gemm(torch.zeros(100, 64, device=dev, dtype=torch.bfloat16), torch.zeros(64, 64, device=dev, dtype=torch.bfloat16))
+
+
+@need2
+def test_fused_tp_ffn_two_gpus():
+    assert_all_ok(run_ranks(2, "tp_ffn", worker="_gpu_worker.py", timeout=300))
+    assert_all_ok(run_ranks(2, "tp_ffn", worker="_gpu_worker.py", timeout=300,
+                            args={"tokens": 2048, "hidden": 1024, "ffn": 7168}))
+
+
+@pytest.mark.skipif(NGPU < 8, reason="needs eight GPUs")
+def test_fused_tp_ffn_eight_gpus():
+    assert_all_ok(run_ranks(8, "tp_ffn", worker="_gpu_worker.py", timeout=600,
+                            args={"tokens": 8192, "hidden": 2048, "ffn": 8192}))
