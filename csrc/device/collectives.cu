@@ -41,7 +41,7 @@ int pickCtas(const mcclComm* c, size_t bytes, int algo) {
   if (bytes <= (64u << 10)) g = 2;
   else if (bytes <= (512u << 10)) g = 8;
   else if (bytes <= (1u << 20)) g = 16;
-  else if (bytes <= (64u << 20) || algo == mcclAlgoNvls) g = 32;
+  else if (bytes <= (8u << 20) || algo == mcclAlgoNvls) g = 32;
   else g = 64;
   if (algo == mcclAlgoOneShot) g = std::min(g, 8);
   const int limit = c->graphs[algo >= 0 && algo < mcclNumAlgos ? algo : mcclAlgoTwoShot].nChannels;
