@@ -86,7 +86,7 @@ def main() -> int:
     def fused_down():
         layer.calls += 1
         mccl._lib.check(lib.mcclTpGemmReduceScatter(h, layer.h.data_ptr(), w_down.data_ptr(), layer.partial.data_ptr(),
-                                                    layer.flags.data_ptr(), layer.out.data_ptr(), M, H, F // n, layer.calls, s()))
+                                                    layer.flags.data_ptr(), layer.out.data_ptr(), layer.accum.data_ptr(), M, H, F // n, layer.calls, s()))
 
     # NCCL + cuBLAS baseline on the same shapes
     x_full = torch.empty(M, H, device=dev, dtype=torch.bfloat16)

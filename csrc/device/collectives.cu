@@ -236,11 +236,13 @@ mcclResult_t launchNvls(const Call& k, const NvlsArgs& a, bool reducing) {
   return launchNvlsU<4>(k, a, reducing);
 }
 
-NvlsArgs baseNvls(const Call& k, size_t bytes) {
+// `rootOnly`: one rank moves the whole message (broadcast, reduce), so it needs the CTAs that an
+// all-reduce spreads over all ranks.
+NvlsArgs baseNvls(const Call& k, size_t bytes, bool rootOnly = false) {
   NvlsArgs a;
   memset(&a, 0, sizeof(a));
   a.peers = k.st->peers;
-  a.nCtas = pickCtas(k.c, bytes, mcclAlgoNvls);
+  a.nCtas = pickCtas(k.c, bytes, rootOnly ? mcclAlgoTwoShot : mcclAlgoNvls);
   a.op = (k.op == mcclAvg) ? mcclSum : k.op;
   a.divisor = 1;
   a.active = 1;
@@ -470,7 +472,7 @@ mcclResult_t broadcast(const Call& k, const void* send, void* recv, size_t count
   const View rv = viewOf(k.st, recv, bytes);
   const bool direct = algo == mcclAlgoOneShot;
   if (algo == mcclAlgoNvls && k.st->nvls && rv.sym() && rv.mc() && bytes % 16 == 0 && al16(recv) && (k.r != root || al16(send))) {
-    NvlsArgs a = baseNvls(k, bytes);
+    NvlsArgs a = baseNvls(k, bytes, true);
     a.loadReduce = 0;
     a.mcStore = 1;
     a.active = k.r == root;
@@ -522,7 +524,7 @@ mcclResult_t reduce(const Call& k, const void* send, void* recv, size_t count, i
   const bool direct = algo == mcclAlgoOneShot;
   if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op) && bytes % 16 == 0 && al16(send) &&
       (k.r != root || al16(recv))) {
-    NvlsArgs a = baseNvls(k, bytes);
+    NvlsArgs a = baseNvls(k, bytes, true);
     a.loadReduce = 1;
     a.mcStore = 0;
     a.active = k.r == root;

@@ -194,6 +194,22 @@ __device__ __forceinline__ void copyVecs(const char* src, char* dst, uint64_t lo
   for (; i < hi; i += nthreads) stLocal128(dst + i * 16, ldSys128(src + i * 16));
 }
 
+// Work split of V units over G CTAs.  Up to 16384 units (256 KB of 16-byte vectors) per CTA it is one
+// contiguous slice each; beyond that the CTAs take 256 KB tiles round-robin, so at any moment all CTAs of a
+// GPU work inside one window of G x 256 KB.  (With one huge contiguous slice per CTA, a 32 GB all-reduce
+// touched 32 windows 128 MB apart on every GPU at once and lost a fifth of its bandwidth.)  The split
+// depends on (V, G) only, so CTA b covers the same units on every rank and in every phase.
+__device__ __forceinline__ uint64_t tileUnits(uint64_t V, int G) {
+  uint64_t per = (V + (uint64_t)G - 1) / (uint64_t)G;
+  per = (per + 511) / 512 * 512;
+  return per > 16384 ? 16384 : (per < 512 ? 512 : per);
+}
+template <typename F>
+__device__ __forceinline__ void forTiles(uint64_t V, int G, int cta, F&& body) {
+  const uint64_t tile = tileUnits(V, G);
+  for (uint64_t lo = (uint64_t)cta * tile; lo < V; lo += (uint64_t)G * tile) body(lo, lo + tile < V ? lo + tile : V);
+}
+
 // Slice [lo, hi) of `total` units for part `i` of `parts`.
 __device__ __forceinline__ uint64_t sliceLo(uint64_t total, int parts, int i) {
   return (uint64_t)(((unsigned __int128)total * (unsigned)i) / (unsigned)parts);

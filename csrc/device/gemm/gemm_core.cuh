@@ -57,6 +57,8 @@ struct GemmArgs {
   uint64_t* tileReadyPeer[MCCL_MAX_RANKS];   // RS: every rank's flags [n][stripes per block]
   uint64_t* stripeCount;       // RS: local counters [M/128]: tiles of the stripe stored so far
   __nv_bfloat16* out;          // RS: [M/n, N]
+  float* accum;                // RS: [M/n, N] fp32 running sum of the partials that have arrived
+  int panel;                   // stripes per rasterisation panel (divides the stripes of a row block)
 };
 
 template <int BN> struct Smem {
@@ -108,14 +110,21 @@ __device__ __forceinline__ bool commBarrier(const DevPeers& P, uint64_t& epoch, 
   return !namedBarrierOr(2, kCommThreads, *sFail != 0);
 }
 
-// Row stripe (128 rows) that the i-th group of tiles covers.  AG walks the own shard first, then the
-// shards in the order they arrive; RS walks the other ranks' row blocks first and the own block last.
+// Tile t -> (row stripe, column tile).  Tiles are walked panel by panel: a panel is `panel` consecutive
+// stripes, and inside it the stripe index runs fastest, so the CTAs that run together share a few B tiles and
+// `panel` A stripes (both stay in L2) instead of one A stripe and every B tile.  The order of the row blocks:
+// AG starts with the own shard and continues in the order the shards arrive; RS starts with the block of
+// rank+1 and ends with the own block, so partial results for the peers leave early.
 template <int MODE>
-__device__ __forceinline__ int stripeOf(int ord, int stripesPerBlock, int rank, int n) {
-  if (MODE == MODE_PLAIN) return ord;
-  const int blockOrd = ord / stripesPerBlock, within = ord - blockOrd * stripesPerBlock;
+__device__ __forceinline__ void tileCoords(int t, int tilesN, int panel, int stripesPerBlock, int rank, int n, int* stripe, int* nt) {
+  const int perPanel = panel * tilesN;
+  const int p = t / perPanel, within = t - p * perPanel;
+  const int ord = p * panel + within % panel;
+  *nt = within / panel;
+  if (MODE == MODE_PLAIN) { *stripe = ord; return; }
+  const int blockOrd = ord / stripesPerBlock, inBlock = ord - blockOrd * stripesPerBlock;
   const int block = (MODE == MODE_AG) ? (rank + blockOrd) % n : (rank + 1 + blockOrd) % n;
-  return block * stripesPerBlock + within;
+  *stripe = block * stripesPerBlock + inBlock;
 }
 
 template <int BN, int MODE>
@@ -158,7 +167,8 @@ __global__ void __launch_bounds__(kThreadsGemm, 1) tpGemmKernel(const __grid_con
     // ---------------- TMA producer
     int stage = 0; uint32_t phase = 0;
     for (int t = blockIdx.x; t < totalTiles && *sFail == 0; t += gridDim.x) {
-      const int stripe = stripeOf<MODE>(t / tilesN, stripesPerBlock, rank, n), nt = t % tilesN;
+      int stripe, nt;
+      tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
       if (MODE == MODE_AG) {
         const int shard = stripe / stripesPerBlock;
         if (!waitGpuFlag(&a.shardReady[shard], (uint64_t)gridDim.x, budget)) { *sFail = 1; atomicExch(a.errFlag, 10); break; }
@@ -199,7 +209,8 @@ __global__ void __launch_bounds__(kThreadsGemm, 1) tpGemmKernel(const __grid_con
     const int q = warp - 4;                      // == warp % 4: the TMEM lane quarter this warp may read
     int acc = 0; uint32_t accPhase = 0;
     for (int t = blockIdx.x; t < totalTiles; t += gridDim.x) {
-      const int stripe = stripeOf<MODE>(t / tilesN, stripesPerBlock, rank, n), nt = t % tilesN;
+      int stripe, nt;
+      tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
       bool good = *sFail == 0 && umma::mbarWait(&tmemFull[acc], accPhase, budget);
       if (!good && *sFail == 0) { *sFail = 1; atomicExch(a.errFlag, 14); }
       // In RS mode the four warps meet at a named barrier below, so they must agree on leaving.
@@ -265,19 +276,38 @@ __global__ void __launch_bounds__(kThreadsGemm, 1) tpGemmKernel(const __grid_con
       }
     }
     if (MODE == MODE_RS && ok) {
+      // Partials for this rank's row block arrive in a fixed order: rank-1 computes the block first, then
+      // rank-2, ..., and the own GEMM last.  Each arrival is folded into an fp32 running sum as soon as its
+      // stripe flag is up, so the NVLink reads spread over the whole GEMM and only the last fold (own
+      // partial, local) remains at the end.  The fold order is the same on every run.
       const uint64_t stripeBytes = (uint64_t)BM * a.N * 2, V = stripeBytes / 16;
-      const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
       const uint64_t* ready = a.tileReadyPeer[rank];
-      for (int lt = 0; lt < stripesPerBlock; ++lt) {
-        if (ct < n && !waitFlag(&ready[(size_t)ct * stripesPerBlock + lt], a.callIndex, P, 2u, ct, lt)) *sFail = 1;
-        if (namedBarrierOr(2, kCommThreads, *sFail != 0)) break;
-        const uint64_t base = ((uint64_t)rank * stripesPerBlock + lt) * stripeBytes;
-        char* dst = reinterpret_cast<char*>(a.out) + (uint64_t)lt * stripeBytes;
-        for (uint64_t i = lo + ct; i < hi; i += kCommThreads) {
-          float acc[8];
-          accInit<__nv_bfloat16>(acc, ldSys128(a.partialPeer[0] + base + i * 16));
-          for (int p = 1; p < n; ++p) accFold<__nv_bfloat16>(acc, ldSys128(a.partialPeer[p] + base + i * 16), mcclSum);
-          stLocal128(dst + i * 16, accFinish<__nv_bfloat16>(acc, 1));
+      bool failed = false;
+      for (int ord = 0; ord < n && !failed; ++ord) {
+        const int src = (ord == n - 1) ? rank : (rank - 1 - ord + 2 * n) % n;
+        for (int lt = 0; lt < stripesPerBlock; ++lt) {
+          if (ct == 0 && !waitFlag(&ready[(size_t)src * stripesPerBlock + lt], a.callIndex, P, 2u, src, lt)) *sFail = 1;
+          if (namedBarrierOr(2, kCommThreads, *sFail != 0)) { failed = true; break; }
+          const char* part = a.partialPeer[src] + ((uint64_t)rank * stripesPerBlock + lt) * stripeBytes;
+          float4* acc4 = reinterpret_cast<float4*>(a.accum) + (uint64_t)lt * V * 2;
+          char* dst = reinterpret_cast<char*>(a.out) + (uint64_t)lt * stripeBytes;
+          forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
+            for (uint64_t i = lo + ct; i < hi; i += kCommThreads) {
+              float acc[8];
+              accInit<__nv_bfloat16>(acc, ldSys128(part + i * 16));
+              if (ord > 0) {
+                const float4 x = acc4[2 * i], y = acc4[2 * i + 1];
+                acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+                acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+              }
+              if (ord == n - 1) {
+                stLocal128(dst + i * 16, accFinish<__nv_bfloat16>(acc, 1));
+              } else {
+                acc4[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                acc4[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+              }
+            }
+          });
         }
       }
     }

@@ -110,6 +110,12 @@ mcclResult_t checkShapes(int M, int N, int K, int nRanks) {
   return mcclSuccess;
 }
 
+// Largest panel height (in stripes) not above 8 that divides the stripes of one row block.
+int pickPanel(int stripesPerBlock) {
+  for (int p = 8; p > 1; --p) if (stripesPerBlock % p == 0) return p;
+  return 1;
+}
+
 int smCount() {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -151,6 +157,7 @@ mcclResult_t mcclTpGemm(const void* A, const void* B, void* C, int M, int N, int
   int* hostFlag = errFlagFor(dev);
   if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
   a.budgetNs = 2000000000ull;
+  a.panel = pickPanel(M / BM);
   const int tiles = (M / BM) * (N / bn);
   return launchMode<MODE_PLAIN>(a, bn, tiles < sms ? tiles : sms, reinterpret_cast<cudaStream_t>(stream));
 }
@@ -187,6 +194,7 @@ mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFul
   a.peers = comm->cu->peers;
   a.budgetNs = 2 * a.peers.timeoutNs;
   a.callIndex = 1;
+  a.panel = pickPanel(M / BM / n);
   a.shardReady = static_cast<uint64_t*>(flags);
   const size_t off = (size_t)(static_cast<const char*>(xShard) - seg->local);
   for (int p = 0; p < n; ++p) a.xPeer[p] = seg->peer[p] + off;
@@ -204,11 +212,11 @@ mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFul
 // Fused GEMM -> reduce-scatter over the row (token) dimension.  H: [M, K] local activations; W: [N, K] local
 // weight shard; partial: [M, N] staging in symmetric memory; flags: symmetric memory of at least
 // (16 + M/128 + n * M/(128 n)) uint64, zeroed once at allocation; out: [M/n, N] reduced rows of this rank's
-// block.  callIndex counts the calls made with this flags buffer (1, 2, ...).  Collective over `comm`.
+// block; accum: [M/n, N] fp32 local workspace.  callIndex counts the calls made with this flags buffer (1, 2, ...).  Collective over `comm`.
 mcclResult_t mcclTpGemmReduceScatter(mcclComm_t comm, const void* H, const void* W, void* partial, void* flags, void* out,
-                                     int M, int N, int K, uint64_t callIndex, mcclStream_t stream) {
+                                     float* accum, int M, int N, int K, uint64_t callIndex, mcclStream_t stream) {
   if (comm == nullptr || !comm->cuda || comm->cu == nullptr || H == nullptr || W == nullptr || partial == nullptr ||
-      flags == nullptr || out == nullptr || callIndex == 0) return mcclInvalidArgument;
+      flags == nullptr || out == nullptr || accum == nullptr || callIndex == 0) return mcclInvalidArgument;
   const int n = comm->nRanks;
   MCCLCHECK(checkShapes(M, N, K, n));
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -244,6 +252,8 @@ mcclResult_t mcclTpGemmReduceScatter(mcclComm_t comm, const void* H, const void*
     a.tileReadyPeer[p] = reinterpret_cast<uint64_t*>(fseg->peer[p] + foff) + 16 + stripes;
   }
   a.out = static_cast<__nv_bfloat16*>(out);
+  a.accum = accum;
+  a.panel = pickPanel(stripesPerBlock);
   CUDACHECK(cudaMemsetAsync(a.stripeCount, 0, (size_t)stripes * sizeof(uint64_t), s));   // local counters only
   const int tiles = (M / BM) * (N / bn);
   const int grid = tiles < sms ? tiles : sms;

@@ -110,9 +110,10 @@ __global__ void __launch_bounds__(kThreads, 1) pullKernel(const __grid_constant_
     bool vec = aligned16(a.dstA) && (a.dstA2 == nullptr || aligned16(a.dstA2));
     for (int p = 0; p < a.nSrcA; ++p) vec = vec && aligned16(a.srcA[p]);
     const uint64_t V = a.aBytes / 16;
-    const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
-    if (vec) foldVecs<T, NR>(a, lo, hi, tid, kThreads);
-    else foldElems<T>(a, lo * 16, hi * 16, tid, kThreads);
+    forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
+      if (vec) foldVecs<T, NR>(a, lo, hi, tid, kThreads);
+      else foldElems<T>(a, lo * 16, hi * 16, tid, kThreads);
+    });
     if (cta == G - 1 && V * 16 < a.aBytes) foldElems<T>(a, V * 16, a.aBytes, tid, kThreads);
   }
   if (multi && ok && a.midBarrier) ok = ctaBarrier(P, epoch, &sFail);   // every shard is folded
@@ -122,9 +123,11 @@ __global__ void __launch_bounds__(kThreads, 1) pullKernel(const __grid_constant_
       const CopyJob job = a.jobs[j];
       if (job.bytes == 0) continue;
       const uint64_t V = job.bytes / 16;
-      const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
-      if (aligned16(job.src) && aligned16(job.dst)) copyVecs(job.src, job.dst, lo, hi, tid, kThreads);
-      else copyBytes(job.src, job.dst, lo * 16, hi * 16, tid, kThreads);
+      const bool vec = aligned16(job.src) && aligned16(job.dst);
+      forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
+        if (vec) copyVecs(job.src, job.dst, lo, hi, tid, kThreads);
+        else copyBytes(job.src, job.dst, lo * 16, hi * 16, tid, kThreads);
+      });
       if (cta == G - 1 && V * 16 < job.bytes) copyBytes(job.src, job.dst, V * 16, job.bytes, tid, kThreads);
     }
   }
@@ -200,28 +203,29 @@ __global__ void __launch_bounds__(kThreads, 1) nvlsKernel(const __grid_constant_
   bool ok = ctaBarrier(P, epoch, &sFail);
   if (ok && a.active) {
     const uint64_t V = a.bytes / 16;
-    const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
-    for (uint64_t i = lo + tid; i < hi; i += (uint64_t)U * kThreads) {
-      uint4 v[U];
+    forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
+      for (uint64_t i = lo + tid; i < hi; i += (uint64_t)U * kThreads) {
+        uint4 v[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const uint64_t idx = i + (uint64_t)u * kThreads;
-        if (idx < hi) v[u] = a.loadReduce ? mmLdReduce<T>(a.mcSrc + idx * 16, a.op) : ldLocal128(a.src + idx * 16);
-      }
+        for (int u = 0; u < U; ++u) {
+          const uint64_t idx = i + (uint64_t)u * kThreads;
+          if (idx < hi) v[u] = a.loadReduce ? mmLdReduce<T>(a.mcSrc + idx * 16, a.op) : ldLocal128(a.src + idx * 16);
+        }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const uint64_t idx = i + (uint64_t)u * kThreads;
-        if (idx < hi) {
-          uint4 out = v[u];
-          if (a.divisor > 1) {
-            A acc[N];
-            accInit<T>(acc, out);
-            out = accFinish<T>(acc, a.divisor);
+        for (int u = 0; u < U; ++u) {
+          const uint64_t idx = i + (uint64_t)u * kThreads;
+          if (idx < hi) {
+            uint4 out = v[u];
+            if (a.divisor > 1) {
+              A acc[N];
+              accInit<T>(acc, out);
+              out = accFinish<T>(acc, a.divisor);
+            }
+            if (a.mcStore) mmStore128(a.mcDst + idx * 16, out); else stLocal128(a.dst + idx * 16, out);
           }
-          if (a.mcStore) mmStore128(a.mcDst + idx * 16, out); else stLocal128(a.dst + idx * 16, out);
         }
       }
-    }
+    });
   }
   if (ok) ok = ctaBarrier(P, epoch, &sFail);
   if (tid == 0) mine->epoch[cta] = epoch;

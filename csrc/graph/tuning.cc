@@ -157,9 +157,9 @@ bool algoSupports(int algo, int coll, int dt, int op, bool cudaTransport) {
       if (dt == mcclInt32 || dt == mcclUint32) return op == mcclSum || op == mcclMax || op == mcclMin || op == mcclAvg;
       return false;
     case mcclAlgoRing: case mcclAlgoTree:
-      return coll != mcclCollAllToAll;
+      return coll == mcclCollAllReduce;       // the other collectives have direct, two-shot and NVLS kernels only
     case mcclAlgoTwoShot:
-      return coll == mcclCollAllReduce;
+      return coll == mcclCollAllReduce || coll == mcclCollBroadcast || coll == mcclCollReduce;
     case mcclAlgoOneShot:
       return true;   // "direct": every rank reads/writes every peer once
     default: return false;
@@ -169,6 +169,13 @@ bool algoSupports(int algo, int coll, int dt, int op, bool cudaTransport) {
 mcclResult_t tunerPick(const TunerModel& m, int coll, int n, size_t bytes, int dt, int op, const int enabled[mcclNumAlgos],
                        bool cudaTransport, int* algo) {
   if (algo == nullptr) MCCLFAIL(mcclInvalidArgument);
+  // Measured on 2 and 8 B200: for all-gather, reduce-scatter, broadcast and reduce the NVLS form is at
+  // least as fast as the peer-load form at every size, so the model is only consulted for all-reduce.
+  if (cudaTransport && coll != mcclCollAllReduce && (enabled == nullptr || enabled[mcclAlgoNvls]) && m.viable[mcclAlgoNvls] &&
+      algoSupports(mcclAlgoNvls, coll, dt, op, true)) {
+    *algo = mcclAlgoNvls;
+    return mcclSuccess;
+  }
   int best = -1;
   float bestUs = INFINITY;
   // Ties go to the lower-numbered algorithm (ring), as in the reference.

@@ -25,7 +25,7 @@ def _lib():
         lib.mcclTpAllGatherGemm.restype = i
         lib.mcclTpAllGatherGemm.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, vp]
         lib.mcclTpGemmReduceScatter.restype = i
-        lib.mcclTpGemmReduceScatter.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, C.c_uint64, vp]
+        lib.mcclTpGemmReduceScatter.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, C.c_uint64, vp]
         lib.mcclTpGemmLastError.restype = i
         lib.mcclTpGemmLastError.argtypes = []
         lib._gemm_declared = True

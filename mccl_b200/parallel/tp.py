@@ -39,6 +39,7 @@ class TensorParallelFFN:
         self.x_full = torch.empty(tokens, hidden, device=dev, dtype=torch.bfloat16)
         self.h = torch.empty(tokens, ffn // n, device=dev, dtype=torch.bfloat16)
         self.out = torch.empty(tokens // n, hidden, device=dev, dtype=torch.bfloat16)
+        self.accum = torch.empty(tokens // n, hidden, device=dev, dtype=torch.float32)
         self.calls = 0
         torch.cuda.synchronize(dev)
         comm.host_barrier()
@@ -55,7 +56,7 @@ class TensorParallelFFN:
                 "mcclTpAllGatherGemm")
         self.calls += 1
         L.check(lib.mcclTpGemmReduceScatter(h, self.h.data_ptr(), self.w_down.data_ptr(), self.partial.data_ptr(),
-                                            self.flags.data_ptr(), self.out.data_ptr(), self.tokens, self.hidden,
+                                            self.flags.data_ptr(), self.out.data_ptr(), self.accum.data_ptr(), self.tokens, self.hidden,
                                             self.ffn // self.n, self.calls, s), "mcclTpGemmReduceScatter")
         G._counter["launches"] += 2
         return self.out
