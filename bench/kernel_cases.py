@@ -1,0 +1,101 @@
+#!/usr/bin/env python
+"""Small single-GPU cases of the library's own kernels, sized for profiling (inputs larger than the 126 MB
+L2, a few hundred MB on the device, a handful of launches) and for quick CUDA-event timing.
+
+    python bench/kernel_cases.py gemm   [--m 8192 --n 3584 --k 8192] [--launches 3]
+    python bench/kernel_cases.py adamw  [--elems 67108864]
+    python bench/kernel_cases.py sumsq  [--elems 268435456]
+    python bench/kernel_cases.py copy   [--mbytes 512]      (staging copy kernel through a 1-rank communicator)
+
+Prints one JSON line with the CUDA-event time per launch and the achieved fraction of the measured peaks
+(MEASURED_PEAKS.json next to the repository root if present, else 6451.8 GB/s and 1685 TFLOP/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return 6451.8, 1685.0, "recorded"
+
+
+def timed(fn, launches, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+    total = 0.0
+    for _ in range(launches):
+        flush.zero_()                       # evict the previous launch's data from L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / launches
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "adamw", "sumsq", "copy"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=3584)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--elems", type=int, default=0)
+    ap.add_argument("--mbytes", type=int, default=512)
+    ap.add_argument("--launches", type=int, default=3)
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    hbm, tflops, src = peaks()
+    out = {"case": args.case, "peaks": src}
+    if args.case == "gemm":
+        from mccl_b200.ops import gemm as G
+        x = torch.randn(args.m, args.k, device=dev).to(torch.bfloat16)
+        w = (torch.randn(args.n, args.k, device=dev) * 0.02).to(torch.bfloat16)
+        y = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
+        ms = timed(lambda: G.gemm(x, w, out=y, epilogue="silu"), args.launches)
+        fl = 2.0 * args.m * args.n * args.k
+        out.update({"shape": [args.m, args.n, args.k], "us": round(ms * 1e3, 1), "tflops": round(fl / ms / 1e9, 1),
+                    "frac_of_cublas_peak": round(fl / ms / 1e9 / tflops, 3), "kernel_error": G.last_error()})
+    elif args.case == "adamw":
+        from mccl_b200.ops.optim import fused_adamw_
+        n = args.elems or (64 << 20)
+        p = torch.zeros(n, device=dev, dtype=torch.bfloat16); g = torch.randn(n, device=dev).to(torch.bfloat16)
+        m32 = torch.randn(n, device=dev); ea = torch.zeros(n, device=dev); es = torch.zeros(n, device=dev)
+        ms = timed(lambda: fused_adamw_(p, m32, ea, es, g, lr=1e-3, step=1, zero_grad=False), args.launches)
+        byts = n * (2 + 2 + 3 * 4 * 2)      # read grad, write param, read+write three fp32 arrays
+        out.update({"elems": n, "us": round(ms * 1e3, 1), "gbs": round(byts / ms / 1e6, 1), "frac_of_copy_peak": round(byts / ms / 1e6 / hbm, 3)})
+    elif args.case == "sumsq":
+        from mccl_b200.ops.optim import scratch_floats, sum_squares_
+        n = args.elems or (256 << 20)
+        x = torch.randn(n, device=dev).to(torch.bfloat16)
+        o = torch.zeros(1, device=dev); sc = torch.zeros(scratch_floats(n), device=dev)
+        ms = timed(lambda: sum_squares_(x, o, sc), args.launches)
+        out.update({"elems": n, "us": round(ms * 1e3, 1), "gbs": round(2 * n / ms / 1e6, 1), "frac_of_copy_peak": round(2 * n / ms / 1e6 / hbm, 3)})
+    else:
+        import mccl_b200 as mccl
+        comm = mccl.Communicator(1, mccl.get_unique_id(), 0, transport="cuda")
+        n = args.mbytes << 20
+        a = torch.empty(n, device=dev, dtype=torch.uint8).random_(); b = torch.empty_like(a)
+        ms = timed(lambda: comm.all_reduce(a, b, dtype=mccl.UINT8), args.launches)
+        out.update({"bytes": n, "us": round(ms * 1e3, 1), "gbs": round(2 * n / ms / 1e6, 1), "frac_of_copy_peak": round(2 * n / ms / 1e6 / hbm, 3)})
+        comm.finalize(); comm.destroy()
+    print(json.dumps(out), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -66,7 +66,7 @@ mcclResult_t launchCopy(mcclComm* c, const void* src, void* dst, uint64_t rows, 
                         uint64_t dstPitch, cudaStream_t s) {
   if (rows == 0 || rowBytes == 0 || (src == dst && srcPitch == dstPitch)) return mcclSuccess;
   const uint64_t total = rows * rowBytes;
-  int blocks = (int)std::min<uint64_t>((total / 16 + kThreads - 1) / kThreads + 1, 296);
+  int blocks = (int)std::min<uint64_t>((total / 16 + kThreads - 1) / kThreads + 1, 592);
   copyKernel<<<blocks, kThreads, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), rows, rowBytes, srcPitch, dstPitch);
   return launched(c, "copyKernel");
 }

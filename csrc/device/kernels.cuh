@@ -439,7 +439,22 @@ __global__ void __launch_bounds__(kThreads) copyKernel(const char* src, char* ds
   const bool vec = aligned16(src) && aligned16(dst) && (rowBytes & 15) == 0 && (srcPitch & 15) == 0 && (dstPitch & 15) == 0;
   if (vec) {
     const uint64_t perRow = rowBytes / 16, total = perRow * rows;
-    for (uint64_t i = tid; i < total; i += nth) {
+    constexpr int U = 4;                     // four loads in flight per thread
+    uint64_t i = tid;
+    for (; i + (uint64_t)(U - 1) * nth < total; i += (uint64_t)U * nth) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t k = i + (uint64_t)u * nth, row = k / perRow, col = k - row * perRow;
+        v[u] = ldLocal128(src + row * srcPitch + col * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t k = i + (uint64_t)u * nth, row = k / perRow, col = k - row * perRow;
+        stLocal128(dst + row * dstPitch + col * 16, v[u]);
+      }
+    }
+    for (; i < total; i += nth) {
       const uint64_t row = i / perRow, col = i - row * perRow;
       stLocal128(dst + row * dstPitch + col * 16, ldLocal128(src + row * srcPitch + col * 16));
     }
