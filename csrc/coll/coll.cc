@@ -6,6 +6,7 @@
 #include <cstring>
 
 #include "../comm/comm.h"
+#include "../core/trace.h"
 
 using namespace mccl;
 
@@ -18,9 +19,18 @@ mcclResult_t checkCommon(mcclComm_t comm, mcclDataType_t dt) {
   return mcclSuccess;
 }
 
-mcclResult_t issue(mcclComm_t comm, std::function<mcclResult_t()> fn) {
-  if (groupActive()) return groupRecordColl(comm, [=]() { return commLaunch(comm, fn); });
-  return commLaunch(comm, std::move(fn));
+// `what`, `bytes`, `stream` feed the optional trace (MCCL_TRACE); the span covers the launch on the
+// caller's stream (cuda) or the whole blocking call (tcp).
+mcclResult_t issue(mcclComm_t comm, const char* what, size_t bytes, mcclStream_t stream, std::function<mcclResult_t()> fn) {
+  auto traced = [=]() -> mcclResult_t {
+    if (!traceEnabled()) return fn();
+    TraceSpan span = traceBegin(comm, what, bytes, comm->lastAlgo.load(), stream);
+    const mcclResult_t rc = fn();
+    traceEnd(comm, span, stream);
+    return rc;
+  };
+  if (groupActive()) return groupRecordColl(comm, [=]() { return commLaunch(comm, traced); });
+  return commLaunch(comm, traced);
 }
 
 }  // namespace
@@ -34,7 +44,7 @@ mcclResult_t mcclAllReduce(mcclComm_t comm, const void* sendbuff, void* recvbuff
   if (count == 0) return mcclSuccess;
   if (sendbuff == nullptr || recvbuff == nullptr) MCCLFAIL(mcclInvalidArgument);
   const int algo = commPickAlgo(comm, mcclCollAllReduce, count * mcclDataSize(dt), dt, op);
-  return issue(comm, [=]() -> mcclResult_t {
+  return issue(comm, "AllReduce", count * mcclDataSize(dt), stream, [=]() -> mcclResult_t {
     comm->lastAlgo.store(algo);
     if (comm->cuda) return cudaCollective(comm, mcclCollAllReduce, sendbuff, recvbuff, count, dt, op, 0, algo, stream);
     return cpuAllReduce(comm, sendbuff, recvbuff, count, dt, op, algo);
@@ -47,7 +57,7 @@ mcclResult_t mcclAllGather(mcclComm_t comm, const void* sendbuff, void* recvbuff
   if (sendcount == 0) return mcclSuccess;
   if (sendbuff == nullptr || recvbuff == nullptr) MCCLFAIL(mcclInvalidArgument);
   const int algo = commPickAlgo(comm, mcclCollAllGather, sendcount * mcclDataSize(dt) * comm->nRanks, dt, mcclSum);
-  return issue(comm, [=]() -> mcclResult_t {
+  return issue(comm, "AllGather", sendcount * mcclDataSize(dt) * comm->nRanks, stream, [=]() -> mcclResult_t {
     comm->lastAlgo.store(algo);
     if (comm->cuda) return cudaCollective(comm, mcclCollAllGather, sendbuff, recvbuff, sendcount, dt, mcclSum, 0, algo, stream);
     return cpuAllGather(comm, sendbuff, recvbuff, sendcount, dt, algo);
@@ -61,7 +71,7 @@ mcclResult_t mcclReduceScatter(mcclComm_t comm, const void* sendbuff, void* recv
   if (recvcount == 0) return mcclSuccess;
   if (sendbuff == nullptr || recvbuff == nullptr) MCCLFAIL(mcclInvalidArgument);
   const int algo = commPickAlgo(comm, mcclCollReduceScatter, recvcount * mcclDataSize(dt) * comm->nRanks, dt, op);
-  return issue(comm, [=]() -> mcclResult_t {
+  return issue(comm, "ReduceScatter", recvcount * mcclDataSize(dt) * comm->nRanks, stream, [=]() -> mcclResult_t {
     comm->lastAlgo.store(algo);
     if (comm->cuda) return cudaCollective(comm, mcclCollReduceScatter, sendbuff, recvbuff, recvcount, dt, op, 0, algo, stream);
     return cpuReduceScatter(comm, sendbuff, recvbuff, recvcount, dt, op, algo);
@@ -76,7 +86,7 @@ mcclResult_t mcclBroadcast(mcclComm_t comm, const void* sendbuff, void* recvbuff
   // Only the root reads sendbuff; everyone writes recvbuff.
   if (recvbuff == nullptr || (comm->rank == root && sendbuff == nullptr)) MCCLFAIL(mcclInvalidArgument);
   const int algo = commPickAlgo(comm, mcclCollBroadcast, count * mcclDataSize(dt), dt, mcclSum);
-  return issue(comm, [=]() -> mcclResult_t {
+  return issue(comm, "Broadcast", count * mcclDataSize(dt), stream, [=]() -> mcclResult_t {
     comm->lastAlgo.store(algo);
     if (comm->cuda) return cudaCollective(comm, mcclCollBroadcast, sendbuff, recvbuff, count, dt, mcclSum, root, algo, stream);
     return cpuBroadcast(comm, sendbuff, recvbuff, count, dt, root, algo);
@@ -92,7 +102,7 @@ mcclResult_t mcclReduce(mcclComm_t comm, const void* sendbuff, void* recvbuff, s
   // Everyone reads sendbuff; only the root writes recvbuff.
   if (sendbuff == nullptr || (comm->rank == root && recvbuff == nullptr)) MCCLFAIL(mcclInvalidArgument);
   const int algo = commPickAlgo(comm, mcclCollReduce, count * mcclDataSize(dt), dt, op);
-  return issue(comm, [=]() -> mcclResult_t {
+  return issue(comm, "Reduce", count * mcclDataSize(dt), stream, [=]() -> mcclResult_t {
     comm->lastAlgo.store(algo);
     if (comm->cuda) return cudaCollective(comm, mcclCollReduce, sendbuff, recvbuff, count, dt, op, root, algo, stream);
     return cpuReduce(comm, sendbuff, recvbuff, count, dt, op, root, algo);
@@ -108,7 +118,7 @@ mcclResult_t mcclAllToAll(mcclComm_t comm, const void* sendbuff, void* recvbuff,
   if (sendbuff == recvbuff && comm->nRanks > 1) MCCLFAIL(mcclInvalidUsage);   // blocks would overwrite each other
   const size_t blk = count * mcclDataSize(dt);
   if (comm->cuda) {
-    return issue(comm, [=]() -> mcclResult_t {
+    return issue(comm, "AllToAll", blk * comm->nRanks, stream, [=]() -> mcclResult_t {
       comm->lastAlgo.store(mcclAlgoOneShot);
       return cudaCollective(comm, mcclCollAllToAll, sendbuff, recvbuff, count, dt, mcclSum, 0, mcclAlgoOneShot, stream);
     });

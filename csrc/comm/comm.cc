@@ -13,6 +13,7 @@
 
 #include "../os/pool.h"
 #include "../os/socket.h"
+#include "../core/trace.h"
 
 using namespace mccl;
 
@@ -121,6 +122,7 @@ static mcclResult_t buildPlan(mcclComm* c) {
 static void freeComm(mcclComm* c) {
   if (c == nullptr) return;
   if (c->work) workerStop(c);
+  traceFlush(c);
   if (c->cu) cudaCommDestroy(c);
   if (c->ep) tcpEndpointClose(c->ep);
   if (c->bs) bootstrapClose(c->bs);
@@ -377,6 +379,12 @@ mcclResult_t mcclCommSetCtas(mcclComm_t comm, int ctas) {
   if (comm == nullptr || ctas < 0) MCCLFAIL(mcclInvalidArgument);
   comm->forcedCtas = ctas;
   return mcclSuccess;
+}
+mcclResult_t mcclCommCheckGuards(mcclComm_t comm, int* intact) {
+  if (comm == nullptr || intact == nullptr) MCCLFAIL(mcclInvalidArgument);
+  *intact = 1;
+  if (!comm->cuda || comm->cu == nullptr) return mcclSuccess;
+  return cudaCheckGuards(comm, intact);
 }
 mcclResult_t mcclCommTopoXml(mcclComm_t comm, char** xml) {
   if (comm == nullptr || xml == nullptr) MCCLFAIL(mcclInvalidArgument);

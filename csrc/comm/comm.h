@@ -101,6 +101,7 @@ mcclResult_t cudaDeregister(mcclComm* c, void* handle);
 mcclResult_t cudaPeerPointer(mcclComm* c, const void* local, int peer, void** out);
 mcclResult_t cudaMcPointer(mcclComm* c, const void* local, void** out);
 bool         cudaNvlsEnabled(mcclComm* c);
+mcclResult_t cudaCheckGuards(mcclComm* c, int* intact);
 mcclResult_t cudaCalibrate(mcclComm* c);                           // measure links, refine the tuner
 mcclResult_t cudaFillRankInfo(int device, RankInfo* ri);           // device facts + peer masks
 

@@ -208,6 +208,16 @@ mcclResult_t cudaMcPointer(mcclComm* c, const void* local, void** out) {
   return mcclSuccess;
 }
 
+mcclResult_t cudaCheckGuards(mcclComm* c, int* intact) {
+  CudaState* st = c->cu;
+  uint64_t v = 0;
+  CUDACHECK(cudaSetDevice(c->device));
+  CUDACHECK(cudaDeviceSynchronize());
+  CUDACHECK(cudaMemcpy(&v, st->ctrl->local + st->layout.flagsOff + offsetof(CtrlFlags, canary), sizeof(v), cudaMemcpyDeviceToHost));
+  *intact = v == kCanary ? 1 : 0;
+  return mcclSuccess;
+}
+
 bool cudaNvlsEnabled(mcclComm* c) { return c->cu && c->cu->nvls && c->cu->ctrl && c->cu->ctrl->mc != nullptr; }
 
 }  // namespace mccl

@@ -198,6 +198,9 @@ mcclResult_t mcclCommLaunchCount(mcclComm_t comm, uint64_t* launches);
 mcclResult_t mcclCommSetMaxCtas(mcclComm_t comm, int maxCtas);
 /* Use exactly `ctas` CTAs for every collective kernel (0 = planner's choice); a tuning aid. */
 mcclResult_t mcclCommSetCtas(mcclComm_t comm, int ctas);
+/* Debug aid: verifies the guard word behind the device-side flag arrays of the cuda transport (a kernel that
+ * indexed past them would have overwritten it).  *intact = 1 when fine or when there is nothing to check. */
+mcclResult_t mcclCommCheckGuards(mcclComm_t comm, int* intact);
 /* Topology of the communicator as XML (caller frees with mcclFreeString). */
 mcclResult_t mcclCommTopoXml(mcclComm_t comm, char** xml);
 void         mcclFreeString(char* s);

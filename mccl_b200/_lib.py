@@ -75,7 +75,7 @@ def _declare(lib: C.CDLL) -> None:
     for s in ("mcclCommFinalize", "mcclCommDestroy", "mcclCommAbort", "mcclCommSynchronize", "mcclCommHostBarrier"):
         fn(s, i, vp)
     for s in ("mcclCommCount", "mcclCommUserRank", "mcclCommDevice", "mcclCommGetAsyncError", "mcclCommNvlsEnabled",
-              "mcclCommLastAlgo"):
+              "mcclCommLastAlgo", "mcclCommCheckGuards"):
         fn(s, i, vp, P(i))
     fn("mcclCommHostAllGather", i, vp, vp, vp, sz)
     fn("mcclCommTransport", C.c_char_p, vp)

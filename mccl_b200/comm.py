@@ -153,6 +153,9 @@ class Communicator:
         L.check(self._lib.mcclCommLaunchCount(self._h, C.byref(v)))
         return v.value
 
+    def guards_intact(self) -> bool:
+        return bool(self._q(self._lib.mcclCommCheckGuards))
+
     def async_error(self) -> int:
         return self._q(self._lib.mcclCommGetAsyncError)
 

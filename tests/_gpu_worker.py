@@ -57,7 +57,7 @@ def check(what, got, ref, dtype):
 
 
 def canary_ok(comm):
-    return comm.async_error() == L.SUCCESS
+    return comm.async_error() == L.SUCCESS and comm.guards_intact()
 
 
 def matrix():

@@ -257,3 +257,19 @@ def test_unknown_transport_is_refused():
 def test_unique_ids_differ():
     a, b = mccl.get_unique_id(), mccl.get_unique_id()
     assert a != b
+
+
+def test_trace_file_is_chrome_json(tmp_path):
+    import json
+    import subprocess
+    import sys
+    code = ("import numpy as np, mccl_b200 as m\n"
+            "c = m.Communicator(1, m.get_unique_id(), 0, transport='tcp')\n"
+            "x = np.ones(64, np.float32)\n"
+            "c.all_reduce(x); c.all_gather(x, x.copy()); c.finalize(); c.destroy()\n")
+    env = dict(os.environ, MCCL_TRACE=str(tmp_path / "trace"), PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    subprocess.run([sys.executable, "-c", code], env=env, check=True)
+    data = json.load(open(tmp_path / "trace.0.json"))
+    names = [e["name"] for e in data["traceEvents"]]
+    assert names == ["AllReduce", "AllGather"]
+    assert all(e["ph"] == "X" and e["dur"] >= 0 and e["args"]["bytes"] > 0 for e in data["traceEvents"])
