@@ -229,7 +229,10 @@ mcclResult_t launchNvlsU(const Call& k, const NvlsArgs& a, bool reducing) {
   return launched(k.c, "nvlsKernel");
 }
 
-mcclResult_t launchNvls(const Call& k, const NvlsArgs& a, bool reducing) {
+mcclResult_t launchNvls(const Call& k, const NvlsArgs& a, bool reducing, bool rootOnly = false) {
+  // One rank moving the whole message needs about 8 MB in flight to fill its port (the round trip through
+  // the switch is several microseconds): 128 CTAs x 512 threads x 8 vectors.
+  if (rootOnly) return launchNvlsU<8>(k, a, reducing);
   static const int unroll = (int)envInt("MCCL_NVLS_UNROLL", 4);
   if (unroll >= 8) return launchNvlsU<8>(k, a, reducing);
   if (unroll <= 2) return launchNvlsU<2>(k, a, reducing);
@@ -243,6 +246,8 @@ NvlsArgs baseNvls(const Call& k, size_t bytes, bool rootOnly = false) {
   memset(&a, 0, sizeof(a));
   a.peers = k.st->peers;
   a.nCtas = pickCtas(k.c, bytes, rootOnly ? mcclAlgoTwoShot : mcclAlgoNvls);
+  if (rootOnly && bytes > (32u << 20) && k.c->forcedCtas == 0 && mcclParamNChannels() == 0)
+    a.nCtas = k.c->maxCtas > 0 ? std::min(128, k.c->maxCtas) : 128;
   a.op = (k.op == mcclAvg) ? mcclSum : k.op;
   a.divisor = 1;
   a.active = 1;
@@ -479,7 +484,7 @@ mcclResult_t broadcast(const Call& k, const void* send, void* recv, size_t count
     a.src = static_cast<const char*>(send);
     a.mcDst = rv.mc();
     a.bytes = bytes;
-    return launchNvls(k, a, false);
+    return launchNvls(k, a, false, true);
   }
   k.c->lastAlgo.store(direct ? mcclAlgoOneShot : mcclAlgoTwoShot);
   char* work[MCCL_MAX_RANKS];
@@ -532,7 +537,7 @@ mcclResult_t reduce(const Call& k, const void* send, void* recv, size_t count, i
     a.dst = static_cast<char*>(recv);
     a.bytes = bytes;
     a.divisor = k.divisor;
-    return launchNvls(k, a, true);
+    return launchNvls(k, a, true, true);
   }
   k.c->lastAlgo.store(direct ? mcclAlgoOneShot : mcclAlgoTwoShot);
   // The stage is cut in two: inputs that are not symmetric go to the first half, folded shards to the second.

@@ -291,20 +291,34 @@ __global__ void __launch_bounds__(kThreadsGemm, 1) tpGemmKernel(const __grid_con
           const char* part = a.partialPeer[src] + ((uint64_t)rank * stripesPerBlock + lt) * stripeBytes;
           float4* acc4 = reinterpret_cast<float4*>(a.accum) + (uint64_t)lt * V * 2;
           char* dst = reinterpret_cast<char*>(a.out) + (uint64_t)lt * stripeBytes;
+          // Eight remote vectors in flight per thread: with one, the 148 x 128 communication threads keep
+          // only 0.3 MB on the wire and the pull runs at a tenth of the link rate.
+          constexpr int U = 8;
           forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
-            for (uint64_t i = lo + ct; i < hi; i += kCommThreads) {
-              float acc[8];
-              accInit<__nv_bfloat16>(acc, ldSys128(part + i * 16));
-              if (ord > 0) {
-                const float4 x = acc4[2 * i], y = acc4[2 * i + 1];
-                acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-                acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+            for (uint64_t i = lo + ct; i < hi; i += (uint64_t)U * kCommThreads) {
+              uint4 pv[U];
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                const uint64_t idx = i + (uint64_t)u * kCommThreads;
+                if (idx < hi) pv[u] = ldSys128(part + idx * 16);
               }
-              if (ord == n - 1) {
-                stLocal128(dst + i * 16, accFinish<__nv_bfloat16>(acc, 1));
-              } else {
-                acc4[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                acc4[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                const uint64_t idx = i + (uint64_t)u * kCommThreads;
+                if (idx >= hi) continue;
+                float acc[8];
+                accInit<__nv_bfloat16>(acc, pv[u]);
+                if (ord > 0) {
+                  const float4 x = acc4[2 * idx], y = acc4[2 * idx + 1];
+                  acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+                  acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+                }
+                if (ord == n - 1) {
+                  stLocal128(dst + idx * 16, accFinish<__nv_bfloat16>(acc, 1));
+                } else {
+                  acc4[2 * idx] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                  acc4[2 * idx + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+                }
               }
             }
           });

@@ -217,6 +217,53 @@ def device_timeout():
     comm.abort(); comm.destroy()
 
 
+def large_root_collectives():
+    """Broadcast and reduce of a message large enough for the many-CTA root-only NVLS path, plus a 1 GB
+    all-reduce (round-robin work tiles), against the oracle."""
+    comm = make_comm()
+    n = 12 << 20                                   # 48 MB of fp32
+    for root in (0, WORLD - 1):
+        b = comm.empty(n, torch.float32); b.zero_()
+        if RANK == root:
+            b.copy_(gen(root, n, torch.float32))
+        comm.broadcast(b if RANK == root else None, b, root=root); torch.cuda.synchronize()
+        assert torch.equal(b, gen(root, n, torch.float32)), ("broadcast", root, comm.last_algo)
+        s = comm.empty(n, torch.float32); s.copy_(gen(RANK, n, torch.float32))
+        o = comm.empty(n, torch.float32)
+        comm.reduce(s, o, op="sum", root=root); torch.cuda.synchronize()
+        if RANK == root:
+            check(("reduce", root, comm.last_algo), o, oracle(n, torch.float32, "sum"), torch.float32)
+        for t in (b, s, o):
+            comm.free_raw(t.data_ptr())
+    n = 1 << 29                                    # 1 GB of bf16
+    x = comm.empty(n, torch.bfloat16)
+    x.copy_(gen(RANK, n, torch.bfloat16))
+    comm.all_reduce(x, op="avg"); torch.cuda.synchronize()
+    ref = oracle(n, torch.bfloat16, "avg")
+    check(("allreduce 1GB", comm.last_algo), x, ref, torch.bfloat16)
+    assert canary_ok(comm)
+    comm.finalize(); comm.destroy()
+
+
+def calibrate_and_trace():
+    """MCCL_CALIBRATE=1 measures pair bandwidth and empty-collective latency at init and feeds the tuner;
+    MCCL_TRACE writes a Chrome trace with a device track."""
+    import json as js
+    import xml.etree.ElementTree as ET
+    comm = make_comm()
+    root = ET.fromstring(comm.topo_xml())
+    links = [l for g in root.findall("gpu") for l in g.findall("link")]
+    assert links and all(float(l.get("measured", "0")) > 10.0 for l in links), [l.attrib for l in links][:2]
+    assert all(0.0 < float(l.get("latency_us", "0")) < 1000.0 for l in links)
+    x = torch.ones(1 << 20, device=DEV)
+    comm.all_reduce(x); comm.all_reduce(x, op="avg"); torch.cuda.synchronize()
+    assert torch.all(x == WORLD)
+    comm.finalize(); comm.destroy()
+    data = js.load(open(os.environ["MCCL_TRACE"] + f".{RANK}.json"))
+    dev_events = [e for e in data["traceEvents"] if e["cat"] == "device"]
+    assert len(dev_events) == 2 and all(e["dur"] > 0 for e in dev_events), data
+
+
 def tp_ffn():
     """Fused all-gather->GEMM->SiLU and GEMM->reduce-scatter against an fp32 PyTorch restatement."""
     from mccl_b200.parallel.tp import TensorParallelFFN

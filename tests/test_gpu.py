@@ -1,5 +1,7 @@
 """GPU tests (marker `gpu`).  Single-GPU tests run the native kernels that need no peer; multi-GPU tests
 start one process per GPU and compare every collective kernel with an fp64 / exact-integer PyTorch oracle."""
+import os
+
 import pytest
 import torch
 
@@ -169,3 +171,24 @@ def test_fused_tp_ffn_two_gpus():
 def test_fused_tp_ffn_eight_gpus():
     assert_all_ok(run_ranks(8, "tp_ffn", worker="_gpu_worker.py", timeout=600,
                             args={"tokens": 8192, "hidden": 2048, "ffn": 8192}))
+
+
+@need2
+def test_calibration_and_trace(tmp_path):
+    env = {"MCCL_CALIBRATE": "1", "MCCL_TRACE": str(tmp_path / "t")}
+    assert_all_ok(run_ranks(2, "calibrate_and_trace", worker="_gpu_worker.py", env=env, timeout=300))
+
+
+def test_probes_single_gpu():
+    _require_cuda()
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for args in (["gpu"], ["kernels"], ["coll", "--op", "allreduce", "--transport", "cuda"]):
+        r = subprocess.run([sys.executable, "-m", "mccl_b200.probe", *args], cwd=root, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, (args, r.stdout[-500:], r.stderr[-500:])
+
+
+@need2
+def test_large_messages():
+    assert_all_ok(run_ranks(min(NGPU, 8) if NGPU in (2, 4, 8) else 2, "large_root_collectives", worker="_gpu_worker.py", timeout=600))
