@@ -57,7 +57,7 @@ def close(got, ref, dtype):
 
 # ---- scenarios ---------------------------------------------------------------------------------------------
 def baseline_config():
-    """BASELINE config 1: 1 Mi fp32 per rank ~U[-1,1] seeded by rank; five collectives against numpy; split."""
+    """The CPU plumbing configuration: 1 Mi fp32 per rank ~U[-1,1] seeded by rank; five collectives against numpy; split."""
     comm = make_comm()
     n = 1 << 20
     xs = [data(r, n) for r in range(WORLD)]

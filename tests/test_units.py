@@ -273,3 +273,23 @@ def test_trace_file_is_chrome_json(tmp_path):
     names = [e["name"] for e in data["traceEvents"]]
     assert names == ["AllReduce", "AllGather"]
     assert all(e["ph"] == "X" and e["dur"] >= 0 and e["args"]["bytes"] > 0 for e in data["traceEvents"])
+
+
+def test_env_knobs_at_init(tmp_path, monkeypatch):
+    """MCCL_TOPO_DUMP_FILE, MCCL_ALGO and MCCL_TUNER_CACHE are read when a communicator is created."""
+    import subprocess
+    import sys
+    import xml.etree.ElementTree as ET
+    cache = tmp_path / "tuner.txt"
+    cache.write_text("ring 7.5 2.5 3.25\ntree 1 1 1\n")
+    code = ("import mccl_b200 as m\n"
+            "c = m.Communicator(1, m.get_unique_id(), 0, transport='tcp')\n"
+            "print('PICK', c.pick_algo('allreduce', 1 << 26))\n"
+            "c.destroy()\n")
+    env = dict(os.environ, MCCL_TOPO_DUMP_FILE=str(tmp_path / "topo.xml"), MCCL_ALGO="^ring", MCCL_TUNER_CACHE=str(cache),
+               PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    out = subprocess.run([sys.executable, "-c", code], env=env, check=True, capture_output=True, text=True).stdout
+    assert "PICK tree" in out                                  # ring is denied
+    root = ET.parse(tmp_path / "topo.xml").getroot()
+    ring = [a for a in root.findall("algo") if a.get("name") == "ring"][0]
+    assert float(ring.get("alpha_us")) == 7.5 and float(ring.get("step_us")) == 2.5 and float(ring.get("model_bw")) == 3.25
