@@ -74,11 +74,13 @@ def main() -> int:
     B, S = args.micro_batch, cfg.seq_len
 
     comm = None
-    model = GPT2(cfg).to(device=dev, dtype=torch.bfloat16)
+    # The NCCL arm is what a user runs without this library: stock PyTorch loss, DDP and optimizer.
+    model = GPT2(cfg, fused_loss=args.impl == "mccl").to(device=dev, dtype=torch.bfloat16)
     n_params = model.num_params()
     launches = lambda: 0
     if args.impl == "mccl":
         import mccl_b200 as mccl
+        from mccl_b200.ops import loss as loss_ops
         from mccl_b200.ops import optim
         from mccl_b200.parallel.ddp import DistributedDataParallel
         if world > 1:
@@ -86,7 +88,7 @@ def main() -> int:
             uid = mccl.unique_id_from_env(os.environ.get("MASTER_ADDR", "127.0.0.1"), port)
             comm = mccl.Communicator(world, uid, rank, transport="cuda")
         ddp = DistributedDataParallel(model, comm, bucket_mb=args.bucket_mb)
-        launches = lambda: (comm.launch_count if comm is not None else 0) + optim.launches()
+        launches = lambda: (comm.launch_count if comm is not None else 0) + optim.launches() + loss_ops.launches()
 
         def train_step(tokens):
             loss = ddp(tokens[:, :-1], tokens[:, 1:])

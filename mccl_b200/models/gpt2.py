@@ -61,9 +61,10 @@ class Block(nn.Module):
 
 
 class GPT2(nn.Module):
-    def __init__(self, cfg: GPT2Config):
+    def __init__(self, cfg: GPT2Config, fused_loss: bool = True):
         super().__init__()
         self.cfg = cfg
+        self.fused_loss = fused_loss      # the library's one-pass cross-entropy kernel (CUDA, bf16 logits)
         self.wte = nn.Embedding(cfg.padded_vocab, cfg.d_model)
         self.wpe = nn.Embedding(cfg.seq_len, cfg.d_model)
         self.blocks = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layer))
@@ -93,5 +94,8 @@ class GPT2(nn.Module):
         logits = F.linear(x, self.wte.weight)            # tied output projection, padded vocab
         if targets is None:
             return logits[..., : self.cfg.vocab_size]
-        loss = F.cross_entropy(logits.view(b * s, -1)[:, : self.cfg.vocab_size].float(), targets.reshape(-1))
-        return loss
+        flat = logits.view(b * s, -1)
+        if self.fused_loss and flat.is_cuda and flat.dtype == torch.bfloat16:
+            from ..ops.loss import fused_cross_entropy
+            return fused_cross_entropy(flat, targets.reshape(-1).contiguous(), self.cfg.vocab_size)
+        return F.cross_entropy(flat[:, : self.cfg.vocab_size].float(), targets.reshape(-1))
