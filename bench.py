@@ -81,6 +81,7 @@ def main() -> int:
     if args.impl == "mccl":
         import mccl_b200 as mccl
         from mccl_b200.ops import loss as loss_ops
+        from mccl_b200.ops import norm as norm_ops
         from mccl_b200.ops import optim
         from mccl_b200.parallel.ddp import DistributedDataParallel
         if world > 1:
@@ -88,7 +89,7 @@ def main() -> int:
             uid = mccl.unique_id_from_env(os.environ.get("MASTER_ADDR", "127.0.0.1"), port)
             comm = mccl.Communicator(world, uid, rank, transport="cuda")
         ddp = DistributedDataParallel(model, comm, bucket_mb=args.bucket_mb)
-        launches = lambda: (comm.launch_count if comm is not None else 0) + optim.launches() + loss_ops.launches()
+        launches = lambda: (comm.launch_count if comm is not None else 0) + optim.launches() + loss_ops.launches() + norm_ops.launches()
 
         def train_step(tokens):
             loss = ddp(tokens[:, :-1], tokens[:, 1:])

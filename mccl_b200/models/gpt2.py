@@ -16,6 +16,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.norm import FusedLayerNorm
+
 
 @dataclass
 class GPT2Config:
@@ -41,13 +43,14 @@ class GPT2Config:
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: GPT2Config):
+    def __init__(self, cfg: GPT2Config, fused: bool = True):
         super().__init__()
+        norm = FusedLayerNorm if fused else nn.LayerNorm
         self.n_head = cfg.n_head
-        self.ln1 = nn.LayerNorm(cfg.d_model)
+        self.ln1 = norm(cfg.d_model)
         self.qkv = nn.Linear(cfg.d_model, 3 * cfg.d_model)
         self.proj = nn.Linear(cfg.d_model, cfg.d_model)
-        self.ln2 = nn.LayerNorm(cfg.d_model)
+        self.ln2 = norm(cfg.d_model)
         self.fc = nn.Linear(cfg.d_model, cfg.d_ff)
         self.out = nn.Linear(cfg.d_ff, cfg.d_model)
 
@@ -64,11 +67,11 @@ class GPT2(nn.Module):
     def __init__(self, cfg: GPT2Config, fused_loss: bool = True):
         super().__init__()
         self.cfg = cfg
-        self.fused_loss = fused_loss      # the library's one-pass cross-entropy kernel (CUDA, bf16 logits)
+        self.fused_loss = fused_loss      # the library's cross-entropy and LayerNorm kernels (CUDA, bf16); False = stock PyTorch
         self.wte = nn.Embedding(cfg.padded_vocab, cfg.d_model)
         self.wpe = nn.Embedding(cfg.seq_len, cfg.d_model)
-        self.blocks = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layer))
-        self.ln_f = nn.LayerNorm(cfg.d_model)
+        self.blocks = nn.ModuleList(Block(cfg, fused_loss) for _ in range(cfg.n_layer))
+        self.ln_f = (FusedLayerNorm if fused_loss else nn.LayerNorm)(cfg.d_model)
         self.apply(self._init)
         for blk in self.blocks:  # GPT-2's scaled init of the residual projections
             nn.init.normal_(blk.proj.weight, std=0.02 / math.sqrt(2 * cfg.n_layer))

@@ -216,3 +216,31 @@ def test_fused_cross_entropy_matches_fp32_reference():
         assert torch.count_nonzero(g[:, vocab:]) == 0                       # padding columns get no gradient
         err = (g[:, :vocab] - ref_in.grad).abs().max().item()
         assert err < 1e-2 * ref_in.grad.abs().max().item() + 1e-6, (rows, vocab, err)
+
+
+def test_fused_layer_norm_matches_fp32_reference():
+    _require_cuda()
+    from mccl_b200.ops.norm import FusedLayerNorm
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    for rows, d in [(5, 256), (777, 1024), (8192, 1024), (64, 512)]:
+        ln = FusedLayerNorm(d).to(device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            ln.weight.copy_(torch.randn(d) * 0.5 + 1.0); ln.bias.copy_(torch.randn(d) * 0.1)
+        x = (torch.randn(rows, d, device=dev) * 2 + 0.3).to(torch.bfloat16).requires_grad_(True)
+        dy = torch.randn(rows, d, device=dev).to(torch.bfloat16)
+        y = ln(x)
+        y.backward(dy)
+        xr = x.detach().float().requires_grad_(True)
+        w, b = ln.weight.detach().float().requires_grad_(True), ln.bias.detach().float().requires_grad_(True)
+        yr = torch.nn.functional.layer_norm(xr, (d,), w, b, ln.eps)
+        yr.backward(dy.float())
+        torch.cuda.synchronize()
+        assert (y.float() - yr).abs().max() < 3e-2
+        assert (x.grad.float() - xr.grad).abs().max() < 3e-2 * max(1.0, xr.grad.abs().max().item())
+        tol = 2e-2 * max(1.0, w.grad.abs().max().item())
+        assert (ln.weight.grad.float() - w.grad).abs().max() < tol, (rows, d, (ln.weight.grad.float() - w.grad).abs().max().item())
+        assert (ln.bias.grad.float() - b.grad).abs().max() < 2e-2 * max(1.0, b.grad.abs().max().item())
+    # widths the kernel does not cover fall back to PyTorch
+    ln = FusedLayerNorm(128).to(device=dev, dtype=torch.bfloat16)
+    assert ln(torch.randn(4, 128, device=dev).to(torch.bfloat16)).shape == (4, 128)
