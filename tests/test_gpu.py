@@ -236,8 +236,9 @@ def test_fused_layer_norm_matches_fp32_reference():
         yr = torch.nn.functional.layer_norm(xr, (d,), w, b, ln.eps)
         yr.backward(dy.float())
         torch.cuda.synchronize()
-        assert (y.float() - yr).abs().max() < 3e-2
-        assert (x.grad.float() - xr.grad).abs().max() < 3e-2 * max(1.0, xr.grad.abs().max().item())
+        # outputs are rounded to bf16: compare relative to each value's magnitude
+        assert ((y.float() - yr).abs() / (yr.abs() + 1.0)).max() < 1e-2
+        assert ((x.grad.float() - xr.grad).abs() / (xr.grad.abs() + 1.0)).max() < 2e-2
         tol = 2e-2 * max(1.0, w.grad.abs().max().item())
         assert (ln.weight.grad.float() - w.grad).abs().max() < tol, (rows, d, (ln.weight.grad.float() - w.grad).abs().max().item())
         assert (ln.bias.grad.float() - b.grad).abs().max() < 2e-2 * max(1.0, b.grad.abs().max().item())
