@@ -6,6 +6,8 @@ L2, a few hundred MB on the device, a handful of launches) and for quick CUDA-ev
     python bench/kernel_cases.py adamw  [--elems 67108864]
     python bench/kernel_cases.py sumsq  [--elems 268435456]
     python bench/kernel_cases.py copy   [--mbytes 512]      (staging copy kernel through a 1-rank communicator)
+    python bench/kernel_cases.py emu    [--ranks 8 --mbytes 64 --algo twoshot|oneshot|ring|tree]
+                                        (multi-rank all-reduce kernels with the ranks emulated on this one GPU)
 
 Prints one JSON line with the CUDA-event time per launch and the achieved fraction of the measured peaks
 (MEASURED_PEAKS.json next to the repository root if present, else 6451.8 GB/s and 1685 TFLOP/s).
@@ -49,7 +51,9 @@ def timed(fn, launches, warm=2):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "adamw", "sumsq", "copy"])
+    ap.add_argument("case", choices=["gemm", "adamw", "sumsq", "copy", "emu"])
+    ap.add_argument("--ranks", type=int, default=8)
+    ap.add_argument("--algo", default="twoshot")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=3584)
     ap.add_argument("--k", type=int, default=8192)
@@ -85,6 +89,15 @@ def main() -> int:
         o = torch.zeros(1, device=dev); sc = torch.zeros(scratch_floats(n), device=dev)
         ms = timed(lambda: sum_squares_(x, o, sc), args.launches)
         out.update({"elems": n, "us": round(ms * 1e3, 1), "gbs": round(2 * n / ms / 1e6, 1), "frac_of_copy_peak": round(2 * n / ms / 1e6 / hbm, 3)})
+    elif args.case == "emu":
+        from mccl_b200 import emu
+        n = (args.mbytes << 20) // 2
+        xs = [torch.randn(n, device=dev).to(torch.bfloat16) for _ in range(args.ranks)]
+        ms = timed(lambda: emu.all_reduce(xs, op="sum", algo=args.algo, ctas=16), args.launches)
+        # local traffic of the emulation: every rank reads n-1 remote shards' worth twice and writes its buffer once
+        out.update({"ranks": args.ranks, "bytes_per_rank": n * 2, "algo": args.algo, "us": round(ms * 1e3, 1),
+                    "note": "all ranks share one GPU: times say nothing about NVLink"})
+        emu.destroy()
     else:
         import mccl_b200 as mccl
         comm = mccl.Communicator(1, mccl.get_unique_id(), 0, transport="cuda")

@@ -92,7 +92,7 @@ __device__ __forceinline__ void foldVecs(const PullArgs& a, uint64_t lo, uint64_
 __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename T, int NR>
-__global__ void __launch_bounds__(kThreads, 1) pullKernel(const __grid_constant__ PullArgs a) {
+__device__ __forceinline__ void pullBody(const PullArgs& a) {
   __shared__ int sFail;
   const DevPeers& P = a.peers;
   const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
@@ -135,9 +135,12 @@ __global__ void __launch_bounds__(kThreads, 1) pullKernel(const __grid_constant_
   if (tid == 0) mine->epoch[cta] = epoch;
 }
 
+template <typename T, int NR>
+__global__ void __launch_bounds__(kThreads, 1) pullKernel(const __grid_constant__ PullArgs a) { pullBody<T, NR>(a); }
+
 // ---- one-shot ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) oneShotKernel(const __grid_constant__ OneShotArgs a) {
+__device__ __forceinline__ void oneShotBody(const OneShotArgs& a) {
   __shared__ int sFail;
   using A = typename Acc<T>::type;
   constexpr int N = Pack<T>::N;
@@ -179,6 +182,9 @@ __global__ void __launch_bounds__(kThreads, 1) oneShotKernel(const __grid_consta
   }
   if (tid == 0) mine->oneShotCalls[cta] = call;
 }
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) oneShotKernel(const __grid_constant__ OneShotArgs a) { oneShotBody<T>(a); }
 
 // ---- NVLS ---------------------------------------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ uint4 mmLdReduce(const void* mc, int op);
@@ -233,7 +239,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvlsKernel(const __grid_constant_
 
 // ---- ring -----------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) ringKernel(const __grid_constant__ RingArgs a) {
+__device__ __forceinline__ void ringBody(const RingArgs& a) {
   __shared__ int sFail;
   using A = typename Acc<T>::type;
   constexpr int N = Pack<T>::N;
@@ -280,9 +286,12 @@ __global__ void __launch_bounds__(kThreads, 1) ringKernel(const __grid_constant_
   if (tid == 0) mine->epoch[cta] = epoch;
 }
 
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) ringKernel(const __grid_constant__ RingArgs a) { ringBody<T>(a); }
+
 // ---- double-binary tree ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) treeKernel(const __grid_constant__ TreeArgs a) {
+__device__ __forceinline__ void treeBody(const TreeArgs& a) {
   __shared__ int sFail;
   using A = typename Acc<T>::type;
   constexpr int N = Pack<T>::N;
@@ -344,6 +353,24 @@ __global__ void __launch_bounds__(kThreads, 1) treeKernel(const __grid_constant_
   if (ok) ok = ctaBarrier(P, epoch, &sFail);
   if (tid == 0) mine->epoch[cta] = epoch;
 }
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) treeKernel(const __grid_constant__ TreeArgs a) { treeBody<T>(a); }
+
+// Single-GPU emulation of a multi-rank launch: one cooperative grid of (CTAs per rank) x (ranks), block row y
+// runs rank y's arguments through the very same kernel body.  Every "peer" buffer lives on this GPU, so the
+// NVLink traffic becomes local traffic; flags, barriers, slicing and the fold are exercised unchanged.  Used
+// by the single-GPU tests and to put the collective kernels under a profiler, which cannot wrap a multi-rank
+// job (kernels of different ranks must never be separate launches on one GPU: nothing would guarantee that
+// they run at the same time).
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) pullKernelEmu(const PullArgs* all) { pullBody<T, 0>(all[blockIdx.y]); }
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) oneShotKernelEmu(const OneShotArgs* all) { oneShotBody<T>(all[blockIdx.y]); }
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) ringKernelEmu(const RingArgs* all) { ringBody<T>(all[blockIdx.y]); }
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) treeKernelEmu(const TreeArgs* all) { treeBody<T>(all[blockIdx.y]); }
 
 // ---- Send / Recv -------------------------------------------------------------------------------------------------
 // One CTA per flow (peer, direction); ops of a flow run in order.  The sender writes chunks into the

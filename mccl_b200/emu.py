@@ -1,0 +1,30 @@
+"""Single-GPU emulation of a multi-rank all-reduce: n buffers on one device stand for n ranks and one
+cooperative launch runs every rank's CTAs through the production kernel bodies (two-shot, one-shot, ring,
+double-binary tree).  For tests on machines with one GPU and for profiling the collective kernels."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+import torch
+
+from . import _lib as L
+from .comm import _torch_dtypes
+
+
+def all_reduce(tensors: Sequence[torch.Tensor], op: str = "sum", algo: str = "twoshot", ctas: int = 0, stream=None) -> None:
+    """In-place all-reduce across `tensors` (same shape and dtype, all on the current CUDA device)."""
+    lib = L.load()
+    f = lib.mcclEmuAllReduce
+    f.restype = C.c_int
+    f.argtypes = [C.c_int, C.POINTER(C.c_void_p), C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    n = len(tensors)
+    assert all(t.is_cuda and t.is_contiguous() and t.shape == tensors[0].shape and t.dtype == tensors[0].dtype for t in tensors)
+    ptrs = (C.c_void_p * n)(*[t.data_ptr() for t in tensors])
+    s = stream.cuda_stream if stream is not None else torch.cuda.current_stream(tensors[0].device).cuda_stream
+    L.check(f(n, ptrs, tensors[0].numel(), _torch_dtypes()[tensors[0].dtype], L.OPS[op], L.ALGOS[algo], ctas, C.c_void_p(s)),
+            "mcclEmuAllReduce")
+
+
+def destroy() -> None:
+    L.load().mcclEmuDestroy()

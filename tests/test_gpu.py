@@ -245,3 +245,39 @@ def test_fused_layer_norm_matches_fp32_reference():
     # widths the kernel does not cover fall back to PyTorch
     ln = FusedLayerNorm(128).to(device=dev, dtype=torch.bfloat16)
     assert ln(torch.randn(4, 128, device=dev).to(torch.bfloat16)).shape == (4, 128)
+
+
+@pytest.mark.parametrize("algo", ["twoshot", "oneshot", "ring", "tree"])
+def test_emulated_ranks_all_reduce_on_one_gpu(algo):
+    """The production kernel bodies with 2-8 emulated ranks in one cooperative launch on one GPU."""
+    _require_cuda()
+    from mccl_b200 import emu
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    for n in (2, 3, 8):
+        for dtype in (torch.float32, torch.bfloat16, torch.int32):
+            for numel in ((4096, 60000) if algo == "oneshot" else (4096, 1_000_003 if algo == "twoshot" else 1_000_000)):
+                if algo in ("ring", "tree", "oneshot") and (numel * torch.empty((), dtype=dtype).element_size()) % 16:
+                    continue
+                for op in ("sum", "avg", "max"):
+                    g = torch.Generator(device="cuda").manual_seed(n * 1000 + numel)
+                    if dtype.is_floating_point:
+                        xs = [(torch.rand(numel, generator=g, device=dev) * 2 - 1).to(dtype) for _ in range(n)]
+                        st = torch.stack([x.double() for x in xs])
+                    else:
+                        xs = [torch.randint(-1000, 1000, (numel,), generator=g, device=dev, dtype=dtype) for _ in range(n)]
+                        st = torch.stack([x.long() for x in xs])
+                    ref = st.sum(0) if op in ("sum", "avg") else st.max(0).values
+                    if op == "avg":
+                        ref = ref / n if dtype.is_floating_point else torch.div(ref.to(dtype), n, rounding_mode="trunc")
+                    emu.all_reduce(xs, op=op, algo=algo)
+                    torch.cuda.synchronize()
+                    for r, x in enumerate(xs):
+                        if dtype.is_floating_point:
+                            tol = {torch.float32: 1e-5, torch.bfloat16: 3e-2}[dtype] * (n if algo in ("ring", "tree") else 1)
+                            err = ((x.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
+                            assert err <= tol, (algo, n, dtype, numel, op, r, err)
+                        else:
+                            assert torch.equal(x, ref.to(dtype)), (algo, n, dtype, numel, op, r)
+                        assert torch.equal(x, xs[0]), "ranks must end with identical bytes"
+    emu.destroy()
