@@ -281,3 +281,26 @@ def test_emulated_ranks_all_reduce_on_one_gpu(algo):
                             assert torch.equal(x, ref.to(dtype)), (algo, n, dtype, numel, op, r)
                         assert torch.equal(x, xs[0]), "ranks must end with identical bytes"
     emu.destroy()
+
+
+def test_emulated_ranks_misaligned_buffers():
+    """Buffers that do not start on a 16-byte boundary take the element-granular path of the two-shot kernel."""
+    _require_cuda()
+    from mccl_b200 import emu
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    for dtype, numel in ((torch.float32, 100_003), (torch.bfloat16, 77_777), (torch.int32, 5)):
+        n = 4
+        g = torch.Generator(device="cuda").manual_seed(7)
+        bases = [torch.zeros(numel + 3, device=dev, dtype=dtype) for _ in range(n)]
+        views = [b[1:numel + 1] for b in bases]                       # 2 or 4 bytes past a 16-byte boundary
+        for v in views:
+            v.copy_((torch.rand(numel, generator=g, device=dev) * 200 - 100).to(dtype))
+        ref = torch.stack([v.double() for v in views]).sum(0)
+        emu.all_reduce(views, op="sum", algo="twoshot")
+        torch.cuda.synchronize()
+        for b, v in zip(bases, views):
+            err = ((v.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
+            assert err <= (3e-2 if dtype == torch.bfloat16 else 1e-5), (dtype, err)
+            assert b[0] == 0 and b[numel + 1] == 0 and b[numel + 2] == 0     # neighbours untouched
+    emu.destroy()
