@@ -141,6 +141,12 @@ PullArgs basePull(const Call& k, size_t bytesForCtas, int algo) {
   return a;
 }
 
+// Defined further down (they need the ring / tree launcher).
+mcclResult_t agRingFwd(const Call& k, const void* send, void* recv, size_t slot);
+mcclResult_t rsRingFwd(const Call& k, const void* send, void* recv, size_t blk);
+mcclResult_t bcastTreeFwd(const Call& k, const void* send, void* recv, size_t bytes, int root);
+mcclResult_t reduceTreeFwd(const Call& k, const void* send, void* recv, size_t bytes, int root);
+
 }  // namespace
 
 namespace {
@@ -281,7 +287,7 @@ mcclResult_t arNvls(const Call& k, const void* send, void* recv, size_t bytes) {
   return mcclSuccess;
 }
 
-mcclResult_t ringTreeOn(const Call& k, char* const buf[], size_t bytes, int algo) {
+mcclResult_t ringTreeOn(const Call& k, char* const buf[], size_t bytes, int algo, int phases = 0, int shift = 0) {
   const Channel& ch = k.c->chan;
   if (algo == mcclAlgoRing) {
     RingArgs a;
@@ -293,6 +299,8 @@ mcclResult_t ringTreeOn(const Call& k, char* const buf[], size_t bytes, int algo
     a.prev = ch.ring.prev;
     a.next = ch.ring.next;
     a.bytes = bytes;
+    a.phases = phases;
+    a.shift = shift;
     for (int p = 0; p < k.n; ++p) a.buf[p] = buf[p];
     DISPATCH_ALL_TYPES(k.dt, ringKernel, a.nCtas, k.s, a);
     return launched(k.c, "ringKernel");
@@ -304,6 +312,7 @@ mcclResult_t ringTreeOn(const Call& k, char* const buf[], size_t bytes, int algo
   a.op = (k.op == mcclAvg) ? mcclSum : k.op;
   a.divisor = k.divisor;
   a.bytes = bytes;
+  a.phases = phases;
   const TreeView* tv[2] = {&ch.tree, ch.dtree ? &ch.treeB : &ch.tree};
   for (int t = 0; t < 2; ++t) {
     a.up[t] = tv[t]->up;
@@ -313,6 +322,14 @@ mcclResult_t ringTreeOn(const Call& k, char* const buf[], size_t bytes, int algo
   for (int p = 0; p < k.n; ++p) a.buf[p] = buf[p];
   DISPATCH_ALL_TYPES(k.dt, treeKernel, a.nCtas, k.s, a);
   return launched(k.c, "treeKernel");
+}
+
+// Roots of the two trees the tree kernel walks (the second equals the first without a double-binary tree).
+void treeRoots(const mcclComm* c, int* rootA, int* rootB) {
+  *rootA = *rootB = 0;
+  for (int r = 0; r < c->nRanks; ++r) if (c->chan.treeParent[r] < 0) *rootA = r;
+  *rootB = *rootA;
+  if (c->chan.dtree) for (int r = 0; r < c->nRanks; ++r) if (c->chan.treeParentB[r] < 0) *rootB = r;
 }
 
 mcclResult_t arRingTree(const Call& k, const void* send, void* recv, size_t bytes, int algo) {
@@ -376,6 +393,7 @@ mcclResult_t allGather(const Call& k, const void* send, void* recv, size_t sendc
     a.bytes = slot;
     return launchNvls(k, a, false);
   }
+  if (algo == mcclAlgoRing && slot % 16 == 0 && slot >= 16 && al16(send) && al16(recv)) return agRingFwd(k, send, recv, slot);
   k.c->lastAlgo.store(mcclAlgoOneShot);
   if ((inPlace && rv.sym()) || sv.sym()) {
     PullArgs a = basePull(k, slot * k.n, mcclAlgoTwoShot);
@@ -416,6 +434,7 @@ mcclResult_t reduceScatter(const Call& k, const void* send, void* recv, size_t r
     a.divisor = k.divisor;
     return launchNvls(k, a, true);
   }
+  if (algo == mcclAlgoRing && blk % 16 == 0 && blk >= 16 && al16(send) && al16(recv)) return rsRingFwd(k, send, recv, blk);
   k.c->lastAlgo.store(mcclAlgoOneShot);
   if (sv.sym()) {
     PullArgs a = basePull(k, blk * k.n, mcclAlgoTwoShot);
@@ -486,6 +505,8 @@ mcclResult_t broadcast(const Call& k, const void* send, void* recv, size_t count
     a.bytes = bytes;
     return launchNvls(k, a, false, true);
   }
+  if (algo == mcclAlgoTree && bytes % 16 == 0 && bytes >= 64 && al16(recv) && (k.r != root || al16(send)))
+    return bcastTreeFwd(k, send, recv, bytes, root);
   k.c->lastAlgo.store(direct ? mcclAlgoOneShot : mcclAlgoTwoShot);
   char* work[MCCL_MAX_RANKS];
   if (rv.sym()) {
@@ -539,6 +560,8 @@ mcclResult_t reduce(const Call& k, const void* send, void* recv, size_t count, i
     a.divisor = k.divisor;
     return launchNvls(k, a, true, true);
   }
+  if (algo == mcclAlgoTree && bytes % 16 == 0 && bytes >= 64 && al16(send) && (k.r != root || al16(recv)))
+    return reduceTreeFwd(k, send, recv, bytes, root);
   k.c->lastAlgo.store(direct ? mcclAlgoOneShot : mcclAlgoTwoShot);
   // The stage is cut in two: inputs that are not symmetric go to the first half, folded shards to the second.
   size_t half = k.stageBytes() / 2 / 256 * 256;
@@ -586,6 +609,122 @@ mcclResult_t allToAll(const Call& k, const void* send, void* recv, size_t count)
   return mcclSuccess;
 }
 
+}  // namespace
+
+namespace {
+
+// Ring all-gather: the gather steps of the ring kernel on a buffer of n slots; with shift 1 a rank starts
+// out holding its own slot.
+mcclResult_t agRing(const Call& k, const void* send, void* recv, size_t slot) {
+  char* out = static_cast<char*>(recv);
+  const View rv = viewOf(k.st, recv, slot * k.n);
+  Call kk = k; kk.op = mcclSum; kk.divisor = 1; kk.dt = carrierType(slot); kk.es = mcclDataSize(kk.dt);
+  char* buf[MCCL_MAX_RANKS];
+  if (rv.sym() && al16(recv)) {
+    MCCLCHECK(launchCopy(k.c, send, out + (size_t)k.r * slot, 1, slot, slot, slot, k.s));
+    for (int p = 0; p < k.n; ++p) buf[p] = rv.peer(p);
+    return ringTreeOn(kk, buf, slot * k.n, mcclAlgoRing, 2, 1);
+  }
+  size_t chunk = stageChunk(k, k.n) / 16 * 16;
+  for (int p = 0; p < k.n; ++p) buf[p] = k.stagePeer(p);
+  for (size_t off = 0; off < slot; off += chunk) {
+    const size_t len = std::min(chunk, slot - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal() + (size_t)k.r * len, 1, len, len, len, k.s));
+    MCCLCHECK(ringTreeOn(kk, buf, len * k.n, mcclAlgoRing, 2, 1));
+    MCCLCHECK(launchCopy(k.c, k.stageLocal(), out + off, k.n, len, len, slot, k.s));
+  }
+  return mcclSuccess;
+}
+
+// Ring reduce-scatter: the reduce steps of the ring kernel on a staged copy of the input (they fold in
+// place); with shift 1 rank r ends up owning block r.
+mcclResult_t rsRing(const Call& k, const void* send, void* recv, size_t blk) {
+  size_t chunk = stageChunk(k, k.n) / 16 * 16;
+  char* buf[MCCL_MAX_RANKS];
+  for (int p = 0; p < k.n; ++p) buf[p] = k.stagePeer(p);
+  for (size_t off = 0; off < blk; off += chunk) {
+    const size_t len = std::min(chunk, blk - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), k.n, len, blk, len, k.s));
+    MCCLCHECK(ringTreeOn(k, buf, len * k.n, mcclAlgoRing, 1, 1));
+    MCCLCHECK(launchCopy(k.c, k.stageLocal() + (size_t)k.r * len, static_cast<char*>(recv) + off, 1, len, len, len, k.s));
+  }
+  return mcclSuccess;
+}
+
+// The two halves the tree kernel works on, as byte ranges.
+void treeHalves(size_t bytes, size_t* h0, size_t* h1) {
+  const size_t V = bytes / 16;
+  *h0 = (V / 2) * 16;
+  *h1 = bytes - *h0;
+}
+
+// Tree broadcast: the tree roots fetch their halves from the broadcast root, then the down phase of the tree
+// kernel carries them to everyone.
+mcclResult_t bcastTreeOn(const Call& k, char* const work[], size_t bytes, int root) {
+  int rootA, rootB;
+  treeRoots(k.c, &rootA, &rootB);
+  size_t h0, h1;
+  treeHalves(bytes, &h0, &h1);
+  Call kk = k; kk.op = mcclSum; kk.divisor = 1; kk.dt = carrierType(bytes); kk.es = mcclDataSize(kk.dt);
+  PullArgs a = basePull(kk, bytes, mcclAlgoTwoShot);
+  if (k.r == rootA && k.r != root && h0 > 0) a.jobs[a.nJobs++] = CopyJob{work[root], work[k.r], h0};
+  if (k.r == rootB && k.r != root && h1 > 0) a.jobs[a.nJobs++] = CopyJob{work[root] + h0, work[k.r] + h0, h1};
+  MCCLCHECK(launchPull(k.c, a, kk.dt, k.s));
+  return ringTreeOn(kk, work, bytes, mcclAlgoTree, 2, 0);
+}
+
+mcclResult_t bcastTree(const Call& k, const void* send, void* recv, size_t bytes, int root) {
+  const View rv = viewOf(k.st, recv, bytes);
+  char* work[MCCL_MAX_RANKS];
+  if (rv.sym() && al16(recv)) {
+    if (k.r == root) MCCLCHECK(launchCopy(k.c, send, recv, 1, bytes, bytes, bytes, k.s));
+    for (int p = 0; p < k.n; ++p) work[p] = rv.peer(p);
+    return bcastTreeOn(k, work, bytes, root);
+  }
+  const size_t chunk = stageChunk(k, 1) / 16 * 16;
+  for (int p = 0; p < k.n; ++p) work[p] = k.stagePeer(p);
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    if (k.r == root) MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+    MCCLCHECK(bcastTreeOn(k, work, len, root));
+    MCCLCHECK(launchCopy(k.c, k.stageLocal(), static_cast<char*>(recv) + off, 1, len, len, len, k.s));
+  }
+  return mcclSuccess;
+}
+
+// Tree reduce: the up phase of the tree kernel on a staged copy of the input leaves each half reduced at its
+// tree's root; the reduce root then fetches the two halves.
+mcclResult_t reduceTree(const Call& k, const void* send, void* recv, size_t bytes, int root) {
+  int rootA, rootB;
+  treeRoots(k.c, &rootA, &rootB);
+  const size_t chunk = stageChunk(k, 1) / 16 * 16;
+  char* work[MCCL_MAX_RANKS];
+  for (int p = 0; p < k.n; ++p) work[p] = k.stagePeer(p);
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+    MCCLCHECK(ringTreeOn(k, work, len, mcclAlgoTree, 1, 0));
+    size_t h0, h1;
+    treeHalves(len, &h0, &h1);
+    Call kk = k; kk.op = mcclSum; kk.divisor = 1;
+    PullArgs a = basePull(kk, len, mcclAlgoTwoShot);
+    if (k.r == root) {
+      char* dst = static_cast<char*>(recv) + off;
+      if (h0 > 0) a.jobs[a.nJobs++] = CopyJob{work[rootA], dst, h0};
+      if (h1 > 0) a.jobs[a.nJobs++] = CopyJob{work[rootB] + h0, dst + h0, h1};
+    }
+    MCCLCHECK(launchPull(k.c, a, carrierType(len), k.s));
+  }
+  return mcclSuccess;
+}
+
+}  // namespace
+
+namespace {
+mcclResult_t agRingFwd(const Call& k, const void* send, void* recv, size_t slot) { return agRing(k, send, recv, slot); }
+mcclResult_t rsRingFwd(const Call& k, const void* send, void* recv, size_t blk) { return rsRing(k, send, recv, blk); }
+mcclResult_t bcastTreeFwd(const Call& k, const void* send, void* recv, size_t bytes, int root) { return bcastTree(k, send, recv, bytes, root); }
+mcclResult_t reduceTreeFwd(const Call& k, const void* send, void* recv, size_t bytes, int root) { return reduceTree(k, send, recv, bytes, root); }
 }  // namespace
 
 // ---- entry points used by the runtime ------------------------------------------------------------------------------
@@ -855,8 +994,10 @@ mcclResult_t emuLaunch(const void* kernel, const std::vector<Args>& args, int ct
 
 // In-place all-reduce over `nRanks` buffers of this device, one per emulated rank.  algo: two-shot, one-shot,
 // ring or tree.  Returns mcclRemoteError if a device wait gave up.
-extern "C" mcclResult_t mcclEmuAllReduce(int nRanks, void* const* bufs, uint64_t count, int dt, int op, int algo, int ctas,
-                                         mcclStream_t stream) {
+// `phases` / `shift`: the ring kernel's reduce (1) and gather (2) steps or the tree kernel's up (1) and down (2)
+// phases on their own, as the reduce-scatter / all-gather / reduce / broadcast launchers use them (0 = both).
+extern "C" mcclResult_t mcclEmuPhases(int nRanks, void* const* bufs, uint64_t count, int dt, int op, int algo, int phases,
+                                      int shift, int ctas, mcclStream_t stream) {
   using namespace mccl;
   if (nRanks < 2 || nRanks > MCCL_MAX_RANKS || bufs == nullptr || count == 0 || (unsigned)op >= (unsigned)mcclNumOps) return mcclInvalidArgument;
   const size_t es = mcclDataSize((mcclDataType_t)dt);
@@ -903,7 +1044,7 @@ extern "C" mcclResult_t mcclEmuAllReduce(int nRanks, void* const* bufs, uint64_t
       RingArgs& a = args[r];
       memset(&a, 0, sizeof(a));
       a.peers = emuPeers(r); a.nCtas = ctas; a.op = redOp; a.divisor = divisor;
-      a.prev = (r + n - 1) % n; a.next = (r + 1) % n; a.bytes = bytes;
+      a.prev = (r + n - 1) % n; a.next = (r + 1) % n; a.bytes = bytes; a.phases = phases; a.shift = shift;
       for (int p = 0; p < n; ++p) a.buf[p] = static_cast<char*>(bufs[p]);
     }
     rc = emuLaunch(EMU_KERNEL(dt, ringKernelEmu), args, ctas, s);
@@ -913,7 +1054,7 @@ extern "C" mcclResult_t mcclEmuAllReduce(int nRanks, void* const* bufs, uint64_t
     for (int r = 0; r < n; ++r) {
       TreeArgs& a = args[r];
       memset(&a, 0, sizeof(a));
-      a.peers = emuPeers(r); a.nCtas = ctas; a.op = redOp; a.divisor = divisor; a.bytes = bytes;
+      a.peers = emuPeers(r); a.nCtas = ctas; a.op = redOp; a.divisor = divisor; a.bytes = bytes; a.phases = phases;
       getDtree(n, r, &a.up[0], &a.down[0][0], &a.down[0][1], &a.up[1], &a.down[1][0], &a.down[1][1]);
       for (int p = 0; p < n; ++p) a.buf[p] = static_cast<char*>(bufs[p]);
     }
@@ -924,6 +1065,11 @@ extern "C" mcclResult_t mcclEmuAllReduce(int nRanks, void* const* bufs, uint64_t
   MCCLCHECK(rc);
   CUDACHECK(cudaStreamSynchronize(s));
   return gEmu.statusHost->code == 0 ? mcclSuccess : mcclRemoteError;
+}
+
+extern "C" mcclResult_t mcclEmuAllReduce(int nRanks, void* const* bufs, uint64_t count, int dt, int op, int algo, int ctas,
+                                         mcclStream_t stream) {
+  return mcclEmuPhases(nRanks, bufs, count, dt, op, algo, 0, 0, ctas, stream);
 }
 
 extern "C" void mcclEmuDestroy(void) { mccl::emuDestroy(); }

@@ -125,6 +125,10 @@ struct RingArgs {
   char* buf[MCCL_MAX_RANKS];   // every rank's work buffer (peer-visible), in place
   uint64_t bytes;
   int divisor;
+  int phases;                  // bit 0: reduce-scatter steps, bit 1: all-gather steps (0 = both = all-reduce)
+  int shift;                   // ring chunk c stands for the ((c - shift) mod n)-th part of the buffer; with
+                               // shift 1 a rank ends the reduce phase owning (and starts the gather phase
+                               // holding) its own part, which is what reduce-scatter / all-gather need
 };
 
 struct TreeArgs {
@@ -136,6 +140,7 @@ struct TreeArgs {
   char* buf[MCCL_MAX_RANKS];
   uint64_t bytes;
   int divisor;
+  int phases;                  // bit 0: up (fold towards the tree roots), bit 1: down (copy from the roots); 0 = both
 };
 
 struct P2pDesc {

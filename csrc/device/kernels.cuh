@@ -256,10 +256,13 @@ __device__ __forceinline__ void ringBody(const RingArgs& a) {
   uint64_t* nextSig = &flagsOf(P, a.next)->sig[cta][r];
   const uint64_t* prevSig = &mine->sig[cta][a.prev];
   int done = 0;
-  for (int step = 0; ok && step < 2 * (n - 1); ++step) {
-    const bool reducing = step < n - 1;
-    const int i = reducing ? step : step - (n - 1);
-    const int chunk = reducing ? ((r - (i + 1)) % n + n) % n : ((r - i) % n + n) % n;
+  const bool hasRS = a.phases == 0 || (a.phases & 1), hasAG = a.phases == 0 || (a.phases & 2);
+  const int nSteps = (hasRS ? n - 1 : 0) + (hasAG ? n - 1 : 0);
+  for (int step = 0; ok && step < nSteps; ++step) {
+    const bool reducing = hasRS && step < n - 1;
+    const int i = reducing ? step : step - (hasRS ? n - 1 : 0);
+    const int ringChunk = reducing ? ((r - (i + 1)) % n + n) % n : ((r - i) % n + n) % n;
+    const int chunk = ((ringChunk - a.shift) % n + n) % n;
     if (step > 0) {
       if (tid == 0 && !waitFlag(prevSig, tag + step, P, 2u, a.prev, step)) sFail = 1;
       __syncthreads();
@@ -315,15 +318,16 @@ __device__ __forceinline__ void treeBody(const TreeArgs& a) {
     // two trees use disjoint, increasing values.
     const uint64_t upTag = tag + 4 * t + 1, downTag = tag + 4 * t + 2;
     char* own = a.buf[r];
+    const bool doUp = a.phases == 0 || (a.phases & 1), doDown = a.phases == 0 || (a.phases & 2);
     // up: fold the children's partial sums into mine
-    if (tid == 0) {
+    if (tid == 0 && doUp) {
       if (d0 >= 0 && !waitFlag(&mine->sig[cta][d0], upTag, P, 2u, d0, 1)) sFail = 1;
       if (d1 >= 0 && !sFail && !waitFlag(&mine->sig[cta][d1], upTag, P, 2u, d1, 1)) sFail = 1;
     }
     __syncthreads();
     if (sFail) { ok = false; break; }
     const int divisor = up < 0 ? a.divisor : 1;               // the root finishes the sum
-    if (d0 >= 0 || d1 >= 0 || divisor > 1) {
+    if (doUp && (d0 >= 0 || d1 >= 0 || divisor > 1)) {
       for (uint64_t k = lo + tid; k < hi; k += kThreads) {
         A acc[N];
         accInit<T>(acc, ldLocal128(own + k * 16));
@@ -336,15 +340,15 @@ __device__ __forceinline__ void treeBody(const TreeArgs& a) {
     if (up >= 0) {
       if (tid == 0) {
         __threadfence_system();
-        stReleaseSys(&flagsOf(P, up)->sig[cta][r], upTag);
-        if (!waitFlag(&mine->sig[cta][up], downTag, P, 2u, up, 2)) sFail = 1;   // down: parent holds the result
+        if (doUp) stReleaseSys(&flagsOf(P, up)->sig[cta][r], upTag);
+        if (doDown && !waitFlag(&mine->sig[cta][up], downTag, P, 2u, up, 2)) sFail = 1;   // down: parent holds the result
       }
       __syncthreads();
       if (sFail) { ok = false; break; }
-      copyVecs(a.buf[up], own, lo, hi, tid, kThreads);
+      if (doDown) copyVecs(a.buf[up], own, lo, hi, tid, kThreads);
       __syncthreads();
     }
-    if (tid == 0) {
+    if (tid == 0 && doDown) {
       __threadfence_system();
       if (d0 >= 0) stReleaseSys(&flagsOf(P, d0)->sig[cta][r], downTag);
       if (d1 >= 0) stReleaseSys(&flagsOf(P, d1)->sig[cta][r], downTag);

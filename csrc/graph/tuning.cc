@@ -156,8 +156,10 @@ bool algoSupports(int algo, int coll, int dt, int op, bool cudaTransport) {
       if (dt == mcclFloat16 || dt == mcclBfloat16) return op == mcclSum || op == mcclAvg || op == mcclMax || op == mcclMin;
       if (dt == mcclInt32 || dt == mcclUint32) return op == mcclSum || op == mcclMax || op == mcclMin || op == mcclAvg;
       return false;
-    case mcclAlgoRing: case mcclAlgoTree:
-      return coll == mcclCollAllReduce;       // the other collectives have direct, two-shot and NVLS kernels only
+    case mcclAlgoRing:    // the ring kernel's reduce steps / gather steps
+      return coll == mcclCollAllReduce || coll == mcclCollAllGather || coll == mcclCollReduceScatter;
+    case mcclAlgoTree:    // the tree kernel's up phase / down phase
+      return coll == mcclCollAllReduce || coll == mcclCollBroadcast || coll == mcclCollReduce;
     case mcclAlgoTwoShot:
       return coll == mcclCollAllReduce || coll == mcclCollBroadcast || coll == mcclCollReduce;
     case mcclAlgoOneShot:

@@ -26,5 +26,19 @@ def all_reduce(tensors: Sequence[torch.Tensor], op: str = "sum", algo: str = "tw
             "mcclEmuAllReduce")
 
 
+def phases(tensors: Sequence[torch.Tensor], algo: str, phase_mask: int, shift: int = 0, op: str = "sum", ctas: int = 0) -> None:
+    """Run only part of the ring kernel (1 = reduce steps, 2 = gather steps) or of the tree kernel (1 = up,
+    2 = down) in place over `tensors`; `shift=1` makes ring rank r own / start with the r-th part."""
+    lib = L.load()
+    f = lib.mcclEmuPhases
+    f.restype = C.c_int
+    f.argtypes = [C.c_int, C.POINTER(C.c_void_p), C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    n = len(tensors)
+    ptrs = (C.c_void_p * n)(*[t.data_ptr() for t in tensors])
+    s = torch.cuda.current_stream(tensors[0].device).cuda_stream
+    L.check(f(n, ptrs, tensors[0].numel(), _torch_dtypes()[tensors[0].dtype], L.OPS[op], L.ALGOS[algo], phase_mask, shift, ctas,
+              C.c_void_p(s)), "mcclEmuPhases")
+
+
 def destroy() -> None:
     L.load().mcclEmuDestroy()

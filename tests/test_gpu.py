@@ -304,3 +304,59 @@ def test_emulated_ranks_misaligned_buffers():
             assert err <= (3e-2 if dtype == torch.bfloat16 else 1e-5), (dtype, err)
             assert b[0] == 0 and b[numel + 1] == 0 and b[numel + 2] == 0     # neighbours untouched
     emu.destroy()
+
+
+def test_emulated_ring_and_tree_phases():
+    """The partial forms the cuda transport uses for ring all-gather / reduce-scatter and tree broadcast / reduce."""
+    _require_cuda()
+    from mccl_b200 import emu
+    import ctypes as C
+    lib = __import__("mccl_b200").load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    for n in (2, 3, 8):
+        part = 4096 + 8 * n                                         # elements per part, a multiple of 4 (16 bytes of fp32)
+        g = torch.Generator(device="cuda").manual_seed(n)
+        # ring gather steps, shift 1: rank r starts with part r filled, everyone ends with all parts
+        truth = torch.rand(n * part, generator=g, device=dev)
+        bufs = [torch.full((n * part,), -1.0, device=dev) for _ in range(n)]
+        for r in range(n):
+            bufs[r][r * part:(r + 1) * part] = truth[r * part:(r + 1) * part]
+        emu.phases(bufs, "ring", 2, shift=1)
+        torch.cuda.synchronize()
+        assert all(torch.equal(b, truth) for b in bufs), ("ring gather", n)
+        # ring reduce steps, shift 1: rank r ends owning the fully reduced part r
+        ins = [torch.rand(n * part, generator=g, device=dev) for _ in range(n)]
+        ref = torch.stack([x.double() for x in ins]).sum(0)
+        work = [x.clone() for x in ins]
+        emu.phases(work, "ring", 1, shift=1, op="avg")
+        torch.cuda.synchronize()
+        for r in range(n):
+            got = work[r][r * part:(r + 1) * part].double()
+            assert ((got - ref[r * part:(r + 1) * part] / n).abs() / (ref[r * part:(r + 1) * part].abs() / n + 1)).max() < 1e-5, ("ring reduce", n, r)
+        # tree up: each half ends reduced at its tree's root; tree down: the roots' halves reach everyone
+        roots = []
+        for t in (0, 1):
+            for r in range(n):
+                out = (C.c_int * 6)()
+                lib.mcclDbgDtree(n, r, out)
+                if out[3 * t] < 0:
+                    roots.append(r)
+        half = (n * part // 4 // 2) * 4
+        work = [x.clone() for x in ins]
+        emu.phases(work, "tree", 1)
+        torch.cuda.synchronize()
+        assert ((work[roots[0]][:half].double() - ref[:half]).abs() / (ref[:half].abs() + 1)).max() < 1e-5, ("tree up A", n)
+        assert ((work[roots[1]][half:].double() - ref[half:]).abs() / (ref[half:].abs() + 1)).max() < 1e-5, ("tree up B", n)
+        bufs = [torch.full((n * part,), -1.0, device=dev) for _ in range(n)]
+        bufs[roots[0]][:half] = truth[:half]
+        bufs[roots[1]][half:] = truth[half:]
+        emu.phases(bufs, "tree", 2)
+        torch.cuda.synchronize()
+        assert all(torch.equal(b, truth) for b in bufs), ("tree down", n)
+    emu.destroy()
+
+
+@need2
+def test_forced_ring_and_tree_for_other_collectives():
+    assert_all_ok(run_ranks(min(NGPU, 4), "forced_ring_tree", worker="_gpu_worker.py", timeout=600))
