@@ -178,6 +178,21 @@ def p2p_group():
     comm.finalize(); comm.destroy()
 
 
+def stripe_integrity():
+    """Byte-pattern transfers around the striping threshold with several sockets per connection (the reference's
+    MCCL_M2M_MAIN check: data[i] == i & 0xff on arrival)."""
+    comm = make_comm()
+    peer = 1 - RANK
+    for nbytes in (1, 4095, 256 * 1024 - 1, 256 * 1024, 256 * 1024 + 1, 3 * 1024 * 1024 + 7):
+        pattern = (np.arange(nbytes, dtype=np.uint32) & 0xFF).astype(np.uint8)
+        got = np.zeros(nbytes, np.uint8)
+        with mccl.group():
+            comm.send(pattern, peer)
+            comm.recv(got, peer)
+        assert np.array_equal(got, pattern), nbytes
+    comm.finalize(); comm.destroy()
+
+
 def nonblocking():
     comm = make_comm(blocking=False)
     n = 1 << 18

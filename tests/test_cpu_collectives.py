@@ -53,3 +53,8 @@ def test_usage_errors_do_not_latch():
 
 def test_ddp_matches_single_process():
     assert_all_ok(run_ranks(2, "ddp_cpu"))
+
+
+def test_striped_transfer_integrity():
+    assert_all_ok(run_ranks(2, "stripe_integrity", env={"MCCL_NSOCKS": "4"}))
+    assert_all_ok(run_ranks(2, "stripe_integrity", env={"MCCL_NSOCKS": "1"}))
