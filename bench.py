@@ -50,7 +50,8 @@ def host_max(comm, value: float) -> float:
 def main() -> int:
     args = parse()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also under a multi-rank launch
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
     if args.warmup < 3:
         args.warmup = 3
