@@ -5,7 +5,9 @@ pointer, element count and dtype are taken from the object and handed to libmccl
 """
 from __future__ import annotations
 
+import atexit
 import ctypes as C
+import weakref
 from contextlib import contextmanager
 from typing import Optional
 
@@ -97,6 +99,20 @@ def group():
     L.check(lib.mcclGroupEnd(), "mcclGroupEnd")
 
 
+_live = weakref.WeakSet()
+
+
+@atexit.register
+def _destroy_live_communicators() -> None:
+    # A process that exits with peer mappings and multicast bindings still in place leaves the tear-down to
+    # the driver at an arbitrary moment; destroying explicitly unbinds and unmaps in order.
+    for comm in list(_live):
+        try:
+            comm.destroy()
+        except Exception:
+            pass
+
+
 class Communicator:
     """One rank's handle on a communicator (wraps mcclComm_t)."""
 
@@ -112,6 +128,7 @@ class Communicator:
             L.check(self._lib.mcclCommInitRankConfig(C.byref(self._h), n_ranks, uid, rank, C.byref(cfg)),
                     "mcclCommInitRankConfig")
         self._sym = {}
+        _live.add(self)
 
     # ---- queries
     @property
@@ -198,6 +215,7 @@ class Communicator:
         L.check(self._lib.mcclCommAbort(self._h), "mcclCommAbort")
 
     def destroy(self) -> None:
+        _live.discard(self)
         if self._h:
             self._sym.clear()
             self._lib.mcclCommDestroy(self._h)
