@@ -301,6 +301,17 @@ class Communicator:
         self._sym[t.data_ptr()] = holder
         return t
 
+    def register(self, tensor) -> int:
+        """Collective: map an existing CUDA tensor (cudaMalloc memory, e.g. from torch's allocator) into every
+        peer through CUDA IPC so the peer-load algorithms use it in place.  Returns a handle for deregister()."""
+        h = C.c_void_p()
+        nbytes = tensor.numel() * tensor.element_size()
+        L.check(self._lib.mcclCommRegister(self._h, C.c_void_p(tensor.data_ptr()), nbytes, C.byref(h)), "mcclCommRegister")
+        return h.value
+
+    def deregister(self, handle: int) -> None:
+        L.check(self._lib.mcclCommDeregister(self._h, C.c_void_p(handle)), "mcclCommDeregister")
+
     def peer_pointer(self, tensor_or_ptr, peer: int) -> int:
         p = tensor_or_ptr.data_ptr() if hasattr(tensor_or_ptr, "data_ptr") else int(tensor_or_ptr)
         out = C.c_void_p()

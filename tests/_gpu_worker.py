@@ -253,6 +253,33 @@ def forced_ring_tree():
     comm.finalize(); comm.destroy()
 
 
+def register_user_buffer():
+    """mcclCommRegister: a tensor from torch's allocator becomes peer-visible (CUDA IPC) and is reduced in place."""
+    comm = make_comm()
+    n = (1 << 20) + 4
+    x = torch.empty(n, device=DEV, dtype=torch.float32)
+    peer = (RANK + 1) % WORLD
+    assert comm.peer_pointer(x, peer) == 0
+    before = comm.launch_count
+    h = comm.register(x)
+    assert comm.peer_pointer(x, peer) != 0 and comm.peer_pointer(x, RANK) == x.data_ptr()
+    x.copy_(gen(RANK, n, torch.float32))
+    with mccl.forced_algo("twoshot"):
+        comm.all_reduce(x, op="sum")
+    torch.cuda.synchronize()
+    check("registered all-reduce", x, oracle(n, torch.float32, "sum"), torch.float32)
+    assert comm.launch_count - before == 1, "a registered buffer needs no staging copies"
+    g = torch.empty(n * WORLD, device=DEV, dtype=torch.float32)
+    comm.all_gather(x, g); torch.cuda.synchronize()          # registered source, plain destination
+    assert torch.equal(g[RANK * n:(RANK + 1) * n], x)
+    comm.deregister(h)
+    assert comm.peer_pointer(x, peer) == 0
+    y = gen(RANK, 1000, torch.float32)
+    comm.all_reduce(y); torch.cuda.synchronize()             # staging path still fine afterwards
+    check("after deregister", y, oracle(1000, torch.float32, "sum"), torch.float32)
+    comm.finalize(); comm.destroy()
+
+
 def large_root_collectives():
     """Broadcast and reduce of a message large enough for the many-CTA root-only NVLS path, plus a 1 GB
     all-reduce (round-robin work tiles), against the oracle."""

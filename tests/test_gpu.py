@@ -360,3 +360,8 @@ def test_emulated_ring_and_tree_phases():
 @need2
 def test_forced_ring_and_tree_for_other_collectives():
     assert_all_ok(run_ranks(min(NGPU, 4), "forced_ring_tree", worker="_gpu_worker.py", timeout=600))
+
+
+@need2
+def test_register_user_buffer():
+    assert_all_ok(run_ranks(2, "register_user_buffer", worker="_gpu_worker.py", timeout=300))
