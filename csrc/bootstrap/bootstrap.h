@@ -5,6 +5,7 @@
 // of mis-parsed, and all sockets carry deadlines so a rank that dies mid-round fails the round.
 #pragma once
 
+#include <atomic>
 #include <cstdint>
 #include <mutex>
 #include <vector>
@@ -28,7 +29,7 @@ struct Bootstrap {
   std::vector<int> fds;         // rank 0: fds[r] for r > 0
   uint32_t seq = 0;
   std::mutex mu;                // one round at a time
-  bool aborted = false;
+  std::atomic<bool> aborted{false};   // set by Abort from any thread
 };
 
 MCCL_PARAM(BootstrapTimeoutSec);

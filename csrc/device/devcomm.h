@@ -156,4 +156,8 @@ struct P2pArgs {
   P2pDesc ops[MCCL_MAX_P2P_OPS];
 };
 
+// Shard r of a message of `bytes` bytes cut into n shards on 16-byte boundaries; the last shard takes the tail.
+inline uint64_t shardOff(uint64_t bytes, int n, int r) { return (uint64_t)(((unsigned __int128)(bytes / 16) * (unsigned)r) / (unsigned)n) * 16; }
+inline uint64_t shardEnd(uint64_t bytes, int n, int r) { return r == n - 1 ? bytes : shardOff(bytes, n, r + 1); }
+
 }  // namespace mccl

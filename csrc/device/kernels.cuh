@@ -10,6 +10,7 @@
 //   treeKernel    double-binary-tree all-reduce, even CTAs on tree 0 / first half, odd CTAs on tree 1.
 //   p2pKernel     Send/Recv batch through per-peer FIFO slots.
 //   copyKernel    local 2-D copy used for staging.
+// The non-template kernels are `static` because this header is compiled into more than one translation unit.
 //
 // Algorithm parity with the reference: direct fold order src/device/all_reduce.h:44-58, ring steps
 // :63-101, tree :148-225; fused here: the fold, the dtype widening, the 1/world scale and the
@@ -379,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1) treeKernelEmu(const TreeArgs* all
 // ---- Send / Recv -------------------------------------------------------------------------------------------------
 // One CTA per flow (peer, direction); ops of a flow run in order.  The sender writes chunks into the
 // receiver's slot (two halves) and publishes a running chunk count; the receiver drains and acknowledges.
-__global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_constant__ P2pArgs a) {
+static __global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_constant__ P2pArgs a) {
   __shared__ int sFail;
   const DevPeers& P = a.peers;
   const int tid = threadIdx.x, me = P.rank;
@@ -441,7 +442,7 @@ __global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_constant__
 
 // Wait until any peer has announced a chunk this rank has not drained yet; writes the peer into *out
 // (pinned host memory), or -1 after the time budget.
-__global__ void recvAnyProbeKernel(DevPeers P, int* out) {
+static __global__ void recvAnyProbeKernel(DevPeers P, int* out) {
   if (threadIdx.x != 0) return;
   CtrlFlags* mine = flagsOf(P, P.rank);
   const uint64_t t0 = globalTimerNs();
@@ -454,7 +455,7 @@ __global__ void recvAnyProbeKernel(DevPeers P, int* out) {
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) barrierKernel(DevPeers P) {
+static __global__ void __launch_bounds__(kThreads, 1) barrierKernel(DevPeers P) {
   __shared__ int sFail;
   if (threadIdx.x == 0) sFail = 0;
   CtrlFlags* mine = flagsOf(P, P.rank);
@@ -464,7 +465,7 @@ __global__ void __launch_bounds__(kThreads, 1) barrierKernel(DevPeers P) {
 }
 
 // rows x rowBytes, each row at its own pitch.
-__global__ void __launch_bounds__(kThreads) copyKernel(const char* src, char* dst, uint64_t rows, uint64_t rowBytes,
+static __global__ void __launch_bounds__(kThreads) copyKernel(const char* src, char* dst, uint64_t rows, uint64_t rowBytes,
                                                        uint64_t srcPitch, uint64_t dstPitch) {
   const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (uint64_t)gridDim.x * blockDim.x;
   const bool vec = aligned16(src) && aligned16(dst) && (rowBytes & 15) == 0 && (srcPitch & 15) == 0 && (dstPitch & 15) == 0;
