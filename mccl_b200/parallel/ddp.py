@@ -17,6 +17,7 @@ docs/perf-scaling.png, README.md:55-57); the wrapper itself has no counterpart t
 """
 from __future__ import annotations
 
+from contextlib import contextmanager
 from typing import List, Optional
 
 import torch
@@ -56,6 +57,7 @@ class DistributedDataParallel(nn.Module):
         self.step_count = 0
         self._norm_sq = None
         self._norm_scratch = None
+        self._sync = True
         params = [p for p in module.parameters() if p.requires_grad]
         if not params:
             raise ValueError("module has no trainable parameters")
@@ -119,7 +121,7 @@ class DistributedDataParallel(nn.Module):
     # ---- backward-time communication
     def _launch(self, b: _Bucket) -> None:
         b.launched = True
-        if self.world == 1:
+        if self.world == 1 or not self._sync:
             return
         if self.overlap and self.comm_stream is not None:
             b.ready_event = torch.cuda.Event()
@@ -139,7 +141,19 @@ class DistributedDataParallel(nn.Module):
             self._launch(b)
 
     def forward(self, *args, **kwargs):
+        if torch.is_grad_enabled():
+            self._reset()                 # a new backward pass will count every parameter's gradient again
         return self.module(*args, **kwargs)
+
+    @contextmanager
+    def no_sync(self):
+        """Gradient accumulation: backward passes inside this context add into the buckets without
+        communicating; the first backward pass outside it all-reduces the accumulated gradients."""
+        prev, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = prev
 
     def finish_backward(self) -> None:
         """Launch whatever has not gone out yet (unused parameters) and make the current stream wait for all buckets."""

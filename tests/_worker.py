@@ -360,5 +360,31 @@ def ddp_cpu():
     comm.finalize(); comm.destroy()
 
 
+def ddp_accumulate():
+    """Two micro-batches (the first under no_sync) give the gradient of the concatenated batch."""
+    import torch
+    from mccl_b200.models.gpt2 import GPT2, GPT2Config
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    comm = make_comm()
+    torch.manual_seed(0)
+    cfg = GPT2Config.tiny()
+    model = GPT2(cfg)
+    ddp = DistributedDataParallel(model, comm, bucket_mb=0.25)
+    g = torch.Generator().manual_seed(11)
+    tokens = torch.randint(0, cfg.vocab_size, (4 * WORLD, cfg.seq_len + 1), generator=g)
+    mine = tokens[4 * RANK: 4 * RANK + 4]
+    before = comm.launch_count
+    with ddp.no_sync():
+        (ddp(mine[:2, :-1], mine[:2, 1:]) / 2).backward()
+    (ddp(mine[2:, :-1], mine[2:, 1:]) / 2).backward()
+    ddp.finish_backward()
+    torch.manual_seed(0)
+    single = GPT2(cfg)
+    single(tokens[:, :-1], tokens[:, 1:]).backward()
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), single.named_parameters()):
+        assert torch.allclose(p1.grad, p2.grad, atol=2e-6, rtol=1e-4), (n1, (p1.grad - p2.grad).abs().max().item())
+    comm.finalize(); comm.destroy()
+
+
 if __name__ == "__main__":
     globals()[sys.argv[1]]()

@@ -58,3 +58,7 @@ def test_ddp_matches_single_process():
 def test_striped_transfer_integrity():
     assert_all_ok(run_ranks(2, "stripe_integrity", env={"MCCL_NSOCKS": "4"}))
     assert_all_ok(run_ranks(2, "stripe_integrity", env={"MCCL_NSOCKS": "1"}))
+
+
+def test_ddp_gradient_accumulation():
+    assert_all_ok(run_ranks(2, "ddp_accumulate"))
