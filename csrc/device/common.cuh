@@ -199,7 +199,7 @@ __device__ __forceinline__ void copyVecs(const char* src, char* dst, uint64_t lo
 // GPU work inside one window of G x 256 KB.  (With one huge contiguous slice per CTA, a 32 GB all-reduce
 // touched 32 windows 128 MB apart on every GPU at once and lost a fifth of its bandwidth.)  The split
 // depends on (V, G) only, so CTA b covers the same units on every rank and in every phase.
-__device__ __forceinline__ uint64_t tileUnits(uint64_t V, int G) {
+__host__ __device__ __forceinline__ uint64_t tileUnits(uint64_t V, int G) {
   uint64_t per = (V + (uint64_t)G - 1) / (uint64_t)G;
   per = (per + 511) / 512 * 512;
   return per > 16384 ? 16384 : (per < 512 ? 512 : per);

@@ -169,3 +169,19 @@ extern "C" mcclResult_t mcclEmuAllReduce(int nRanks, void* const* bufs, uint64_t
 }
 
 extern "C" void mcclEmuDestroy(void) { mccl::emuDestroy(); }
+
+// ---- index-arithmetic probes (host only): the work splits the kernels rely on, for exhaustive CPU tests ----------------
+
+// Tiles CTA `cta` of `G` takes out of V units: writes up to `cap` (lo, hi) pairs, returns how many there are.
+extern "C" int mcclDbgWorkSplit(uint64_t V, int G, int cta, uint64_t* lo, uint64_t* hi, int cap) {
+  const uint64_t tile = mccl::tileUnits(V, G);
+  int k = 0;
+  for (uint64_t a = (uint64_t)cta * tile; a < V; a += (uint64_t)G * tile, ++k)
+    if (k < cap) { lo[k] = a; hi[k] = a + tile < V ? a + tile : V; }
+  return k;
+}
+
+extern "C" void mcclDbgShard(uint64_t bytes, int n, int r, uint64_t* off, uint64_t* end) {
+  *off = mccl::shardOff(bytes, n, r);
+  *end = mccl::shardEnd(bytes, n, r);
+}

@@ -116,7 +116,7 @@ __device__ __forceinline__ bool commBarrier(const DevPeers& P, uint64_t& epoch, 
 // AG starts with the own shard and continues in the order the shards arrive; RS starts with the block of
 // rank+1 and ends with the own block, so partial results for the peers leave early.
 template <int MODE>
-__device__ __forceinline__ void tileCoords(int t, int tilesN, int panel, int stripesPerBlock, int rank, int n, int* stripe, int* nt) {
+__host__ __device__ __forceinline__ void tileCoords(int t, int tilesN, int panel, int stripesPerBlock, int rank, int n, int* stripe, int* nt) {
   const int perPanel = panel * tilesN;
   const int p = t / perPanel, within = t - p * perPanel;
   const int ord = p * panel + within % panel;

@@ -138,6 +138,21 @@ int mcclTpGemmLastError(void) {
   return v;
 }
 
+// Index-arithmetic probe (host only): the (row stripe, column tile) the t-th tile of a GEMM maps to, for
+// mode 0 = plain, 1 = all-gather, 2 = reduce-scatter.  Also reports the tile width the launcher would pick.
+int mcclDbgGemmTile(int mode, int M, int N, int nRanks, int rank, int sms, int t, int* stripe, int* nt, int* bn, int* panel) {
+  if (M % (BM * nRanks) || N % 64) return -1;
+  *bn = pickBN(M, N, sms);
+  if (*bn == 0) return -1;
+  const int stripes = M / BM, stripesPerBlock = stripes / nRanks, tilesN = N / *bn;
+  *panel = pickPanel(stripesPerBlock);
+  if (t < 0 || t >= stripes * tilesN) return -1;
+  if (mode == 0) tileCoords<MODE_PLAIN>(t, tilesN, *panel, stripesPerBlock, rank, nRanks, stripe, nt);
+  else if (mode == 1) tileCoords<MODE_AG>(t, tilesN, *panel, stripesPerBlock, rank, nRanks, stripe, nt);
+  else tileCoords<MODE_RS>(t, tilesN, *panel, stripesPerBlock, rank, nRanks, stripe, nt);
+  return stripes * tilesN;
+}
+
 // C[M,N] = act(A[M,K] * B[N,K]^T), bf16 in and out, on the current device.
 mcclResult_t mcclTpGemm(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int maxCtas, mcclStream_t stream) {
   if (A == nullptr || B == nullptr || C == nullptr) return mcclInvalidArgument;

@@ -293,3 +293,65 @@ def test_env_knobs_at_init(tmp_path, monkeypatch):
     root = ET.parse(tmp_path / "topo.xml").getroot()
     ring = [a for a in root.findall("algo") if a.get("name") == "ring"][0]
     assert float(ring.get("alpha_us")) == 7.5 and float(ring.get("step_us")) == 2.5 and float(ring.get("model_bw")) == 3.25
+
+
+def test_work_split_covers_every_unit_once(lib):
+    """The CTA work split of the collective kernels: tiles of all CTAs partition [0, V) for any size and CTA count."""
+    f = lib.mcclDbgWorkSplit
+    f.restype = C.c_int
+    f.argtypes = [C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int]
+    cap = 4096
+    lo, hi = (C.c_uint64 * cap)(), (C.c_uint64 * cap)()
+    for V in (0, 1, 7, 511, 512, 513, 16384, 16385, 1_000_003, 32 * 16384, 32 * 16384 + 5, 50_000_000):
+        for G in (1, 2, 3, 16, 32, 64, 128):
+            spans = []
+            for cta in range(G):
+                k = f(V, G, cta, lo, hi, cap)
+                assert k <= cap
+                spans += [(lo[i], hi[i]) for i in range(k)]
+            spans.sort()
+            pos = 0
+            for a, b in spans:
+                assert a == pos and b > a, (V, G, a, b, pos)
+                pos = b
+            assert pos == V, (V, G, pos)
+
+
+def test_shards_are_16_byte_aligned_and_cover_the_message(lib):
+    f = lib.mcclDbgShard
+    f.restype = None
+    f.argtypes = [C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    for nbytes in (1, 15, 16, 17, 100, 4099, 1 << 20, (1 << 30) + 6, 34359738368):
+        for n in (2, 3, 4, 8, 16):
+            pos = 0
+            for r in range(n):
+                off, end = C.c_uint64(), C.c_uint64()
+                f(nbytes, n, r, C.byref(off), C.byref(end))
+                assert off.value == pos and off.value % 16 == 0 and end.value >= off.value
+                pos = end.value
+            assert pos == nbytes                                # the last shard takes the tail
+
+
+def test_gemm_tile_order_visits_every_tile_once(lib):
+    """Rasterisation of the tcgen05 GEMM: plain, all-gather (own shard first) and reduce-scatter (own block last)."""
+    f = lib.mcclDbgGemmTile
+    f.restype = C.c_int
+    f.argtypes = [C.c_int] * 7 + [C.POINTER(C.c_int)] * 4
+    for mode, M, N, n in ((0, 8192, 3584, 1), (0, 384, 448, 1), (0, 128 * 13, 64, 1), (1, 8192, 3584, 8), (2, 8192, 8192, 8),
+                          (1, 8192, 7168, 4), (2, 2048, 1024, 2), (2, 128 * 6, 192, 3)):
+        for rank in range(n):
+            s_, nt_, bn, panel = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+            total = f(mode, M, N, n, rank, 148, 0, C.byref(s_), C.byref(nt_), C.byref(bn), C.byref(panel))
+            assert total == (M // 128) * (N // bn.value) and N % bn.value == 0
+            seen, order = set(), []
+            for t in range(total):
+                assert f(mode, M, N, n, rank, 148, t, C.byref(s_), C.byref(nt_), C.byref(bn), C.byref(panel)) == total
+                assert 0 <= s_.value < M // 128 and 0 <= nt_.value < N // bn.value
+                seen.add((s_.value, nt_.value)); order.append(s_.value)
+            assert len(seen) == total                               # a bijection
+            per_block = (M // 128) // n
+            blocks = [order[i] // per_block for i in range(0, total, per_block * (N // bn.value))]
+            if mode == 1:
+                assert blocks == [(rank + i) % n for i in range(n)]     # own shard first, then in arrival order
+            if mode == 2:
+                assert blocks == [(rank + 1 + i) % n for i in range(n)]  # peers' blocks first, own block last
