@@ -5,12 +5,24 @@
 // Parity: src/coll/coll.cc:16-106 of the reference.
 #include <cstring>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../comm/comm.h"
 #include "../core/trace.h"
 
 using namespace mccl;
 
+DEFINE_MCCL_PARAM(Nvtx, "NVTX", 1)
+
 namespace {
+
+// An NVTX range around the host side of every collective ("mcclAllReduce", ...), visible to any attached
+// profiler; with none attached the header-only NVTX stubs return at once.  MCCL_NVTX=0 removes the calls.
+struct NvtxRange {
+  bool on;
+  explicit NvtxRange(const char* name) : on(mcclParamNvtx() != 0) { if (on) nvtxRangePushA(name); }
+  ~NvtxRange() { if (on) nvtxRangePop(); }
+};
 
 mcclResult_t checkCommon(mcclComm_t comm, mcclDataType_t dt) {
   if (comm == nullptr) return mcclInvalidArgument;
@@ -23,6 +35,7 @@ mcclResult_t checkCommon(mcclComm_t comm, mcclDataType_t dt) {
 // caller's stream (cuda) or the whole blocking call (tcp).
 mcclResult_t issue(mcclComm_t comm, const char* what, size_t bytes, mcclStream_t stream, std::function<mcclResult_t()> fn) {
   auto traced = [=]() -> mcclResult_t {
+    NvtxRange range(what);
     if (!traceEnabled()) return fn();
     TraceSpan span = traceBegin(comm, what, bytes, comm->lastAlgo.load(), stream);
     const mcclResult_t rc = fn();

@@ -17,6 +17,7 @@ docs/perf-scaling.png, README.md:55-57); the wrapper itself has no counterpart t
 """
 from __future__ import annotations
 
+import os
 from contextlib import contextmanager
 from typing import List, Optional
 
@@ -46,7 +47,7 @@ class _Bucket:
 
 
 class DistributedDataParallel(nn.Module):
-    def __init__(self, module: nn.Module, comm: Optional[Communicator] = None, bucket_mb: float = 25.0,
+    def __init__(self, module: nn.Module, comm: Optional[Communicator] = None, bucket_mb: Optional[float] = None,
                  overlap: bool = True, comm_ctas: int = 16, weight_decay: float = 0.1, betas=(0.9, 0.95), eps: float = 1e-8):
         super().__init__()
         self.module = module
@@ -65,6 +66,8 @@ class DistributedDataParallel(nn.Module):
         self.dtype = params[0].dtype
         if self.device.type == "cuda" and self.dtype != torch.bfloat16:
             raise ValueError("the fused optimizer path expects bf16 parameters")
+        if bucket_mb is None:
+            bucket_mb = float(os.environ.get("MCCL_BUCKET_MB", "25"))
         cap = int(bucket_mb * (1 << 20)) // params[0].element_size()
         # Matrices decay, vectors (biases, norms) do not: they live in separate buckets so a bucket has one setting.
         self.buckets: List[_Bucket] = []
