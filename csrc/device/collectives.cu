@@ -256,6 +256,31 @@ NvlsArgs baseNvls(const Call& k, size_t bytes, bool rootOnly = false) {
   return a;
 }
 
+// Rooted collectives with one shard per rank (NvlsRootedArgs).  Off unless MCCL_NVLS_SPREAD=1: the root-only
+// form below stays the default until this one has been timed against it.
+bool nvlsSpread() {
+  static const bool on = envInt("MCCL_NVLS_SPREAD", 0) != 0;
+  return on;
+}
+
+mcclResult_t launchNvlsRooted(const Call& k, const NvlsRootedArgs& a) {
+  static const int unroll = (int)envInt("MCCL_NVLS_UNROLL", 4);
+  const mcclDataType_t dt = a.reducing ? k.dt : mcclFloat32;      // a broadcast moves bits
+#define ROOTED(T)                                                                        \
+  do {                                                                                   \
+    if (unroll >= 8) nvlsRootedKernel<T, 8><<<a.nCtas, kThreads, 0, k.s>>>(a);           \
+    else nvlsRootedKernel<T, 4><<<a.nCtas, kThreads, 0, k.s>>>(a);                       \
+  } while (0)
+  switch (dt) {
+    case mcclFloat32:  ROOTED(float); break;
+    case mcclFloat16:  ROOTED(__half); break;
+    case mcclBfloat16: ROOTED(__nv_bfloat16); break;
+    default: return mcclInvalidArgument;
+  }
+#undef ROOTED
+  return launched(k.c, "nvlsRootedKernel");
+}
+
 // NVLS all-reduce on multicast-mapped memory: the switch adds my shard across ranks and replicates the result.
 mcclResult_t arNvlsOn(const Call& k, char* mcIn, char* mcOut, size_t bytes) {
   NvlsArgs a = baseNvls(k, bytes);
@@ -492,6 +517,21 @@ mcclResult_t broadcast(const Call& k, const void* send, void* recv, size_t count
   const View rv = viewOf(k.st, recv, bytes);
   const bool direct = algo == mcclAlgoOneShot;
   if (algo == mcclAlgoNvls && k.st->nvls && rv.sym() && rv.mc() && bytes % 16 == 0 && al16(recv) && (k.r != root || al16(send))) {
+    if (nvlsSpread() && bytes >= (size_t)k.n * 16) {
+      // The peers read the root's destination buffer, so an out-of-place root copies there first.
+      if (k.r == root) MCCLCHECK(launchCopy(k.c, send, recv, 1, bytes, bytes, bytes, k.s));
+      NvlsRootedArgs a;
+      memset(&a, 0, sizeof(a));
+      a.peers = k.st->peers;
+      a.nCtas = pickCtas(k.c, bytes, mcclAlgoNvls);
+      a.root = root;
+      a.reducing = 0;
+      a.rootBuf = k.r == root ? static_cast<const char*>(recv) : rv.peer(root);
+      a.mcDst = rv.mc();
+      a.bytes = bytes;
+      a.divisor = 1;
+      return launchNvlsRooted(k, a);
+    }
     NvlsArgs a = baseNvls(k, bytes, true);
     a.loadReduce = 0;
     a.mcStore = 1;
@@ -546,6 +586,30 @@ mcclResult_t reduce(const Call& k, const void* send, void* recv, size_t count, i
   const bool direct = algo == mcclAlgoOneShot;
   if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op) && bytes % 16 == 0 && al16(send) &&
       (k.r != root || al16(recv))) {
+    if (nvlsSpread() && bytes >= (size_t)k.n * 16) {
+      NvlsRootedArgs a;
+      memset(&a, 0, sizeof(a));
+      a.peers = k.st->peers;
+      a.nCtas = baseNvls(k, bytes, true).nCtas;      // enough CTAs for the root to work alone if it has to
+      a.op = (k.op == mcclAvg) ? mcclSum : k.op;
+      a.root = root;
+      a.reducing = 1;
+      a.rootBuf = sv.peer(root);
+      a.mcSrc = sv.mc();
+      a.bytes = bytes;
+      a.divisor = k.divisor;
+      if (k.r == root) {
+        // The peers can reach the destination only through their mapping of the root's source allocation.
+        const View rv = viewOf(k.st, recv, bytes);
+        a.local = static_cast<char*>(recv);
+        a.note = kNoteAlone;
+        if (rv.sym() && rv.seg == sv.seg) {
+          const int64_t delta = (int64_t)rv.off - (int64_t)sv.off;
+          if (delta == 0 || (uint64_t)(delta < 0 ? -delta : delta) >= bytes) a.note = (uint64_t)delta;
+        }
+      }
+      return launchNvlsRooted(k, a);
+    }
     NvlsArgs a = baseNvls(k, bytes, true);
     a.loadReduce = 1;
     a.mcStore = 0;

@@ -12,6 +12,12 @@
 #define MCCL_MAX_CTAS 160      // upper bound on CTAs ("channels") of one collective kernel
 #define MCCL_COLL_THREADS 512
 
+#ifdef __CUDACC__
+#define MCCL_HD __host__ __device__
+#else
+#define MCCL_HD
+#endif
+
 namespace mccl {
 
 // Device status word (pinned host memory, one per communicator).  A wait that runs out of time records
@@ -41,7 +47,9 @@ struct CtrlFlags {
   uint64_t p2pTail[MCCL_MAX_RANKS];
   uint64_t p2pSent[MCCL_MAX_RANKS];
   uint64_t p2pRecvd[MCCL_MAX_RANKS];
-  // RecvAny: pending[src] = messages announced by `src` and not yet consumed.
+  // note[cta]: a word the root of a rooted collective publishes before the entry barrier of a call and its
+  // peers read after it (which form of the algorithm the root can take part in).
+  uint64_t note[MCCL_MAX_CTAS];
   uint64_t canary;            // 0x6d63636c63616e61, checked by tests after every run
 };
 
@@ -117,6 +125,30 @@ struct NvlsArgs {
   int divisor;
 };
 
+// Rooted NVLS collectives with the root's work spread over all ranks: every rank handles one shard.
+//   broadcast: rank r loads shard r of the root's buffer (a peer load; the root reads its own memory) and
+//              replicates it into every rank's copy with multimem.st;
+//   reduce:    rank r lets the switch add shard r over all ranks (multimem.ld_reduce) and stores the sum
+//              into the root's buffer (a peer store; the root writes its own memory).
+// Only the root knows where its destination of a reduce lies.  It publishes `note` (destination minus its
+// source, in bytes, when both lie in one symmetric allocation; kNoteAlone otherwise) and the peers add it
+// to their mapping of the root's source; with kNoteAlone the root reduces the whole message by itself.
+constexpr uint64_t kNoteAlone = 0x7fffffffffffffffull;
+struct NvlsRootedArgs {
+  DevPeers peers;
+  int nCtas;
+  int op;
+  int root;
+  int reducing;                // 1: reduce, 0: broadcast
+  const char* rootBuf;         // the root's buffer as mapped here: source of a broadcast, the root's SOURCE of a reduce
+  char* local;                 // root of a reduce: its destination
+  const char* mcSrc;           // reduce: multicast alias of the source
+  char* mcDst;                 // broadcast: multicast alias of the destination
+  uint64_t bytes;              // whole message, a multiple of 16
+  uint64_t note;               // reduce, root only
+  int divisor;
+};
+
 struct RingArgs {
   DevPeers peers;
   int nCtas;
@@ -157,7 +189,7 @@ struct P2pArgs {
 };
 
 // Shard r of a message of `bytes` bytes cut into n shards on 16-byte boundaries; the last shard takes the tail.
-inline uint64_t shardOff(uint64_t bytes, int n, int r) { return (uint64_t)(((unsigned __int128)(bytes / 16) * (unsigned)r) / (unsigned)n) * 16; }
-inline uint64_t shardEnd(uint64_t bytes, int n, int r) { return r == n - 1 ? bytes : shardOff(bytes, n, r + 1); }
+MCCL_HD inline uint64_t shardOff(uint64_t bytes, int n, int r) { return (uint64_t)(((unsigned __int128)(bytes / 16) * (unsigned)r) / (unsigned)n) * 16; }
+MCCL_HD inline uint64_t shardEnd(uint64_t bytes, int n, int r) { return r == n - 1 ? bytes : shardOff(bytes, n, r + 1); }
 
 }  // namespace mccl

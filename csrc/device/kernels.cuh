@@ -238,6 +238,66 @@ __global__ void __launch_bounds__(kThreads, 1) nvlsKernel(const __grid_constant_
   if (tid == 0) mine->epoch[cta] = epoch;
 }
 
+// Broadcast / reduce through the switch with one shard per rank (see NvlsRootedArgs).
+template <typename T, int U>
+__global__ void __launch_bounds__(kThreads, 1) nvlsRootedKernel(const __grid_constant__ NvlsRootedArgs a) {
+  __shared__ int sFail;
+  using A = typename Acc<T>::type;
+  constexpr int N = Pack<T>::N;
+  const DevPeers& P = a.peers;
+  const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x, n = P.n, r = P.rank;
+  const bool isRoot = r == a.root;
+  if (tid == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, r);
+  uint64_t epoch = mine->epoch[cta];
+  if (a.reducing && isRoot && tid == 0) mine->note[cta] = a.note;      // published by the entry barrier
+  bool ok = ctaBarrier(P, epoch, &sFail);
+  if (ok) {
+    uint64_t o0 = shardOff(a.bytes, n, r), o1 = shardEnd(a.bytes, n, r);
+    char* dst = nullptr;
+    bool active = true;
+    if (a.reducing) {
+      const uint64_t note = isRoot ? a.note : ldAcquireSys(&flagsOf(P, a.root)->note[cta]);
+      if (note == kNoteAlone) { active = isRoot; o0 = 0; o1 = a.bytes; dst = a.local; }
+      else dst = isRoot ? a.local : const_cast<char*>(a.rootBuf) + (int64_t)note;
+    }
+    if (active) {
+      const uint64_t V = (o1 - o0) / 16;
+      forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
+        for (uint64_t i = lo + tid; i < hi; i += (uint64_t)U * kThreads) {
+          uint4 v[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint64_t idx = i + (uint64_t)u * kThreads;
+            if (idx < hi) {
+              const uint64_t off = o0 + idx * 16;
+              v[u] = a.reducing ? mmLdReduce<T>(a.mcSrc + off, a.op) : (isRoot ? ldLocal128(a.rootBuf + off) : ldSys128(a.rootBuf + off));
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint64_t idx = i + (uint64_t)u * kThreads;
+            if (idx < hi) {
+              const uint64_t off = o0 + idx * 16;
+              uint4 out = v[u];
+              if (a.divisor > 1) {
+                A acc[N];
+                accInit<T>(acc, out);
+                out = accFinish<T>(acc, a.divisor);
+              }
+              if (!a.reducing) mmStore128(a.mcDst + off, out);
+              else if (isRoot) stLocal128(dst + off, out);
+              else stSys128(dst + off, out);
+            }
+          }
+        }
+      });
+    }
+  }
+  if (ok) ok = ctaBarrier(P, epoch, &sFail);
+  if (tid == 0) mine->epoch[cta] = epoch;
+}
+
 // ---- ring -----------------------------------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ void ringBody(const RingArgs& a) {

@@ -308,6 +308,39 @@ def large_root_collectives():
     comm.finalize(); comm.destroy()
 
 
+def rooted_spread():
+    """MCCL_NVLS_SPREAD=1: broadcast and reduce with one shard per rank.  In place, out of place inside one
+    allocation (the root publishes the offset), and with a destination the peers cannot reach (the root then
+    reduces alone); every root; sizes around the shard boundaries."""
+    comm = make_comm()
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (WORLD * 8, 4096 + 8, (3 << 20) + 64):
+            for root in range(WORLD):
+                b = comm.empty(n, dtype); b.zero_()
+                src = gen(root, n, dtype)
+                comm.broadcast(src if RANK == root else None, b, root=root); torch.cuda.synchronize()   # out of place on the root
+                assert torch.equal(b, src), ("broadcast", dtype, n, root, comm.last_algo)
+                two = comm.empty(2 * n, dtype)                  # source and destination halves of one allocation
+                s, o = two[:n], two[n:]
+                s.copy_(gen(RANK, n, dtype)); o.zero_()
+                ref = oracle(n, dtype, "sum")
+                comm.reduce(s, o, op="sum", root=root); torch.cuda.synchronize()
+                if RANK == root:
+                    check(("reduce same allocation", dtype, n, root, comm.last_algo), o, ref, dtype)
+                assert torch.equal(s, gen(RANK, n, dtype)), "reduce changed its source"
+                other = torch.zeros(n, device=DEV, dtype=dtype)   # not symmetric: the root works alone
+                comm.reduce(s, other, op="sum", root=root); torch.cuda.synchronize()
+                if RANK == root:
+                    check(("reduce alone", dtype, n, root), other, ref, dtype)
+                comm.reduce(s, s, op="avg", root=root); torch.cuda.synchronize()   # in place
+                if RANK == root:
+                    check(("reduce in place", dtype, n, root), s, oracle(n, dtype, "avg"), dtype)
+                for t in (b, two):
+                    comm.free_raw(t.data_ptr())
+    assert canary_ok(comm)
+    comm.finalize(); comm.destroy()
+
+
 def calibrate_and_trace():
     """MCCL_CALIBRATE=1 measures pair bandwidth and empty-collective latency at init and feeds the tuner;
     MCCL_TRACE writes a Chrome trace with a device track."""

@@ -363,5 +363,10 @@ def test_forced_ring_and_tree_for_other_collectives():
 
 
 @need2
+def test_rooted_collectives_spread_over_all_ranks():
+    assert_all_ok(run_ranks(min(NGPU, 4), "rooted_spread", worker="_gpu_worker.py", env={"MCCL_NVLS_SPREAD": "1"}, timeout=600))
+
+
+@need2
 def test_register_user_buffer():
     assert_all_ok(run_ranks(2, "register_user_buffer", worker="_gpu_worker.py", timeout=300))
