@@ -142,6 +142,10 @@ mcclResult_t agRingFwd(const Call& k, const void* send, void* recv, size_t slot)
 mcclResult_t rsRingFwd(const Call& k, const void* send, void* recv, size_t blk);
 mcclResult_t bcastTreeFwd(const Call& k, const void* send, void* recv, size_t bytes, int root);
 mcclResult_t reduceTreeFwd(const Call& k, const void* send, void* recv, size_t bytes, int root);
+mcclResult_t bcastRingFwd(const Call& k, const void* send, void* recv, size_t bytes, int root);
+mcclResult_t reduceRingFwd(const Call& k, const void* send, void* recv, size_t bytes, int root);
+mcclResult_t agTreeFwd(const Call& k, const void* send, void* recv, size_t slot);
+mcclResult_t rsTreeFwd(const Call& k, const void* send, void* recv, size_t blk);
 
 }  // namespace
 
@@ -415,6 +419,7 @@ mcclResult_t allGather(const Call& k, const void* send, void* recv, size_t sendc
     return launchNvls(k, a, false);
   }
   if (algo == mcclAlgoRing && slot % 16 == 0 && slot >= 16 && al16(send) && al16(recv)) return agRingFwd(k, send, recv, slot);
+  if (algo == mcclAlgoTree && slot % 16 == 0 && slot * k.n >= 64 && al16(send) && al16(recv)) return agTreeFwd(k, send, recv, slot);
   k.c->lastAlgo.store(mcclAlgoOneShot);
   if ((inPlace && rv.sym()) || sv.sym()) {
     PullArgs a = basePull(k, slot * k.n, mcclAlgoTwoShot);
@@ -456,6 +461,7 @@ mcclResult_t reduceScatter(const Call& k, const void* send, void* recv, size_t r
     return launchNvls(k, a, true);
   }
   if (algo == mcclAlgoRing && blk % 16 == 0 && blk >= 16 && al16(send) && al16(recv)) return rsRingFwd(k, send, recv, blk);
+  if (algo == mcclAlgoTree && blk % 16 == 0 && blk * k.n >= 64 && al16(send) && al16(recv)) return rsTreeFwd(k, send, recv, blk);
   k.c->lastAlgo.store(mcclAlgoOneShot);
   if (sv.sym()) {
     PullArgs a = basePull(k, blk * k.n, mcclAlgoTwoShot);
@@ -543,6 +549,8 @@ mcclResult_t broadcast(const Call& k, const void* send, void* recv, size_t count
   }
   if (algo == mcclAlgoTree && bytes % 16 == 0 && bytes >= 64 && al16(recv) && (k.r != root || al16(send)))
     return bcastTreeFwd(k, send, recv, bytes, root);
+  if (algo == mcclAlgoRing && bytes % 16 == 0 && bytes / 16 >= (size_t)k.n && al16(recv) && (k.r != root || al16(send)))
+    return bcastRingFwd(k, send, recv, bytes, root);
   k.c->lastAlgo.store(direct ? mcclAlgoOneShot : mcclAlgoTwoShot);
   char* work[MCCL_MAX_RANKS];
   if (rv.sym()) {
@@ -622,6 +630,8 @@ mcclResult_t reduce(const Call& k, const void* send, void* recv, size_t count, i
   }
   if (algo == mcclAlgoTree && bytes % 16 == 0 && bytes >= 64 && al16(send) && (k.r != root || al16(recv)))
     return reduceTreeFwd(k, send, recv, bytes, root);
+  if (algo == mcclAlgoRing && bytes % 16 == 0 && bytes / 16 >= (size_t)2 * k.n && al16(send) && (k.r != root || al16(recv)))
+    return reduceRingFwd(k, send, recv, bytes, root);
   k.c->lastAlgo.store(direct ? mcclAlgoOneShot : mcclAlgoTwoShot);
   // The stage is cut in two: inputs that are not symmetric go to the first half, folded shards to the second.
   size_t half = k.stageBytes() / 2 / 256 * 256;
@@ -778,9 +788,139 @@ mcclResult_t reduceTree(const Call& k, const void* send, void* recv, size_t byte
   return mcclSuccess;
 }
 
+// Ring broadcast: every rank fetches its own part from the root, then the gather steps of the ring kernel pass
+// the parts around (the root's outbound traffic is one copy of the message).
+mcclResult_t bcastRingOn(const Call& k, char* const work[], size_t bytes, int root) {
+  Call kk = k; kk.op = mcclSum; kk.divisor = 1; kk.dt = carrierType(bytes); kk.es = mcclDataSize(kk.dt);
+  PullArgs a = basePull(kk, bytes, mcclAlgoTwoShot);
+  const uint64_t o0 = shardOff(bytes, k.n, k.r), o1 = shardEnd(bytes, k.n, k.r);
+  if (k.r != root && o1 > o0) a.jobs[a.nJobs++] = CopyJob{work[root] + o0, work[k.r] + o0, o1 - o0};
+  MCCLCHECK(launchPull(k.c, a, kk.dt, k.s));
+  return ringTreeOn(kk, work, bytes, mcclAlgoRing, 2, 1);
+}
+
+mcclResult_t bcastRing(const Call& k, const void* send, void* recv, size_t bytes, int root) {
+  const View rv = viewOf(k.st, recv, bytes);
+  char* work[MCCL_MAX_RANKS];
+  if (rv.sym()) {
+    if (k.r == root) MCCLCHECK(launchCopy(k.c, send, recv, 1, bytes, bytes, bytes, k.s));
+    for (int p = 0; p < k.n; ++p) work[p] = rv.peer(p);
+    return bcastRingOn(k, work, bytes, root);
+  }
+  const size_t chunk = stageChunk(k, 1) / (16 * (size_t)k.n) * (16 * (size_t)k.n);
+  if (chunk == 0) return mcclInternalError;
+  for (int p = 0; p < k.n; ++p) work[p] = k.stagePeer(p);
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    if (k.r == root) MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+    if (len / 16 >= (size_t)k.n) MCCLCHECK(bcastRingOn(k, work, len, root));
+    else MCCLCHECK(bcastOn(k, work, nullptr, len, root, true));          // a tail shorter than one vector per rank
+    MCCLCHECK(launchCopy(k.c, k.stageLocal(), static_cast<char*>(recv) + off, 1, len, len, len, k.s));
+  }
+  return mcclSuccess;
+}
+
+// Ring reduce: the reduce steps of the ring kernel on a staged copy of the input leave part p reduced at rank
+// p; the root then fetches every part from its owner (src/device/reduce.h:104-173 of the reference).
+mcclResult_t reduceRing(const Call& k, const void* send, void* recv, size_t bytes, int root) {
+  const size_t chunk = stageChunk(k, 1) / (16 * (size_t)k.n) * (16 * (size_t)k.n);
+  if (chunk == 0) return mcclInternalError;
+  char* work[MCCL_MAX_RANKS];
+  for (int p = 0; p < k.n; ++p) work[p] = k.stagePeer(p);
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
+    if (len / 16 < (size_t)2 * k.n) {                                     // a tail too short for the ring
+      MCCLCHECK(reduceOn(k, work, work, k.r == root ? static_cast<char*>(recv) + off : nullptr, len, root, true));
+      continue;
+    }
+    MCCLCHECK(ringTreeOn(k, work, len, mcclAlgoRing, 1, 1));
+    Call kk = k; kk.op = mcclSum; kk.divisor = 1;
+    PullArgs a = basePull(kk, len, mcclAlgoTwoShot);
+    if (k.r == root) {
+      for (int i = 0; i < k.n; ++i) {
+        const int p = (k.r + i) % k.n;
+        const uint64_t q0 = shardOff(len, k.n, p), q1 = shardEnd(len, k.n, p);
+        if (q1 > q0) a.jobs[a.nJobs++] = CopyJob{work[p] + q0, static_cast<char*>(recv) + off + q0, q1 - q0};
+      }
+    }
+    MCCLCHECK(launchPull(k.c, a, carrierType(len), k.s));
+  }
+  return mcclSuccess;
+}
+
+// Tree all-gather: every rank puts its slot into a zeroed buffer of n slots and the tree kernel adds the
+// buffers as integers (x + 0 + ... + 0 = x bit for bit), the masked-sum form the reference uses for its deep
+// tree broadcast (src/device/broadcast.h:85-88).
+mcclResult_t agTree(const Call& k, const void* send, void* recv, size_t slot) {
+  char* out = static_cast<char*>(recv);
+  const View rv = viewOf(k.st, recv, slot * k.n);
+  Call kk = k; kk.op = mcclSum; kk.divisor = 1; kk.dt = mcclUint32; kk.es = 4;
+  char* buf[MCCL_MAX_RANKS];
+  if (rv.sym()) {
+    char* mine = out + (size_t)k.r * slot;
+    if (send != mine) MCCLCHECK(launchCopy(k.c, send, mine, 1, slot, slot, slot, k.s));
+    if (k.r > 0 && cudaMemsetAsync(out, 0, (size_t)k.r * slot, k.s) != cudaSuccess) return mcclSystemError;
+    if (k.r < k.n - 1 && cudaMemsetAsync(mine + slot, 0, (size_t)(k.n - 1 - k.r) * slot, k.s) != cudaSuccess) return mcclSystemError;
+    for (int p = 0; p < k.n; ++p) buf[p] = rv.peer(p);
+    return ringTreeOn(kk, buf, slot * k.n, mcclAlgoTree);
+  }
+  const size_t chunk = stageChunk(k, k.n) / 16 * 16;
+  if (chunk == 0) return mcclInternalError;
+  for (int p = 0; p < k.n; ++p) buf[p] = k.stagePeer(p);
+  for (size_t off = 0; off < slot; off += chunk) {
+    const size_t len = std::min(chunk, slot - off);
+    if (cudaMemsetAsync(k.stageLocal(), 0, len * k.n, k.s) != cudaSuccess) return mcclSystemError;
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal() + (size_t)k.r * len, 1, len, len, len, k.s));
+    if (len * k.n >= 64) MCCLCHECK(ringTreeOn(kk, buf, len * k.n, mcclAlgoTree));
+    else MCCLCHECK(twoShot(kk, buf, buf, nullptr, len * k.n, true, mcclAlgoTwoShot));
+    MCCLCHECK(launchCopy(k.c, k.stageLocal(), out + off, k.n, len, len, slot, k.s));
+  }
+  return mcclSuccess;
+}
+
+// Tree reduce-scatter: the up phase of the tree kernel on a staged copy of the n blocks leaves each half of it
+// reduced at its tree's root; rank r then fetches block r, which may straddle the two halves.
+mcclResult_t rsTree(const Call& k, const void* send, void* recv, size_t blk) {
+  int rootA, rootB;
+  treeRoots(k.c, &rootA, &rootB);
+  const size_t chunk = stageChunk(k, k.n) / 16 * 16;
+  if (chunk == 0) return mcclInternalError;
+  char* work[MCCL_MAX_RANKS];
+  for (int p = 0; p < k.n; ++p) work[p] = k.stagePeer(p);
+  for (size_t off = 0; off < blk; off += chunk) {
+    const size_t len = std::min(chunk, blk - off), total = len * k.n;
+    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), k.n, len, blk, len, k.s));
+    char* dst = static_cast<char*>(recv) + off;
+    if (total < 64) {                                                      // too short for two halves
+      PullArgs a = basePull(k, total, mcclAlgoTwoShot);
+      a.nSrcA = k.n;
+      for (int p = 0; p < k.n; ++p) a.srcA[p] = work[p] + (size_t)k.r * len;
+      a.dstA = dst;
+      a.aBytes = len;
+      MCCLCHECK(launchPull(k.c, a, k.dt, k.s));
+      continue;
+    }
+    MCCLCHECK(ringTreeOn(k, work, total, mcclAlgoTree, 1, 0));
+    size_t h0, h1;
+    treeHalves(total, &h0, &h1);
+    Call kk = k; kk.op = mcclSum; kk.divisor = 1;
+    PullArgs a = basePull(kk, total, mcclAlgoTwoShot);
+    const size_t b0 = (size_t)k.r * len, b1 = b0 + len;
+    if (b0 < h0) a.jobs[a.nJobs++] = CopyJob{work[rootA] + b0, dst, std::min(b1, h0) - b0};
+    if (b1 > h0) { const size_t s0 = std::max(b0, h0); a.jobs[a.nJobs++] = CopyJob{work[rootB] + s0, dst + (s0 - b0), b1 - s0}; }
+    MCCLCHECK(launchPull(k.c, a, carrierType(len), k.s));
+  }
+  return mcclSuccess;
+}
+
 }  // namespace
 
 namespace {
+mcclResult_t bcastRingFwd(const Call& k, const void* send, void* recv, size_t bytes, int root) { return bcastRing(k, send, recv, bytes, root); }
+mcclResult_t reduceRingFwd(const Call& k, const void* send, void* recv, size_t bytes, int root) { return reduceRing(k, send, recv, bytes, root); }
+mcclResult_t agTreeFwd(const Call& k, const void* send, void* recv, size_t slot) { return agTree(k, send, recv, slot); }
+mcclResult_t rsTreeFwd(const Call& k, const void* send, void* recv, size_t blk) { return rsTree(k, send, recv, blk); }
 mcclResult_t agRingFwd(const Call& k, const void* send, void* recv, size_t slot) { return agRing(k, send, recv, slot); }
 mcclResult_t rsRingFwd(const Call& k, const void* send, void* recv, size_t blk) { return rsRing(k, send, recv, blk); }
 mcclResult_t bcastTreeFwd(const Call& k, const void* send, void* recv, size_t bytes, int root) { return bcastTree(k, send, recv, bytes, root); }

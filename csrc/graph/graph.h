@@ -137,6 +137,7 @@ struct TunerModel {
   bool  viable[mcclNumAlgos];
   size_t oneShotMaxBytes;   // one-shot scratch slot size (cuda) / MCCL_DIRECT_MAX_BYTES (tcp)
   int    oneShotMaxRanks;
+  bool   cuda;              // constants describe the cuda transport's kernels
 };
 
 mcclResult_t tunerInit(const TopoSystem& sys, const TopoGraph graphs[mcclNumAlgos], bool cudaTransport, TunerModel* out);

@@ -55,6 +55,7 @@ double algoTraffic(int algo, int coll, int n) {
         case mcclAlgoRing: return 1.0;
         case mcclAlgoTree: return 2.0;            // an interior node forwards to two children
         case mcclAlgoNvls: return 1.0;
+        case mcclAlgoTwoShot: return 2.0 * f;     // scatter from the root, then all-gather
         default:           return (double)(n - 1); // root writes every peer
       }
     case mcclCollReduce:
@@ -62,6 +63,7 @@ double algoTraffic(int algo, int coll, int n) {
         case mcclAlgoRing: return f + 1.0 / n;
         case mcclAlgoTree: return 2.0;
         case mcclAlgoNvls: return 1.0;
+        case mcclAlgoTwoShot: return 2.0 * f;     // every rank folds a shard, the root collects them
         default:           return (double)(n - 1); // root reads every peer
       }
   }
@@ -71,6 +73,7 @@ double algoTraffic(int algo, int coll, int n) {
 mcclResult_t tunerInit(const TopoSystem& sys, const TopoGraph graphs[mcclNumAlgos], bool cudaTransport, TunerModel* out) {
   if (out == nullptr) MCCLFAIL(mcclInvalidArgument);
   (void)sys;
+  out->cuda = cudaTransport;
   for (int a = 0; a < mcclNumAlgos; ++a) {
     out->viable[a] = graphs[a].viable;
     out->bw[a] = graphs[a].bw;
@@ -131,8 +134,12 @@ mcclResult_t tunerSaveCache(const TunerModel& m, const char* path) {
 mcclResult_t tunerAlgoTime(const TunerModel& m, int algo, int coll, int n, size_t bytes, float* us) {
   if (us == nullptr || (unsigned)algo >= (unsigned)mcclNumAlgos) MCCLFAIL(mcclInvalidArgument);
   if (!m.viable[algo] || m.bw[algo] <= 0.f) { *us = INFINITY; return mcclSuccess; }
+  // bw[oneshot] describes the push all-reduce.  The "direct" forms of the other collectives on the cuda transport
+  // are plain peer copies / folds in the pull kernel, which sustains what two-shot's phases do.
+  const float bw = (m.cuda && algo == mcclAlgoOneShot && coll != mcclCollAllReduce && m.bw[mcclAlgoTwoShot] > 0.f)
+                       ? m.bw[mcclAlgoTwoShot] : m.bw[algo];
   *us = m.alphaUs[algo] + m.stepUs[algo] * (float)algoSteps(algo, n) +
-        (float)((double)bytes * algoTraffic(algo, coll, n) / (1000.0 * m.bw[algo]));
+        (float)((double)bytes * algoTraffic(algo, coll, n) / (1000.0 * bw));
   return mcclSuccess;
 }
 
@@ -156,10 +163,9 @@ bool algoSupports(int algo, int coll, int dt, int op, bool cudaTransport) {
       if (dt == mcclFloat16 || dt == mcclBfloat16) return op == mcclSum || op == mcclAvg || op == mcclMax || op == mcclMin;
       if (dt == mcclInt32 || dt == mcclUint32) return op == mcclSum || op == mcclMax || op == mcclMin || op == mcclAvg;
       return false;
-    case mcclAlgoRing:    // the ring kernel's reduce steps / gather steps
-      return coll == mcclCollAllReduce || coll == mcclCollAllGather || coll == mcclCollReduceScatter;
-    case mcclAlgoTree:    // the tree kernel's up phase / down phase
-      return coll == mcclCollAllReduce || coll == mcclCollBroadcast || coll == mcclCollReduce;
+    case mcclAlgoRing:    // the ring kernel's reduce steps / gather steps, with a scatter before or a collect after
+    case mcclAlgoTree:    // the tree kernel's up phase / down phase, likewise
+      return coll != mcclCollAllToAll;
     case mcclAlgoTwoShot:
       return coll == mcclCollAllReduce || coll == mcclCollBroadcast || coll == mcclCollReduce;
     case mcclAlgoOneShot:

@@ -218,38 +218,40 @@ def device_timeout():
 
 
 def forced_ring_tree():
-    """Ring all-gather / reduce-scatter and tree broadcast / reduce (partial phases of the ring and tree kernels),
-    symmetric and staged, sizes that do and do not meet the 16-byte rule (the latter fall back)."""
+    """Ring and tree forms of all-gather, reduce-scatter, broadcast and reduce (partial phases of the ring and tree
+    kernels plus a scatter before or a collect after), symmetric and staged, sizes that do and do not meet the
+    16-byte rule (the latter fall back)."""
     comm = make_comm()
-    for dtype in (torch.float32, torch.bfloat16):
-        for n in (8, 1000, 1027, 1 << 18):
-            for sym in (False, True):
-                mk = (lambda m: comm.empty(m, dtype)) if sym else (lambda m: torch.empty(m, device=DEV, dtype=dtype))
-                x = gen(RANK, n, dtype)
-                with mccl.forced_algo("ring"):
-                    s = mk(n); s.copy_(x); g = mk(n * WORLD)
-                    comm.all_gather(s, g); torch.cuda.synchronize()
-                    assert torch.equal(g, torch.cat([gen(r, n, dtype) for r in range(WORLD)])), ("ring allgather", dtype, n, sym, comm.last_algo)
-                    s2 = mk(n * WORLD); s2.copy_(gen(RANK + 50, n * WORLD, dtype)); keep = s2.clone(); o2 = mk(n)
-                    comm.reduce_scatter(s2, o2, op="avg"); torch.cuda.synchronize()
-                    assert torch.equal(s2, keep), "reduce-scatter must not modify its input"
-                    tol_scale = oracle(n * WORLD, dtype, "avg", 50)[RANK * n:(RANK + 1) * n]
-                    err = ((o2.double() - tol_scale).abs() / (tol_scale.abs() + 1.0)).max().item()
-                    assert err < (3e-2 * WORLD if dtype == torch.bfloat16 else 1e-5), ("ring reducescatter", dtype, n, sym, err)
-                with mccl.forced_algo("tree"):
-                    for root in {0, WORLD - 1}:
-                        b = mk(n); b.zero_()
-                        if RANK == root:
-                            b.copy_(x)
-                        comm.broadcast(b if RANK == root else None, b, root=root); torch.cuda.synchronize()
-                        assert torch.equal(b, gen(root, n, dtype)), ("tree broadcast", dtype, n, sym, root, comm.last_algo)
-                        s3 = mk(n); s3.copy_(x); o3 = mk(n)
-                        comm.reduce(s3, o3, op="sum", root=root); torch.cuda.synchronize()
-                        if RANK == root:
-                            ref = oracle(n, dtype, "sum")
-                            err = ((o3.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
-                            assert err < (3e-2 * WORLD if dtype == torch.bfloat16 else 1e-5), ("tree reduce", dtype, n, sym, root, err)
-                assert canary_ok(comm)
+    ftol = lambda dtype: 3e-2 * WORLD if dtype == torch.bfloat16 else 1e-5
+    cases = [(dtype, n, sym) for dtype in (torch.float32, torch.bfloat16) for n in (8, 1000, 1027, 1 << 18) for sym in (False, True)]
+    for dtype, n, sym in cases:
+        mk = (lambda m: comm.empty(m, dtype)) if sym else (lambda m: torch.empty(m, device=DEV, dtype=dtype))
+        x = gen(RANK, n, dtype)
+        for algo in ("ring", "tree"):
+            with mccl.forced_algo(algo):
+                s = mk(n); s.copy_(x); g = mk(n * WORLD)
+                comm.all_gather(s, g); torch.cuda.synchronize()
+                assert torch.equal(g, torch.cat([gen(r, n, dtype) for r in range(WORLD)])), (algo, "allgather", dtype, n, sym, comm.last_algo)
+                s2 = mk(n * WORLD); s2.copy_(gen(RANK + 50, n * WORLD, dtype)); keep = s2.clone(); o2 = mk(n)
+                comm.reduce_scatter(s2, o2, op="avg"); torch.cuda.synchronize()
+                assert torch.equal(s2, keep), "reduce-scatter must not modify its input"
+                ref = oracle(n * WORLD, dtype, "avg", 50)[RANK * n:(RANK + 1) * n]
+                err = ((o2.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
+                assert err < ftol(dtype), (algo, "reducescatter", dtype, n, sym, err)
+                for root in {0, WORLD - 1}:
+                    b = mk(n); b.zero_()
+                    if RANK == root:
+                        b.copy_(x)
+                    comm.broadcast(b if RANK == root else None, b, root=root); torch.cuda.synchronize()
+                    assert torch.equal(b, gen(root, n, dtype)), (algo, "broadcast", dtype, n, sym, root, comm.last_algo)
+                    s3 = mk(n); s3.copy_(x); o3 = mk(n)
+                    comm.reduce(s3, o3, op="sum", root=root); torch.cuda.synchronize()
+                    assert torch.equal(s3, x), "reduce must not modify its input"
+                    if RANK == root:
+                        ref = oracle(n, dtype, "sum")
+                        err = ((o3.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
+                        assert err < ftol(dtype), (algo, "reduce", dtype, n, sym, root, err)
+        assert canary_ok(comm)
     comm.finalize(); comm.destroy()
 
 

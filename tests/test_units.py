@@ -215,6 +215,13 @@ def test_tuner_choices(lib):
     assert _pick(lib, 4, 0, 0, 1 << 10)[0] == "oneshot"                  # tcp: direct path below 2 MiB
     assert _pick(lib, 4, 0, 0, 64 << 20)[0] == "ring"
     assert _pick(lib, 4, 0, 0, 1 << 10, coll="broadcast")[0] in ("ring", "tree")
+    # cuda without NVLS: ring and tree can run every collective but are never the model's choice; forced, they are used
+    for coll in ("allgather", "reducescatter", "broadcast", "reduce"):
+        for nbytes in (1 << 10, 1 << 20, 1 << 30):
+            assert _pick(lib, 8, 1, 0, nbytes, coll=coll)[0] in ("oneshot", "twoshot")
+            assert _pick(lib, 8, 1, 1, nbytes, coll=coll)[0] == "nvls"
+        assert _pick(lib, 8, 1, 1, 1 << 20, coll=coll, algos=b"ring")[0] == "ring"
+        assert _pick(lib, 8, 1, 1, 1 << 20, coll=coll, algos=b"tree")[0] == "tree"
 
 
 def test_mem_pool(lib):
