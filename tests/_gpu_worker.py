@@ -228,29 +228,35 @@ def forced_ring_tree():
         mk = (lambda m: comm.empty(m, dtype)) if sym else (lambda m: torch.empty(m, device=DEV, dtype=dtype))
         x = gen(RANK, n, dtype)
         for algo in ("ring", "tree"):
+            # by default the native pairs (ring: all-gather / reduce-scatter, tree: broadcast / reduce); "composed"
+            # adds the forms built from a partial phase plus a scatter or a collect
+            sharded = algo == "ring" or ARGS.get("composed", False)
+            rooted = algo == "tree" or ARGS.get("composed", False)
             with mccl.forced_algo(algo):
-                s = mk(n); s.copy_(x); g = mk(n * WORLD)
-                comm.all_gather(s, g); torch.cuda.synchronize()
-                assert torch.equal(g, torch.cat([gen(r, n, dtype) for r in range(WORLD)])), (algo, "allgather", dtype, n, sym, comm.last_algo)
-                s2 = mk(n * WORLD); s2.copy_(gen(RANK + 50, n * WORLD, dtype)); keep = s2.clone(); o2 = mk(n)
-                comm.reduce_scatter(s2, o2, op="avg"); torch.cuda.synchronize()
-                assert torch.equal(s2, keep), "reduce-scatter must not modify its input"
-                ref = oracle(n * WORLD, dtype, "avg", 50)[RANK * n:(RANK + 1) * n]
-                err = ((o2.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
-                assert err < ftol(dtype), (algo, "reducescatter", dtype, n, sym, err)
-                for root in {0, WORLD - 1}:
-                    b = mk(n); b.zero_()
-                    if RANK == root:
-                        b.copy_(x)
-                    comm.broadcast(b if RANK == root else None, b, root=root); torch.cuda.synchronize()
-                    assert torch.equal(b, gen(root, n, dtype)), (algo, "broadcast", dtype, n, sym, root, comm.last_algo)
-                    s3 = mk(n); s3.copy_(x); o3 = mk(n)
-                    comm.reduce(s3, o3, op="sum", root=root); torch.cuda.synchronize()
-                    assert torch.equal(s3, x), "reduce must not modify its input"
-                    if RANK == root:
-                        ref = oracle(n, dtype, "sum")
-                        err = ((o3.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
-                        assert err < ftol(dtype), (algo, "reduce", dtype, n, sym, root, err)
+                if sharded:
+                    s = mk(n); s.copy_(x); g = mk(n * WORLD)
+                    comm.all_gather(s, g); torch.cuda.synchronize()
+                    assert torch.equal(g, torch.cat([gen(r, n, dtype) for r in range(WORLD)])), (algo, "allgather", dtype, n, sym, comm.last_algo)
+                    s2 = mk(n * WORLD); s2.copy_(gen(RANK + 50, n * WORLD, dtype)); keep = s2.clone(); o2 = mk(n)
+                    comm.reduce_scatter(s2, o2, op="avg"); torch.cuda.synchronize()
+                    assert torch.equal(s2, keep), "reduce-scatter must not modify its input"
+                    ref = oracle(n * WORLD, dtype, "avg", 50)[RANK * n:(RANK + 1) * n]
+                    err = ((o2.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
+                    assert err < ftol(dtype), (algo, "reducescatter", dtype, n, sym, err)
+                if rooted:
+                    for root in {0, WORLD - 1}:
+                        b = mk(n); b.zero_()
+                        if RANK == root:
+                            b.copy_(x)
+                        comm.broadcast(b if RANK == root else None, b, root=root); torch.cuda.synchronize()
+                        assert torch.equal(b, gen(root, n, dtype)), (algo, "broadcast", dtype, n, sym, root, comm.last_algo)
+                        s3 = mk(n); s3.copy_(x); o3 = mk(n)
+                        comm.reduce(s3, o3, op="sum", root=root); torch.cuda.synchronize()
+                        assert torch.equal(s3, x), "reduce must not modify its input"
+                        if RANK == root:
+                            ref = oracle(n, dtype, "sum")
+                            err = ((o3.double() - ref).abs() / (ref.abs() + 1.0)).max().item()
+                            assert err < ftol(dtype), (algo, "reduce", dtype, n, sym, root, err)
         assert canary_ok(comm)
     comm.finalize(); comm.destroy()
 
