@@ -60,6 +60,7 @@ def main() -> int:
     ap.add_argument("--elems", type=int, default=0)
     ap.add_argument("--mbytes", type=int, default=512)
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--two-sm", action="store_true", help="gemm: the form in which pairs of SMs share a 256-row tile")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
@@ -70,9 +71,9 @@ def main() -> int:
         x = torch.randn(args.m, args.k, device=dev).to(torch.bfloat16)
         w = (torch.randn(args.n, args.k, device=dev) * 0.02).to(torch.bfloat16)
         y = torch.empty(args.m, args.n, device=dev, dtype=torch.bfloat16)
-        ms = timed(lambda: G.gemm(x, w, out=y, epilogue="silu"), args.launches)
+        ms = timed(lambda: G.gemm(x, w, out=y, epilogue="silu", two_sm=args.two_sm), args.launches)
         fl = 2.0 * args.m * args.n * args.k
-        out.update({"shape": [args.m, args.n, args.k], "us": round(ms * 1e3, 1), "tflops": round(fl / ms / 1e9, 1),
+        out.update({"shape": [args.m, args.n, args.k], "two_sm": args.two_sm, "us": round(ms * 1e3, 1), "tflops": round(fl / ms / 1e9, 1),
                     "frac_of_cublas_peak": round(fl / ms / 1e9 / tflops, 3), "kernel_error": G.last_error()})
     elif args.case == "adamw":
         from mccl_b200.ops.optim import fused_adamw_

@@ -127,6 +127,83 @@ __host__ __device__ __forceinline__ void tileCoords(int t, int tilesN, int panel
   *stripe = block * stripesPerBlock + inBlock;
 }
 
+// The communication warps (threads 256..383, named barrier 2) of the fused modes; `stripesPerBlock` counts
+// 128-row stripes of one rank's row block.
+template <int MODE>
+__device__ __forceinline__ void commWarps(const GemmArgs& a, volatile int* sFail, int n, int rank, int stripesPerBlock) {
+  const int ct = threadIdx.x - 256;
+  const DevPeers& P = a.peers;
+  CtrlFlags* mine = flagsOf(P, P.rank);
+  uint64_t epoch = mine->epoch[blockIdx.x];
+  bool ok = commBarrier(P, epoch, sFail, ct);              // peers' inputs exist, their buffers are free
+  const int G = gridDim.x, cta = blockIdx.x;
+  if (MODE == MODE_AG && ok) {
+    const uint64_t shardBytes = (uint64_t)(a.M / n) * a.K * 2, V = shardBytes / 16;
+    const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
+    for (int i = 0; i < n; ++i) {
+      const int s = (rank + i) % n;
+      const char* src = a.xPeer[s];
+      char* dst = a.xFull + (uint64_t)s * shardBytes;
+      if (src != dst) copyVecs(src, dst, lo, hi, ct, kCommThreads);
+      if (namedBarrierOr(2, kCommThreads, *sFail != 0)) break;
+      if (ct == 0) { __threadfence(); atomicAdd(reinterpret_cast<unsigned long long*>(&a.shardReady[s]), 1ull); }
+    }
+  }
+  if (MODE == MODE_RS && ok) {
+    // Partials for this rank's row block arrive in a fixed order: rank-1 computes the block first, then
+    // rank-2, ..., and the own GEMM last.  Each arrival is folded into an fp32 running sum as soon as its
+    // stripe flag is up, so the NVLink reads spread over the whole GEMM and only the last fold (own
+    // partial, local) remains at the end.  The fold order is the same on every run.
+    const uint64_t stripeBytes = (uint64_t)BM * a.N * 2, V = stripeBytes / 16;
+    const uint64_t* ready = a.tileReadyPeer[rank];
+    bool failed = false;
+    for (int ord = 0; ord < n && !failed; ++ord) {
+      const int src = (ord == n - 1) ? rank : (rank - 1 - ord + 2 * n) % n;
+      for (int lt = 0; lt < stripesPerBlock; ++lt) {
+        if (ct == 0 && !waitFlag(&ready[(size_t)src * stripesPerBlock + lt], a.callIndex, P, 2u, src, lt)) *sFail = 1;
+        if (namedBarrierOr(2, kCommThreads, *sFail != 0)) { failed = true; break; }
+        const char* part = a.partialPeer[src] + ((uint64_t)rank * stripesPerBlock + lt) * stripeBytes;
+        float4* acc4 = reinterpret_cast<float4*>(a.accum) + (uint64_t)lt * V * 2;
+        char* dst = reinterpret_cast<char*>(a.out) + (uint64_t)lt * stripeBytes;
+        // Eight remote vectors in flight per thread: with one, the 148 x 128 communication threads keep
+        // only 0.3 MB on the wire and the pull runs at a tenth of the link rate.
+        constexpr int U = 8;
+        forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
+          for (uint64_t i = lo + ct; i < hi; i += (uint64_t)U * kCommThreads) {
+            uint4 pv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint64_t idx = i + (uint64_t)u * kCommThreads;
+              if (idx < hi) pv[u] = ldSys128(part + idx * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint64_t idx = i + (uint64_t)u * kCommThreads;
+              if (idx >= hi) continue;
+              float acc[8];
+              accInit<__nv_bfloat16>(acc, pv[u]);
+              if (ord > 0) {
+                const float4 x = acc4[2 * idx], y = acc4[2 * idx + 1];
+                acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+                acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+              }
+              if (ord == n - 1) {
+                stLocal128(dst + idx * 16, accFinish<__nv_bfloat16>(acc, 1));
+              } else {
+                acc4[2 * idx] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                acc4[2 * idx + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+              }
+            }
+          }
+        });
+      }
+    }
+  }
+  if (!namedBarrierOr(2, kCommThreads, !ok || *sFail != 0)) commBarrier(P, epoch, sFail, ct);   // nobody still reads this rank's buffers
+  if (ct == 0) mine->epoch[blockIdx.x] = epoch;
+  if (*sFail && ct == 0) atomicCAS(a.errFlag, 0, 15);
+}
+
 template <int BN, int MODE>
 __global__ void __launch_bounds__(kThreadsGemm, 1) tpGemmKernel(const __grid_constant__ GemmArgs a) {
   using S = Smem<BN>;
@@ -256,78 +333,7 @@ __global__ void __launch_bounds__(kThreadsGemm, 1) tpGemmKernel(const __grid_con
       }
     }
   } else if (warp >= 8 && MODE != MODE_PLAIN) {
-    // ---------------- communication warps
-    const int ct = threadIdx.x - 256;
-    const DevPeers& P = a.peers;
-    CtrlFlags* mine = flagsOf(P, P.rank);
-    uint64_t epoch = mine->epoch[blockIdx.x];
-    bool ok = commBarrier(P, epoch, sFail, ct);              // peers' inputs exist, their buffers are free
-    const int G = gridDim.x, cta = blockIdx.x;
-    if (MODE == MODE_AG && ok) {
-      const uint64_t shardBytes = (uint64_t)(a.M / n) * a.K * 2, V = shardBytes / 16;
-      const uint64_t lo = sliceLo(V, G, cta), hi = sliceLo(V, G, cta + 1);
-      for (int i = 0; i < n; ++i) {
-        const int s = (rank + i) % n;
-        const char* src = a.xPeer[s];
-        char* dst = a.xFull + (uint64_t)s * shardBytes;
-        if (src != dst) copyVecs(src, dst, lo, hi, ct, kCommThreads);
-        if (namedBarrierOr(2, kCommThreads, *sFail != 0)) break;
-        if (ct == 0) { __threadfence(); atomicAdd(reinterpret_cast<unsigned long long*>(&a.shardReady[s]), 1ull); }
-      }
-    }
-    if (MODE == MODE_RS && ok) {
-      // Partials for this rank's row block arrive in a fixed order: rank-1 computes the block first, then
-      // rank-2, ..., and the own GEMM last.  Each arrival is folded into an fp32 running sum as soon as its
-      // stripe flag is up, so the NVLink reads spread over the whole GEMM and only the last fold (own
-      // partial, local) remains at the end.  The fold order is the same on every run.
-      const uint64_t stripeBytes = (uint64_t)BM * a.N * 2, V = stripeBytes / 16;
-      const uint64_t* ready = a.tileReadyPeer[rank];
-      bool failed = false;
-      for (int ord = 0; ord < n && !failed; ++ord) {
-        const int src = (ord == n - 1) ? rank : (rank - 1 - ord + 2 * n) % n;
-        for (int lt = 0; lt < stripesPerBlock; ++lt) {
-          if (ct == 0 && !waitFlag(&ready[(size_t)src * stripesPerBlock + lt], a.callIndex, P, 2u, src, lt)) *sFail = 1;
-          if (namedBarrierOr(2, kCommThreads, *sFail != 0)) { failed = true; break; }
-          const char* part = a.partialPeer[src] + ((uint64_t)rank * stripesPerBlock + lt) * stripeBytes;
-          float4* acc4 = reinterpret_cast<float4*>(a.accum) + (uint64_t)lt * V * 2;
-          char* dst = reinterpret_cast<char*>(a.out) + (uint64_t)lt * stripeBytes;
-          // Eight remote vectors in flight per thread: with one, the 148 x 128 communication threads keep
-          // only 0.3 MB on the wire and the pull runs at a tenth of the link rate.
-          constexpr int U = 8;
-          forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
-            for (uint64_t i = lo + ct; i < hi; i += (uint64_t)U * kCommThreads) {
-              uint4 pv[U];
-#pragma unroll
-              for (int u = 0; u < U; ++u) {
-                const uint64_t idx = i + (uint64_t)u * kCommThreads;
-                if (idx < hi) pv[u] = ldSys128(part + idx * 16);
-              }
-#pragma unroll
-              for (int u = 0; u < U; ++u) {
-                const uint64_t idx = i + (uint64_t)u * kCommThreads;
-                if (idx >= hi) continue;
-                float acc[8];
-                accInit<__nv_bfloat16>(acc, pv[u]);
-                if (ord > 0) {
-                  const float4 x = acc4[2 * idx], y = acc4[2 * idx + 1];
-                  acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-                  acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
-                }
-                if (ord == n - 1) {
-                  stLocal128(dst + idx * 16, accFinish<__nv_bfloat16>(acc, 1));
-                } else {
-                  acc4[2 * idx] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                  acc4[2 * idx + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-                }
-              }
-            }
-          });
-        }
-      }
-    }
-    if (!namedBarrierOr(2, kCommThreads, !ok || *sFail != 0)) commBarrier(P, epoch, sFail, ct);   // nobody still reads this rank's buffers
-    if (ct == 0) mine->epoch[blockIdx.x] = epoch;
-    if (*sFail && ct == 0) atomicCAS(a.errFlag, 0, 15);
+    commWarps<MODE>(a, sFail, n, rank, stripesPerBlock);
   }
 
   umma::tcFenceBefore();

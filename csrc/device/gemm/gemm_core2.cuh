@@ -1,0 +1,233 @@
+// Two-SM form of the bf16 GEMM: a cluster of two CTAs works on one 256 x BN output tile with
+// tcgen05.mma.cta_group::2 (M = 256).  Each CTA stages its own 128 rows of A and its own half of the B tile
+// (BN/2 rows), so a pair moves half the B bytes through shared memory per FLOP that two independent CTAs
+// would, and the stage is small enough for a six-deep ring.
+//
+//   CTA 0 of the pair ("leader")            CTA 1
+//   warp 0  TMA: A rows [0,128), B rows      TMA: A rows [128,256), B rows [BN/2, BN) of the tile; all four
+//           [0, BN/2) of the tile             loads of a stage complete on the LEADER's full barrier
+//   warp 1  issues the MMAs for both CTAs,   idle
+//           commits to the empty / tmemFull
+//           barriers of both CTAs
+//   warp 2  allocates / frees tensor memory (cta_group::2: one warp of each CTA takes part)
+//   warps 4-7 epilogue of the CTA's own 128 rows; both CTAs release the accumulator on the leader's barrier
+//
+// TMA loads carry no cluster multicast: each CTA fetches what it needs itself.  Every wait is bounded, as in
+// the one-SM kernel; a CTA that gives up leaves its loops, and its partner then runs into its own time limit
+// before both meet at the closing cluster barrier.  No counterpart in the reference.
+#pragma once
+
+#include "gemm_core.cuh"
+
+namespace mccl {
+namespace gemm {
+
+constexpr int BM2 = 256;               // rows of a pair's tile
+constexpr int kThreadsGemm2 = 256;
+
+template <int BN> struct Smem2 {
+  static constexpr int A_BYTES = BM * BK * 2;              // this CTA's 128 rows
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;        // this CTA's half of the B tile
+  static constexpr int STAGES = (A_BYTES + B_BYTES) * 8 <= 200 * 1024 ? 8 : 6;
+  static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int TOTAL = TILE_BYTES + 512 + 1024;    // barriers + alignment slack
+};
+
+namespace umma2 {
+
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of `localAddr` (a shared::cta address) in the shared memory of CTA `cta` of this cluster.
+__device__ __forceinline__ uint32_t mapToCta(uint32_t localAddr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(localAddr), "r"(cta));
+  return r;
+}
+// Barrier over all threads of both CTAs (the form that does not require converged warps).
+__device__ __forceinline__ void clusterSync() {
+  asm volatile("barrier.cluster.arrive.release;\n barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Arrive on a barrier that may live in the partner CTA (shared::cluster address).
+__device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(clusterAddr) : "memory");
+}
+// 2-D tiled load into this CTA's shared memory whose completion bytes are counted on a barrier of either CTA
+// of the pair (shared::cluster address).  No multicast.
+__device__ __forceinline__ void tmaLoad2dPair(void* smemDst, const CUtensorMap* map, uint32_t barClusterAddr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :: "r"(umma::smemAddr(smemDst)), "l"(map), "r"(barClusterAddr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmemAlloc(uint32_t* smemSlot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(umma::smemAddr(smemSlot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmemRelinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmemDealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
+}
+// D (128 lanes in each CTA's tensor memory) (+)= A (128 rows from each CTA) * B (BN/2 rows from each CTA).
+__device__ __forceinline__ void mmaBf16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+      :: "r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive on the barrier at this offset in both CTAs once every MMA issued so far has completed.
+__device__ __forceinline__ void mmaCommitBoth(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               :: "r"(umma::smemAddr(bar)), "h"(mask) : "memory");
+}
+
+}  // namespace umma2
+
+// Launched as clusters of two CTAs (cluster dimension attribute of the launch).  Threads: 256 in the plain
+// mode, 384 (communication warps 8-11) in the fused modes.
+template <int BN, int MODE>
+__global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsGemm, 1) tpGemm2Kernel(const __grid_constant__ GemmArgs a) {
+  using S = Smem2<BN>;
+  constexpr int STAGES2 = S::STAGES;
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES2 * S::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::TILE_BYTES);
+  uint64_t* full = bars;                          // [STAGES2] used in the leader: all four loads of a stage
+  uint64_t* empty = bars + STAGES2;               // [STAGES2] in each CTA: the MMAs have read the stage
+  uint64_t* tmemFull = bars + 2 * STAGES2;        // [2] in each CTA: accumulator complete
+  uint64_t* tmemEmpty = bars + 2 * STAGES2 + 2;   // [2] used in the leader: both epilogues have drained it
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
+  volatile int* sFail = reinterpret_cast<volatile int*>(tmemSlot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ctaRank = umma2::clusterCtaRank();
+  const int pair = blockIdx.x >> 1, numPairs = gridDim.x >> 1;
+  const int tilesN = a.N / BN, stripes = a.M / BM2, kBlocks = a.K / BK;     // stripes of 256 rows
+  const int totalTiles = tilesN * stripes;
+  const int n = (MODE == MODE_PLAIN) ? 1 : a.peers.n, rank = (MODE == MODE_PLAIN) ? 0 : a.peers.rank;
+  const int stripesPerBlock = stripes / n;          // 256-row stripes of one rank's row block
+  const uint64_t budget = a.budgetNs;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) { umma::mbarInit(&full[s], 1); umma::mbarInit(&empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { umma::mbarInit(&tmemFull[i], 1); umma::mbarInit(&tmemEmpty[i], 8); }
+    *sFail = 0;
+    umma::fenceBarrierInit();
+    umma::prefetchTensorMap(&a.mapA);
+    umma::prefetchTensorMap(&a.mapB);
+  }
+  if (warp == 2) { umma2::tmemAlloc(tmemSlot, kTmemCols); umma2::tmemRelinquish(); }
+  umma::tcFenceBefore();
+  __syncthreads();
+  umma2::clusterSync();                            // both CTAs' barriers exist before anything signals them
+  umma::tcFenceAfter();
+  const uint32_t tmemBase = *tmemSlot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer (both CTAs)
+    int stage = 0; uint32_t phase = 0;
+    for (int t = pair; t < totalTiles && *sFail == 0; t += numPairs) {
+      int stripe, nt;
+      tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
+      if (MODE == MODE_AG) {
+        const int shard = stripe / stripesPerBlock;
+        if (!waitGpuFlag(&a.shardReady[shard], (uint64_t)gridDim.x, budget)) { *sFail = 1; atomicExch(a.errFlag, 20); break; }
+        umma::fenceProxyAsyncGlobal();
+      }
+      for (int kb = 0; kb < kBlocks; ++kb) {
+        if (!umma::mbarWait(&empty[stage], phase ^ 1, budget)) { *sFail = 1; atomicExch(a.errFlag, 21); break; }
+        if (ctaRank == 0) umma::mbarExpectTx(&full[stage], 2 * (S::A_BYTES + S::B_BYTES));
+        const uint32_t leaderFull = umma2::mapToCta(umma::smemAddr(&full[stage]), 0);
+        umma2::tmaLoad2dPair(sA + stage * S::A_BYTES, &a.mapA, leaderFull, kb * BK, stripe * BM2 + (int)ctaRank * BM);
+        umma2::tmaLoad2dPair(sB + stage * S::B_BYTES, &a.mapB, leaderFull, kb * BK, nt * BN + (int)ctaRank * (BN / 2));
+        if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1 && lane == 0 && ctaRank == 0) {
+    // ---------------- MMA issuer (leader only)
+    constexpr uint32_t idesc = umma::instrDescBf16(BM2, BN);
+    int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t accPhase = 0;
+    for (int t = pair; t < totalTiles && *sFail == 0; t += numPairs) {
+      if (!umma::mbarWait(&tmemEmpty[acc], accPhase ^ 1, budget)) { *sFail = 1; atomicExch(a.errFlag, 22); break; }
+      umma::tcFenceAfter();
+      const uint32_t d = tmemBase + (uint32_t)acc * 256u;
+      for (int kb = 0; kb < kBlocks; ++kb) {
+        if (!umma::mbarWait(&full[stage], phase, budget)) { *sFail = 1; atomicExch(a.errFlag, 23); break; }
+        umma::tcFenceAfter();
+        const uint64_t da = umma::smemDescSw128(sA + stage * S::A_BYTES), db = umma::smemDescSw128(sB + stage * S::B_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma2::mmaBf16(d, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb | k) != 0);
+        umma2::mmaCommitBoth(&empty[stage]);
+        if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+      }
+      if (*sFail) break;
+      umma2::mmaCommitBoth(&tmemFull[acc]);
+      acc ^= 1; if (acc == 0) accPhase ^= 1;
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ---------------- epilogue (both CTAs, own 128 rows)
+    const int q = warp - 4;
+    int acc = 0; uint32_t accPhase = 0;
+    for (int t = pair; t < totalTiles; t += numPairs) {
+      int stripe, nt;
+      tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
+      bool good = *sFail == 0 && umma::mbarWait(&tmemFull[acc], accPhase, budget);
+      if (!good && *sFail == 0) { *sFail = 1; atomicExch(a.errFlag, 24); }
+      if (MODE == MODE_RS) good = !namedBarrierOr(1, 128, !good);     // the four warps meet at a barrier below
+      if (!good) break;
+      umma::tcFenceAfter();
+      const int stripe128 = stripe * 2 + (int)ctaRank;                 // this CTA's 128 rows of the pair's tile
+      const size_t row = (size_t)stripe128 * BM + q * 32 + lane;
+      __nv_bfloat16* dstRow = a.C + row * (size_t)a.N + (size_t)nt * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        umma::tmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u + (uint32_t)c * 32u, v);
+        umma::tmemLoadWait();
+        uint4 outv[4];
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(outv);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+          if (a.epilogue == EPI_SILU) { x0 = silu(x0); x1 = silu(x1); }
+          o2[j] = __floats2bfloat162_rn(x0, x1);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(dstRow + c * 32);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[j] = outv[j];
+      }
+      umma::tcFenceBefore();
+      __syncwarp();
+      if (lane == 0) umma2::mbarArriveCluster(umma2::mapToCta(umma::smemAddr(&tmemEmpty[acc]), 0));
+      acc ^= 1; if (acc == 0) accPhase ^= 1;
+      if (MODE == MODE_RS) {
+        // Count the tile towards its 128-row stripe; tell the owner of the row block when the stripe is whole.
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 4 && lane == 0) {
+          __threadfence_system();
+          const unsigned long long doneNow = atomicAdd(reinterpret_cast<unsigned long long*>(&a.stripeCount[stripe128]), 1ull) + 1ull;
+          if (doneNow == (uint64_t)tilesN) {
+            const int per128 = 2 * stripesPerBlock;
+            const int owner = stripe128 / per128, within = stripe128 - owner * per128;
+            __threadfence_system();
+            stReleaseSys(&a.tileReadyPeer[owner][(size_t)rank * per128 + within], a.callIndex);
+          }
+        }
+      }
+    }
+  } else if (warp >= 8 && MODE != MODE_PLAIN) {
+    commWarps<MODE>(a, sFail, n, rank, 2 * stripesPerBlock);
+  }
+
+  umma::tcFenceBefore();
+  __syncthreads();
+  umma2::clusterSync();                            // neither CTA frees tensor memory the other still uses
+  if (warp == 2) umma2::tmemDealloc(tmemBase, kTmemCols);
+}
+
+}  // namespace gemm
+}  // namespace mccl

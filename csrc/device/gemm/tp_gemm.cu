@@ -7,6 +7,7 @@
 #include "../../comm/comm.h"
 #include "../../transport/cuda_mem.h"
 #include "gemm_core.cuh"
+#include "gemm_core2.cuh"
 
 using namespace mccl;
 using namespace mccl::gemm;
@@ -102,6 +103,69 @@ mcclResult_t launchMode(const GemmArgs& a, int bn, int grid, cudaStream_t s) {
   return cudaGetLastError() == cudaSuccess ? mcclSuccess : mcclSystemError;
 }
 
+int smCount() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+// ---- two-SM kernel: clusters of two CTAs ------------------------------------------------------------------------
+bool twoSmWanted() {
+  static const bool on = envInt("MCCL_GEMM_2SM", 0) != 0;     // off until the two-SM kernels have been timed
+  return on;
+}
+
+template <int MODE>
+bool pairKernel(int bn, const void** fn, int* smem) {
+#define MCCL_GEMM2_CASE(BN_) case BN_: *fn = reinterpret_cast<const void*>(&tpGemm2Kernel<BN_, MODE>); *smem = Smem2<BN_>::TOTAL; return true;
+  switch (bn) {
+    MCCL_GEMM2_CASE(256) MCCL_GEMM2_CASE(224) MCCL_GEMM2_CASE(192) MCCL_GEMM2_CASE(160) MCCL_GEMM2_CASE(128) MCCL_GEMM2_CASE(96)
+    MCCL_GEMM2_CASE(64)
+    default: return false;
+  }
+#undef MCCL_GEMM2_CASE
+}
+
+void pairConfig(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int pairs, int threads, int smem, cudaStream_t s) {
+  *cfg = cudaLaunchConfig_t{};
+  cfg->gridDim = dim3(2 * pairs, 1, 1);
+  cfg->blockDim = dim3(threads, 1, 1);
+  cfg->dynamicSmemBytes = smem;
+  cfg->stream = s;
+  attr->id = cudaLaunchAttributeClusterDimension;
+  attr->val.clusterDim.x = 2; attr->val.clusterDim.y = 1; attr->val.clusterDim.z = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+}
+
+mcclResult_t pairPrepare(const void* fn, int smem) {
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) { cudaGetLastError(); return mcclSystemError; }
+  return mcclSuccess;
+}
+
+// Clusters of two that can be resident at once (the fused modes need every CTA of the grid running).
+int residentPairs(const void* fn, int threads, int smem) {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr;
+  pairConfig(&cfg, &attr, smCount() / 2, threads, smem, nullptr);
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
+mcclResult_t launchPairs(const void* fn, int threads, int smem, int pairs, const GemmArgs& a, cudaStream_t s) {
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr;
+  pairConfig(&cfg, &attr, pairs, threads, smem, s);
+  void* args[1] = {const_cast<GemmArgs*>(&a)};
+  if (cudaLaunchKernelExC(&cfg, fn, args) != cudaSuccess) {
+    MCCL_WARN("launch of the two-SM GEMM failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return mcclSystemError;
+  }
+  return mcclSuccess;
+}
+
 mcclResult_t checkShapes(int M, int N, int K, int nRanks) {
   if (M <= 0 || N <= 0 || K <= 0 || M % (BM * nRanks) || K % BK || N % 64) {
     MCCL_WARN("tcgen05 GEMM needs M %% %d == 0, N %% 64 == 0, K %% 64 == 0 (got %d x %d x %d)", BM * nRanks, M, N, K);
@@ -114,13 +178,6 @@ mcclResult_t checkShapes(int M, int N, int K, int nRanks) {
 int pickPanel(int stripesPerBlock) {
   for (int p = 8; p > 1; --p) if (stripesPerBlock % p == 0) return p;
   return 1;
-}
-
-int smCount() {
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return sms;
 }
 
 }  // namespace
@@ -177,6 +234,37 @@ mcclResult_t mcclTpGemm(const void* A, const void* B, void* C, int M, int N, int
   return launchMode<MODE_PLAIN>(a, bn, tiles < sms ? tiles : sms, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// The same product computed by pairs of SMs (tcgen05.mma.cta_group::2 on 256-row tiles); needs M % 256 == 0.
+mcclResult_t mcclTpGemm2(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int maxCtas, mcclStream_t stream) {
+  if (A == nullptr || B == nullptr || C == nullptr) return mcclInvalidArgument;
+  MCCLCHECK(checkShapes(M, N, K, 1));
+  if (M % BM2) {
+    MCCL_WARN("the two-SM GEMM needs M %% %d == 0 (got %d)", BM2, M);
+    return mcclInvalidArgument;
+  }
+  const int pairsMax = std::max(1, (maxCtas > 0 ? maxCtas : smCount()) / 2);
+  const int bn = pickBN(M / 2, N, pairsMax);          // M / 2: pickBN counts 128-row stripes, a pair takes 256 rows
+  const void* fn = nullptr;
+  int smem = 0;
+  if (bn == 0 || !pairKernel<MODE_PLAIN>(bn, &fn, &smem)) return mcclInvalidArgument;
+  MCCLCHECK(pairPrepare(fn, smem));
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  MCCLCHECK(makeMap(&a.mapA, A, M, K, BM));
+  MCCLCHECK(makeMap(&a.mapB, B, N, K, bn / 2));
+  a.M = M; a.N = N; a.K = K;
+  a.C = static_cast<__nv_bfloat16*>(C);
+  a.epilogue = epilogue;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int* hostFlag = errFlagFor(dev);
+  if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
+  a.budgetNs = 2000000000ull;
+  a.panel = pickPanel(M / BM2);
+  const int tiles = (M / BM2) * (N / bn);
+  return launchPairs(fn, kThreadsGemm2, smem, tiles < pairsMax ? tiles : pairsMax, a, reinterpret_cast<cudaStream_t>(stream));
+}
+
 // Fused all-gather -> GEMM -> activation.  xShard: this rank's [M/n, K] activations in symmetric memory;
 // xFull: local [M, K] workspace; W: [N, K] local weight shard; out: [M, N]; flags: >= 16 uint64 of device
 // memory (zeroed by this call).  Collective over `comm`.
@@ -194,13 +282,30 @@ mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFul
     MCCL_WARN("mcclTpAllGatherGemm: the activation shard must live in symmetric memory (mcclMemAlloc)");
     return mcclInvalidArgument;
   }
-  const int sms = std::min(smCount(), MCCL_MAX_CTAS);
-  const int bn = pickBN(M, N, sms);
-  if (bn == 0) return mcclInvalidArgument;
+  // Two-SM form: every rank must take the same branch, which it does because the decision depends on the
+  // shape, an environment variable and the GPU model only.
+  const bool two = twoSmWanted() && (M / n) % BM2 == 0;
+  const void* fn2 = nullptr;
+  int smem2 = 0, pairs = 0;
+  int sms = std::min(smCount(), MCCL_MAX_CTAS);
+  int bn = 0;
+  if (two) {
+    bn = pickBN(M / 2, N, sms / 2);
+    if (bn == 0 || !pairKernel<MODE_AG>(bn, &fn2, &smem2)) return mcclInvalidArgument;
+    MCCLCHECK(pairPrepare(fn2, smem2));
+    pairs = std::min(residentPairs(fn2, kThreadsGemm, smem2), sms / 2);
+    if (pairs <= 0) return mcclSystemError;
+    if (pairs != sms / 2) bn = pickBN(M / 2, N, pairs);
+    if (bn == 0 || !pairKernel<MODE_AG>(bn, &fn2, &smem2)) return mcclInvalidArgument;
+    MCCLCHECK(pairPrepare(fn2, smem2));
+  } else {
+    bn = pickBN(M, N, sms);
+    if (bn == 0) return mcclInvalidArgument;
+  }
   GemmArgs a;
   memset(&a, 0, sizeof(a));
   MCCLCHECK(makeMap(&a.mapA, xFull, M, K, BM));
-  MCCLCHECK(makeMap(&a.mapB, W, N, K, bn));
+  MCCLCHECK(makeMap(&a.mapB, W, N, K, two ? bn / 2 : bn));
   a.M = M; a.N = N; a.K = K;
   a.C = static_cast<__nv_bfloat16*>(out);
   a.epilogue = epilogue;
@@ -209,17 +314,22 @@ mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFul
   a.peers = comm->cu->peers;
   a.budgetNs = 2 * a.peers.timeoutNs;
   a.callIndex = 1;
-  a.panel = pickPanel(M / BM / n);
+  a.panel = pickPanel(M / (two ? BM2 : BM) / n);
   a.shardReady = static_cast<uint64_t*>(flags);
   const size_t off = (size_t)(static_cast<const char*>(xShard) - seg->local);
   for (int p = 0; p < n; ++p) a.xPeer[p] = seg->peer[p] + off;
   a.xFull = static_cast<char*>(xFull);
   CUDACHECK(cudaMemsetAsync(flags, 0, MCCL_MAX_RANKS * sizeof(uint64_t), s));
-  const int tiles = (M / BM) * (N / bn);
   // Every CTA's communication warps take part in the copy and in the cross-GPU barriers, so the grid is
   // the same on every rank and never larger than what is resident at once.
-  const int grid = tiles < sms ? tiles : sms;
-  mcclResult_t rc = launchMode<MODE_AG>(a, bn, grid, s);
+  mcclResult_t rc;
+  if (two) {
+    const int tiles = (M / BM2) * (N / bn);
+    rc = launchPairs(fn2, kThreadsGemm, smem2, tiles < pairs ? tiles : pairs, a, s);
+  } else {
+    const int tiles = (M / BM) * (N / bn);
+    rc = launchMode<MODE_AG>(a, bn, tiles < sms ? tiles : sms, s);
+  }
   if (rc == mcclSuccess) comm->launches.fetch_add(1);
   return rc;
 }
@@ -244,13 +354,28 @@ mcclResult_t mcclTpGemmReduceScatter(mcclComm_t comm, const void* H, const void*
     MCCL_WARN("mcclTpGemmReduceScatter: staging and flags must live in symmetric memory (mcclMemAlloc)");
     return mcclInvalidArgument;
   }
-  const int sms = std::min(smCount(), MCCL_MAX_CTAS);
-  const int bn = pickBN(M, N, sms);
-  if (bn == 0) return mcclInvalidArgument;
+  const bool two = twoSmWanted() && (M / n) % BM2 == 0;
+  const void* fn2 = nullptr;
+  int smem2 = 0, pairs = 0;
+  int sms = std::min(smCount(), MCCL_MAX_CTAS);
+  int bn = 0;
+  if (two) {
+    bn = pickBN(M / 2, N, sms / 2);
+    if (bn == 0 || !pairKernel<MODE_RS>(bn, &fn2, &smem2)) return mcclInvalidArgument;
+    MCCLCHECK(pairPrepare(fn2, smem2));
+    pairs = std::min(residentPairs(fn2, kThreadsGemm, smem2), sms / 2);
+    if (pairs <= 0) return mcclSystemError;
+    if (pairs != sms / 2) bn = pickBN(M / 2, N, pairs);
+    if (bn == 0 || !pairKernel<MODE_RS>(bn, &fn2, &smem2)) return mcclInvalidArgument;
+    MCCLCHECK(pairPrepare(fn2, smem2));
+  } else {
+    bn = pickBN(M, N, sms);
+    if (bn == 0) return mcclInvalidArgument;
+  }
   GemmArgs a;
   memset(&a, 0, sizeof(a));
   MCCLCHECK(makeMap(&a.mapA, H, M, K, BM));
-  MCCLCHECK(makeMap(&a.mapB, W, N, K, bn));
+  MCCLCHECK(makeMap(&a.mapB, W, N, K, two ? bn / 2 : bn));
   a.M = M; a.N = N; a.K = K;
   a.C = static_cast<__nv_bfloat16*>(partial);
   a.epilogue = EPI_NONE;
@@ -268,11 +393,16 @@ mcclResult_t mcclTpGemmReduceScatter(mcclComm_t comm, const void* H, const void*
   }
   a.out = static_cast<__nv_bfloat16*>(out);
   a.accum = accum;
-  a.panel = pickPanel(stripesPerBlock);
+  a.panel = pickPanel(two ? stripesPerBlock / 2 : stripesPerBlock);
   CUDACHECK(cudaMemsetAsync(a.stripeCount, 0, (size_t)stripes * sizeof(uint64_t), s));   // local counters only
-  const int tiles = (M / BM) * (N / bn);
-  const int grid = tiles < sms ? tiles : sms;
-  mcclResult_t rc = launchMode<MODE_RS>(a, bn, grid, s);
+  mcclResult_t rc;
+  if (two) {
+    const int tiles = (M / BM2) * (N / bn);
+    rc = launchPairs(fn2, kThreadsGemm, smem2, tiles < pairs ? tiles : pairs, a, s);
+  } else {
+    const int tiles = (M / BM) * (N / bn);
+    rc = launchMode<MODE_RS>(a, bn, tiles < sms ? tiles : sms, s);
+  }
   if (rc == mcclSuccess) comm->launches.fetch_add(1);
   return rc;
 }

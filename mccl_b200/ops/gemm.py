@@ -22,6 +22,8 @@ def _lib():
         vp, i = C.c_void_p, C.c_int
         lib.mcclTpGemm.restype = i
         lib.mcclTpGemm.argtypes = [vp, vp, vp, i, i, i, i, i, vp]
+        lib.mcclTpGemm2.restype = i
+        lib.mcclTpGemm2.argtypes = [vp, vp, vp, i, i, i, i, i, vp]
         lib.mcclTpAllGatherGemm.restype = i
         lib.mcclTpAllGatherGemm.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, vp]
         lib.mcclTpGemmReduceScatter.restype = i
@@ -41,8 +43,9 @@ def supported(M: int, N: int, K: int, ranks: int = 1) -> bool:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "none", max_ctas: int = 0,
-         stream=None) -> torch.Tensor:
-    """out[M, N] = act(x[M, K] @ w[N, K].T) in bf16 with fp32 accumulation, by the library's own tcgen05 kernel."""
+         stream=None, two_sm: bool = False) -> torch.Tensor:
+    """out[M, N] = act(x[M, K] @ w[N, K].T) in bf16 with fp32 accumulation, by the library's own tcgen05 kernel.
+    `two_sm` selects the form in which pairs of SMs share a 256-row tile (needs M % 256 == 0)."""
     if not x.is_cuda:
         raise RuntimeError("mccl gemm runs on CUDA (sm_100a) only")
     assert x.dtype == w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
@@ -53,8 +56,11 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epil
         raise ValueError(f"unsupported GEMM shape {M}x{N}x{K}: M % 128, N % 64 and K % 64 must be 0")
     if out is None:
         out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
-    L.check(_lib().mcclTpGemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, EPI[epilogue], max_ctas, _stream(x, stream)),
-            "mcclTpGemm")
+    if two_sm and M % 256:
+        raise ValueError(f"the two-SM GEMM needs M % 256 == 0 (got {M})")
+    fn = _lib().mcclTpGemm2 if two_sm else _lib().mcclTpGemm
+    L.check(fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, EPI[epilogue], max_ctas, _stream(x, stream)),
+            "mcclTpGemm2" if two_sm else "mcclTpGemm")
     _counter["launches"] += 1
     return out
 

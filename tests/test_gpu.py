@@ -13,6 +13,11 @@ NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
 need2 = pytest.mark.skipif(NGPU < 2, reason="needs two GPUs")
 
 
+# Paths written after the last session with GPUs: they run when MCCL_TEST_UNVERIFIED=1 until a run has confirmed them.
+unverified = pytest.mark.skipif(os.environ.get("MCCL_TEST_UNVERIFIED") != "1" or NGPU < 2,
+                                reason="not yet confirmed on GPUs: set MCCL_TEST_UNVERIFIED=1 (needs two GPUs)")
+
+
 def _require_cuda():
     if NGPU < 1:
         pytest.fail("GPU tests need a CUDA device (run the CPU tier with -m 'not gpu')")
@@ -158,6 +163,31 @@ def test_tcgen05_gemm_matches_fp32_reference():
             assert err < 1e-2, (M, N, K, epi, err)
     with pytest.raises(ValueError):
         G.gemm(torch.zeros(100, 64, device=dev, dtype=torch.bfloat16), torch.zeros(64, 64, device=dev, dtype=torch.bfloat16))
+
+
+@pytest.mark.skipif(os.environ.get("MCCL_TEST_UNVERIFIED") != "1", reason="not yet confirmed on a GPU: set MCCL_TEST_UNVERIFIED=1")
+def test_two_sm_gemm_matches_fp32_reference():
+    _require_cuda()
+    from mccl_b200.ops import gemm as G
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    for (M, N, K) in [(256, 64, 64), (256, 448, 192), (1024, 3584, 1024), (512, 8192, 3584), (8192, 256, 128)]:
+        x = (torch.randn(M, K, device=dev) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+        for epi in ("none", "silu"):
+            y = G.gemm(x, w, epilogue=epi, two_sm=True)
+            torch.cuda.synchronize()
+            assert G.last_error() == 0
+            ref = x.float() @ w.float().t()
+            if epi == "silu":
+                ref = torch.nn.functional.silu(ref)
+            err = ((y.float() - ref).abs() / (ref.abs() + 1.0)).max().item()
+            assert err < 1e-2, (M, N, K, epi, err)
+
+
+@unverified
+def test_fused_tp_ffn_two_sm_kernels():
+    assert_all_ok(run_ranks(2, "tp_ffn", worker="_gpu_worker.py", env={"MCCL_GEMM_2SM": "1"}, timeout=300))
 
 
 @need2
@@ -360,11 +390,6 @@ def test_emulated_ring_and_tree_phases():
 @need2
 def test_forced_ring_and_tree_for_other_collectives():
     assert_all_ok(run_ranks(min(NGPU, 4), "forced_ring_tree", worker="_gpu_worker.py", timeout=600))
-
-
-# Paths written after the last session with GPUs: they run when MCCL_TEST_UNVERIFIED=1 until a run has confirmed them.
-unverified = pytest.mark.skipif(os.environ.get("MCCL_TEST_UNVERIFIED") != "1" or NGPU < 2,
-                                reason="not yet confirmed on GPUs: set MCCL_TEST_UNVERIFIED=1 (needs two GPUs)")
 
 
 @unverified
