@@ -349,6 +349,36 @@ def rooted_spread():
     comm.finalize(); comm.destroy()
 
 
+def graph_capture():
+    """Collectives captured into a CUDA graph and replayed: every counter the kernels synchronise through lives in
+    device memory, so a replay is a new, valid call.  Small (one-shot), medium and large (NVLS / two-shot) sizes."""
+    comm = make_comm()
+    side = torch.cuda.Stream()
+    for n in (1 << 10, 1 << 18, 1 << 23):
+        x = comm.empty(n, torch.float32)
+        x.fill_(float(RANK + 1))
+        y = comm.empty(n * WORLD, torch.float32)
+        torch.cuda.synchronize(); comm.host_barrier()
+        with torch.cuda.stream(side):
+            comm.all_reduce(x, op="sum")                 # warm-up outside the capture
+        torch.cuda.synchronize(); comm.host_barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            comm.all_reduce(x, op="sum")
+            comm.all_gather(x, y)
+        total = WORLD * (WORLD + 1) // 2                  # after the warm-up every rank holds `total`
+        for replay in range(1, 4):
+            g.replay(); torch.cuda.synchronize()
+            want = float(total * WORLD ** replay)
+            assert torch.all(x == want), ("graph all_reduce", n, replay, x[:4].tolist(), want)
+            assert torch.all(y == want), ("graph all_gather", n, replay)
+        assert canary_ok(comm)
+        del g
+        for t in (x, y):
+            comm.free_raw(t.data_ptr())
+    comm.finalize(); comm.destroy()
+
+
 def calibrate_and_trace():
     """MCCL_CALIBRATE=1 measures pair bandwidth and empty-collective latency at init and feeds the tuner;
     MCCL_TRACE writes a Chrome trace with a device track."""

@@ -393,6 +393,11 @@ def test_forced_ring_and_tree_for_other_collectives():
 
 
 @unverified
+def test_collectives_replay_from_a_cuda_graph():
+    assert_all_ok(run_ranks(2, "graph_capture", worker="_gpu_worker.py", timeout=300))
+
+
+@unverified
 def test_composed_ring_and_tree_forms():
     assert_all_ok(run_ranks(min(NGPU, 4), "forced_ring_tree", worker="_gpu_worker.py", args={"composed": True}, timeout=900))
 
