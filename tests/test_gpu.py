@@ -13,7 +13,8 @@ NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
 need2 = pytest.mark.skipif(NGPU < 2, reason="needs two GPUs")
 
 
-# Paths written after the last session with GPUs: they run when MCCL_TEST_UNVERIFIED=1 until a run has confirmed them.
+# Paths that no run on GPUs has confirmed yet: their tests run only when MCCL_TEST_UNVERIFIED=1, so that an
+# unconfirmed path cannot stop the confirmed tier.
 unverified = pytest.mark.skipif(os.environ.get("MCCL_TEST_UNVERIFIED") != "1" or NGPU < 2,
                                 reason="not yet confirmed on GPUs: set MCCL_TEST_UNVERIFIED=1 (needs two GPUs)")
 
