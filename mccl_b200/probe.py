@@ -10,6 +10,9 @@ allocator, trees, connect, xml, utils, metal, init, m2m, bootstrap, discover, co
     python -m mccl_b200.probe comm                     # rank/world from MCCL_RANK / MCCL_WORLD_SIZE (or RANK / WORLD_SIZE)
     python -m mccl_b200.probe coll --op allreduce|allgather|reducescatter|broadcast|reduce|alltoall [--count N --root R]
     python -m mccl_b200.probe bw [--mbytes 256]        # measured pair bandwidth / empty-collective latency (cuda transport)
+    python -m mccl_b200.probe bootstrap                # control-plane all-gather of 1000 + rank
+    python -m mccl_b200.probe m2m [--bytes 8388608]    # striped TCP transfer rank 0 -> 1 with a byte-pattern check
+    python -m mccl_b200.probe discover                 # what discovery found: ranks, links, NVLS, per-algorithm plans
 
 Distributed probes read MCCL_RANK, MCCL_WORLD_SIZE, MCCL_BOOTSTRAP_IP and MCCL_BOOTSTRAP_PORT (defaults
 0, 1, 127.0.0.1, 53700), like the reference's launch convention (README.md:29-31).  Exit code 0 = pass.
@@ -188,6 +191,66 @@ def probe_coll(a) -> int:
     return 0 if ok else 1
 
 
+def probe_bootstrap(a) -> int:
+    """Every rank contributes 1000 + rank through the control plane and checks the gathered table
+    (src/bootstrap.cc:88-109 of the reference)."""
+    import struct
+    comm = _comm("tcp")
+    got = [struct.unpack("i", b)[0] for b in comm.host_all_gather(struct.pack("i", 1000 + comm.rank))]
+    ok = got == [1000 + r for r in range(comm.size)]
+    print(f"rank {comm.rank}: bootstrap all-gather {got}: {'ok' if ok else 'FAIL'}")
+    comm.finalize(); comm.destroy()
+    return 0 if ok else 1
+
+
+def probe_m2m(a) -> int:
+    """Rank 0 sends `--bytes` bytes of the pattern data[i] = i & 0xff to rank 1 over the striped TCP transport
+    and rank 1 verifies every byte (src/transport/m2m.cc:372-404 of the reference); other ranks idle."""
+    import time
+    comm = _comm("tcp")
+    ok, n = True, a.bytes
+    if comm.size < 2:
+        print("m2m: needs two ranks")
+        comm.destroy()
+        return 1
+    pattern = (np.arange(n, dtype=np.uint64) & 0xff).astype(np.uint8)
+    if comm.rank == 0:
+        comm.send(pattern[:64], 1)                         # opens the connection
+        comm.host_barrier()
+        t0 = time.perf_counter()
+        comm.send(pattern, 1)
+        print(f"rank 0: sent {n} bytes in {(time.perf_counter() - t0) * 1e3:.2f} ms")
+    elif comm.rank == 1:
+        data = np.zeros(n, dtype=np.uint8)
+        comm.recv(data[:64], 0)
+        comm.host_barrier()
+        t0 = time.perf_counter()
+        comm.recv(data, 0)
+        dt = time.perf_counter() - t0
+        ok = bool(np.array_equal(data, pattern))
+        print(f"rank 1: received {n} bytes in {dt * 1e3:.2f} ms ({n / dt / 1e9:.2f} GB/s): {'ok' if ok else 'FAIL'}")
+    else:
+        comm.host_barrier()
+    comm.finalize(); comm.destroy()
+    return 0 if ok else 1
+
+
+def probe_discover(a) -> int:
+    """Prints what discovery and the planner agreed on (src/graph/discover.cc:178-221 of the reference): one line
+    per rank and link of the topology, the multicast capability and each algorithm's plan."""
+    import xml.etree.ElementTree as ET
+    comm = _comm(a.transport)
+    root = ET.fromstring(comm.topo_xml())
+    if comm.rank == 0:
+        for el in root.iter():
+            if el.tag != root.tag and el.attrib:
+                print(f"{el.tag}: " + " ".join(f"{k}={v}" for k, v in el.attrib.items()))
+    print(f"rank {comm.rank}/{comm.size}: transport {comm.transport}, nvls {comm.nvls}")
+    ok = sum(1 for el in root.iter() if el.tag in ("gpu", "node", "rank")) >= 1 or len(list(root)) > 0
+    comm.finalize(); comm.destroy()
+    return 0 if ok else 1
+
+
 def probe_bw(a) -> int:
     os.environ["MCCL_CALIBRATE"] = "1"
     comm = _comm("cuda")
@@ -210,6 +273,9 @@ def main() -> int:
     p = sub.add_parser("coll"); p.add_argument("--op", default="allreduce"); p.add_argument("--count", type=int, default=1 << 16)
     p.add_argument("--root", type=int, default=0); p.add_argument("--transport", default=None)
     p = sub.add_parser("bw"); p.add_argument("--mbytes", type=int, default=256)
+    sub.add_parser("bootstrap")
+    p = sub.add_parser("m2m"); p.add_argument("--bytes", type=int, default=8 << 20)
+    p = sub.add_parser("discover"); p.add_argument("--transport", default=None)
     a = ap.parse_args()
     return globals()["probe_" + a.cmd](a)
 

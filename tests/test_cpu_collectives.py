@@ -1,6 +1,8 @@
 """Multi-process tests of the tcp transport on loopback (no GPU): the reference's MCCL_COLL_MAIN,
 MCCL_BOOTSTRAP_MAIN and MCCL_COMM_MAIN probes (src/coll/coll.cc:110-237, src/bootstrap.cc:88-109,
 src/comm.cc:360-389) grown into a matrix."""
+import os
+
 import pytest
 
 from _mp import assert_all_ok, run_ranks
@@ -62,3 +64,32 @@ def test_striped_transfer_integrity():
 
 def test_ddp_gradient_accumulation():
     assert_all_ok(run_ranks(2, "ddp_accumulate"))
+
+
+def test_distributed_probes_on_loopback():
+    """The bootstrap, m2m and discover probes (MCCL_BOOTSTRAP_MAIN, MCCL_M2M_MAIN, MCCL_DISCOVER_MAIN of the
+    reference) as separate processes that find each other through MCCL_RANK / MCCL_WORLD_SIZE / MCCL_BOOTSTRAP_PORT."""
+    import socket
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for world, args in ((3, ["bootstrap"]), (2, ["m2m", "--bytes", "1000003"]), (2, ["discover", "--transport", "tcp"])):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        procs = []
+        for r in range(world):
+            env = dict(os.environ, MCCL_RANK=str(r), MCCL_WORLD_SIZE=str(world), MCCL_BOOTSTRAP_PORT=str(port),
+                       MCCL_BOOTSTRAP_IP="127.0.0.1")
+            procs.append(subprocess.Popen([sys.executable, "-m", "mccl_b200.probe", *args], cwd=root, env=env,
+                                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        outs = []
+        for p in procs:
+            try:
+                out, _ = p.communicate(timeout=120)
+            except subprocess.TimeoutExpired:
+                p.kill()
+                out, _ = p.communicate()
+            outs.append(out)
+        assert all(p.returncode == 0 for p in procs), (args, outs)
+        assert "FAIL" not in "".join(outs), (args, outs)
