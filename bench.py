@@ -38,6 +38,8 @@ def parse():
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "tiny"])
     ap.add_argument("--no-extras", action="store_true", help="skip the all-reduce bus-bandwidth table")
+    ap.add_argument("--shard-optimizer", action="store_true",
+                    help="reduce-scatter gradients, update 1/world of the parameters per rank, all-gather them (ZeRO stage 1)")
     return ap.parse_args()
 
 
@@ -89,7 +91,7 @@ def main() -> int:
             port = int(os.environ.get("MASTER_PORT", "29500")) + 23
             uid = mccl.unique_id_from_env(os.environ.get("MASTER_ADDR", "127.0.0.1"), port)
             comm = mccl.Communicator(world, uid, rank, transport="cuda")
-        ddp = DistributedDataParallel(model, comm, bucket_mb=args.bucket_mb)
+        ddp = DistributedDataParallel(model, comm, bucket_mb=args.bucket_mb, shard_optimizer=args.shard_optimizer)
         launches = lambda: (comm.launch_count if comm is not None else 0) + optim.launches() + loss_ops.launches() + norm_ops.launches()
 
         def train_step(tokens):
@@ -166,7 +168,7 @@ def main() -> int:
 
     # ---- exposed communication: the same step with the all-reduce switched off
     exposed_ms = None
-    if args.impl == "mccl" and world > 1:
+    if args.impl == "mccl" and world > 1 and not args.shard_optimizer:
         ddp.world = 1
         for b in ddp.buckets:
             b.done_event = None
@@ -195,7 +197,7 @@ def main() -> int:
         "impl": args.impl,
         "config": {"model": args.model, "params": n_params, "layers": cfg.n_layer, "d_model": cfg.d_model, "heads": cfg.n_head,
                    "ffn": cfg.d_ff, "vocab": cfg.vocab_size, "global_batch": world * B, "micro_batch": B, "seq_len": S,
-                   "parallelism": f"dp{world}", "bucket_mb": args.bucket_mb, "optimizer": "adamw (fused, fp32 master), global-norm clip 1.0",
+                   "parallelism": f"dp{world}" + ("+zero1" if args.shard_optimizer and world > 1 else ""), "bucket_mb": args.bucket_mb, "optimizer": "adamw (fused, fp32 master), global-norm clip 1.0",
                    "l2": "working set per step (0.7 GB weights + activations) exceeds the 126 MB L2; no flush needed"},
         "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", [])},
         "e2e": {"value": round(tokens_per_step / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 3),

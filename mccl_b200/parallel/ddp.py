@@ -12,6 +12,11 @@ one flat bf16 parameter buffer the module's parameters are re-pointed into, and 
 buffers for the optimizer.  `param.grad` is a view of the gradient bucket, so autograd accumulates straight
 into communication memory.
 
+With `shard_optimizer=True` (ZeRO stage 1) a bucket's gradients are reduce-scattered instead of all-reduced, each
+rank keeps the fp32 master weights and Adam moments of its 1/world slice only and updates that slice, and the new
+bf16 parameters are all-gathered in place: the same bytes cross NVLink as for an all-reduce, the optimizer kernels
+shrink by the world size, and so does the optimizer state.
+
 The reference publishes this workload only as a benchmark shape ("compute on batch + gradient all-reduce",
 docs/perf-scaling.png, README.md:55-57); the wrapper itself has no counterpart there.
 """
@@ -29,7 +34,7 @@ from ..ops.optim import fused_adamw_, scratch_floats, sum_squares_
 
 
 class _Bucket:
-    def __init__(self, params: List[nn.Parameter], weight_decay: float):
+    def __init__(self, params: List[nn.Parameter], weight_decay: float, align: int = 8):
         self.params = params
         self.weight_decay = weight_decay
         self.numel = 0
@@ -37,6 +42,8 @@ class _Bucket:
         for p in params:
             self.offsets.append(self.numel)
             self.numel += (p.numel() + 7) // 8 * 8          # keep every view 16-byte aligned
+        self.numel = (self.numel + align - 1) // align * align   # sharded: equal 16-byte aligned slices
+        self.gather_event: Optional[torch.cuda.Event] = None
         self.grad: Optional[torch.Tensor] = None
         self.param: Optional[torch.Tensor] = None
         self.master = self.exp_avg = self.exp_avg_sq = None
@@ -48,11 +55,14 @@ class _Bucket:
 
 class DistributedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, comm: Optional[Communicator] = None, bucket_mb: Optional[float] = None,
-                 overlap: bool = True, comm_ctas: int = 16, weight_decay: float = 0.1, betas=(0.9, 0.95), eps: float = 1e-8):
+                 overlap: bool = True, comm_ctas: int = 16, weight_decay: float = 0.1, betas=(0.9, 0.95), eps: float = 1e-8,
+                 shard_optimizer: bool = False):
         super().__init__()
         self.module = module
         self.comm = comm
         self.world = comm.size if comm is not None else 1
+        self.rank = comm.rank if comm is not None else 0
+        self.sharded = bool(shard_optimizer) and self.world > 1
         self.overlap = overlap
         self.betas, self.eps = betas, eps
         self.step_count = 0
@@ -70,6 +80,7 @@ class DistributedDataParallel(nn.Module):
             bucket_mb = float(os.environ.get("MCCL_BUCKET_MB", "25"))
         cap = int(bucket_mb * (1 << 20)) // params[0].element_size()
         # Matrices decay, vectors (biases, norms) do not: they live in separate buckets so a bucket has one setting.
+        align = 8 * self.world if self.sharded else 8
         self.buckets: List[_Bucket] = []
         for decay in (True, False):
             cur: List[nn.Parameter] = []
@@ -78,12 +89,12 @@ class DistributedDataParallel(nn.Module):
                 if (p.dim() >= 2) != decay:
                     continue
                 if cur and size + p.numel() > cap:
-                    self.buckets.append(_Bucket(cur, weight_decay if decay else 0.0))
+                    self.buckets.append(_Bucket(cur, weight_decay if decay else 0.0, align))
                     cur, size = [], 0
                 cur.append(p)
                 size += p.numel()
             if cur:
-                self.buckets.append(_Bucket(cur, weight_decay if decay else 0.0))
+                self.buckets.append(_Bucket(cur, weight_decay if decay else 0.0, align))
         self._bucket_of = {}
         for b in self.buckets:
             self._materialize(b)
@@ -105,16 +116,24 @@ class DistributedDataParallel(nn.Module):
             b.grad.zero_()
         else:
             b.grad = torch.zeros(b.numel, device=dev, dtype=dt)
-        b.param = torch.zeros(b.numel, device=dev, dtype=dt)
-        b.master = torch.zeros(b.numel, device=dev, dtype=torch.float32)
-        b.exp_avg = torch.zeros_like(b.master)
-        b.exp_avg_sq = torch.zeros_like(b.master)
+        if self.sharded and dev.type == "cuda":
+            b.param = self.comm.empty(b.numel, dt)          # all-gathered in place after the optimizer step
+            b.param.zero_()
+        else:
+            b.param = torch.zeros(b.numel, device=dev, dtype=dt)
         for p, off in zip(b.params, b.offsets):
             n = p.numel()
             b.param[off:off + n].copy_(p.data.reshape(-1))
-            b.master[off:off + n].copy_(p.data.reshape(-1).float())
             p.data = b.param[off:off + n].view(p.shape)
             p.grad = b.grad[off:off + n].view(p.shape)
+        # fp32 master weights and moments: the whole bucket, or this rank's slice of it when sharded
+        b.lo, b.hi = 0, b.numel
+        if self.sharded:
+            shard = b.numel // self.world
+            b.lo, b.hi = self.rank * shard, (self.rank + 1) * shard
+        b.master = b.param[b.lo:b.hi].float()
+        b.exp_avg = torch.zeros_like(b.master)
+        b.exp_avg_sq = torch.zeros_like(b.master)
 
     def _reset(self) -> None:
         for b in self.buckets:
@@ -130,12 +149,23 @@ class DistributedDataParallel(nn.Module):
             b.ready_event = torch.cuda.Event()
             b.ready_event.record()
             self.comm_stream.wait_event(b.ready_event)
-            self.comm.all_reduce(b.grad, op="avg", stream=self.comm_stream)
+            self._reduce(b, self.comm_stream)
             b.done_event = torch.cuda.Event()
             b.done_event.record(self.comm_stream)
         else:
-            self.comm.all_reduce(b.grad, op="avg")
+            self._reduce(b, None)
             b.done_event = None
+
+    def _reduce(self, b: _Bucket, stream) -> None:
+        if not self.sharded:
+            self.comm.all_reduce(b.grad, op="avg", stream=stream)
+        elif self.device.type == "cuda":
+            # in place: rank r reduces block r of every rank's bucket into block r of its own
+            self.comm.reduce_scatter(b.grad, b.grad[b.lo:b.hi], op="avg", stream=stream)
+        else:
+            out = torch.empty(b.hi - b.lo, dtype=b.grad.dtype)
+            self.comm.reduce_scatter(b.grad, out, op="avg")
+            b.grad[b.lo:b.hi].copy_(out)
 
     def _on_grad(self, p: nn.Parameter) -> None:
         b = self._bucket_of[p]
@@ -174,37 +204,64 @@ class DistributedDataParallel(nn.Module):
         optimizer kernels clip by it without a host round trip."""
         self.step_count += 1
         norm_sq = None
-        if max_grad_norm is not None and self.device.type == "cuda":
+        cuda = self.device.type == "cuda"
+        if max_grad_norm is not None and cuda:
             if self._norm_sq is None:
-                self._norm_sq = torch.zeros(1, device=self.device, dtype=torch.float32)
-                self._norm_scratch = torch.zeros(scratch_floats(max(b.numel for b in self.buckets)), device=self.device,
+                # four floats: a 16-byte message takes the one-shot all-reduce when the norm is summed over ranks
+                self._norm_sq = (self.comm.empty(4, torch.float32) if self.sharded else
+                                 torch.zeros(4, device=self.device, dtype=torch.float32))
+                self._norm_sq.zero_()
+                self._norm_scratch = torch.zeros(scratch_floats(max(b.hi - b.lo for b in self.buckets)), device=self.device,
                                                  dtype=torch.float32)
-            norm_sq = self._norm_sq
+            norm_sq = self._norm_sq[:1]
             cur0 = torch.cuda.current_stream(self.device)
             for i, b in enumerate(self.buckets):
                 if not b.launched:
                     self._launch(b)
                 if b.done_event is not None:
                     cur0.wait_event(b.done_event)
-                sum_squares_(b.grad, norm_sq, self._norm_scratch, accumulate=i > 0)
+                sum_squares_(b.grad[b.lo:b.hi], norm_sq, self._norm_scratch, accumulate=i > 0)
+            if self.sharded:
+                self.comm.all_reduce(self._norm_sq, op="sum")      # every rank summed its slices only
         for b in self.buckets:
             if not b.launched:
                 self._launch(b)
-        cur = torch.cuda.current_stream(self.device) if self.device.type == "cuda" else None
+        cur = torch.cuda.current_stream(self.device) if cuda else None
+        side = self.comm_stream if (self.sharded and self.overlap and cuda) else None
         for b in self.buckets:
             if b.done_event is not None and cur is not None:
                 cur.wait_event(b.done_event)
-            if self.device.type == "cuda":
-                fused_adamw_(b.param, b.master, b.exp_avg, b.exp_avg_sq, b.grad, lr=lr, betas=self.betas, eps=self.eps,
-                             weight_decay=b.weight_decay, step=self.step_count, zero_grad=True, norm_sq=norm_sq,
+            p_slice, g_slice = b.param[b.lo:b.hi], b.grad[b.lo:b.hi]
+            if cuda:
+                fused_adamw_(p_slice, b.master, b.exp_avg, b.exp_avg_sq, g_slice, lr=lr, betas=self.betas, eps=self.eps,
+                             weight_decay=b.weight_decay, step=self.step_count, zero_grad=not self.sharded, norm_sq=norm_sq,
                              max_norm=max_grad_norm or 0.0)
+                if self.sharded:
+                    b.grad.zero_()                     # the other ranks' slices hold this rank's raw gradients
             else:  # CPU stand-in for tests of the bucket logic
                 from ..ops.optim import adamw_reference
-                new = adamw_reference(b.master, b.exp_avg, b.exp_avg_sq, b.grad, lr=lr, betas=self.betas, eps=self.eps,
+                new = adamw_reference(b.master, b.exp_avg, b.exp_avg_sq, g_slice, lr=lr, betas=self.betas, eps=self.eps,
                                       weight_decay=b.weight_decay, grad_scale=1.0, step=self.step_count)
-                b.param.copy_(new.to(b.param.dtype))
+                p_slice.copy_(new.to(b.param.dtype))
                 b.grad.zero_()
+            if self.sharded:
+                # every rank's new slice into every rank's copy of the bucket, in place; on the side stream it
+                # runs under the next bucket's optimizer kernel
+                if side is not None:
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    side.wait_event(ev)
+                    self.comm.all_gather(p_slice, b.param, stream=side)
+                    b.gather_event = torch.cuda.Event()
+                    b.gather_event.record(side)
+                else:
+                    self.comm.all_gather(p_slice, b.param)
             b.done_event = None
+        if side is not None:
+            for b in self.buckets:
+                if b.gather_event is not None:
+                    cur.wait_event(b.gather_event)
+                    b.gather_event = None
         self._reset()
 
     def bucket_sizes_mb(self) -> List[float]:

@@ -192,6 +192,40 @@ def split_and_ddp():
     comm.finalize(); comm.destroy()
 
 
+def ddp_sharded():
+    """Sharded optimizer on GPUs: same losses as the replicated optimizer step for step (same averaged gradients,
+    same arithmetic per element, clipping by the same global norm), replicas bit-identical, state 1/world."""
+    from mccl_b200.models.gpt2 import GPT2, GPT2Config
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    comm = make_comm()
+    cfg = GPT2Config.tiny()
+    g = torch.Generator().manual_seed(7 + RANK)
+    tokens = torch.randint(0, cfg.vocab_size, (4, cfg.seq_len + 1), generator=g).to(DEV)
+    runs = []
+    for shard in (False, True):
+        torch.manual_seed(0)
+        model = GPT2(cfg).to(device=DEV, dtype=torch.bfloat16)
+        ddp = DistributedDataParallel(model, comm, bucket_mb=0.25, shard_optimizer=shard)
+        losses = []
+        for _ in range(5):
+            loss = ddp(tokens[:, :-1], tokens[:, 1:]); loss.backward(); ddp.step(lr=3e-3, max_grad_norm=1.0)
+            losses.append(loss.item())
+        torch.cuda.synchronize()
+        flat = torch.cat([b.param[:sum((p.numel() + 7) // 8 * 8 for p in b.params)].float() for b in ddp.buckets])
+        runs.append((losses, flat, ddp))
+    (l0, p0, d0), (l1, p1, d1) = runs
+    assert l1[-1] < l1[0], l1
+    assert max(abs(a - b) for a, b in zip(l0, l1)) < 2e-2, (l0, l1)
+    assert (p0 - p1).abs().max().item() < 2e-2, (p0 - p1).abs().max().item()     # a few bf16 steps after 5 updates
+    assert all(b.master.numel() * WORLD == b.numel for b in d1.buckets)
+    gathered = torch.empty(p1.numel() * WORLD, device=DEV)
+    comm.all_gather(p1.contiguous(), gathered); torch.cuda.synchronize()
+    for r in range(WORLD):
+        assert torch.equal(gathered[r * p1.numel():(r + 1) * p1.numel()], p1), f"replica {r} diverged"
+    assert canary_ok(comm)
+    comm.finalize(); comm.destroy()
+
+
 def device_timeout():
     """Rank 1 sits out one collective (between steps, nothing of its own in flight).  The others' kernels
     give up after the device time budget, record why in the status word and return; the host reads it."""

@@ -360,6 +360,43 @@ def ddp_cpu():
     comm.finalize(); comm.destroy()
 
 
+def ddp_zero():
+    """Sharded optimizer (reduce-scatter, update of the own slice, all-gather): the parameters follow
+    single-process training on the concatenated batch, on every rank alike, and the optimizer state is 1/world."""
+    import torch
+    from mccl_b200.models.gpt2 import GPT2, GPT2Config
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    comm = make_comm()
+    torch.manual_seed(0)
+    cfg = GPT2Config.tiny()
+    model = GPT2(cfg)
+    ddp = DistributedDataParallel(model, comm, bucket_mb=0.25, shard_optimizer=True)
+    assert len(ddp.buckets) > 2
+    for b in ddp.buckets:
+        assert b.numel % (8 * WORLD) == 0 and b.master.numel() == b.numel // WORLD == b.exp_avg.numel()
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, cfg.vocab_size, (2 * WORLD, cfg.seq_len + 1), generator=g)
+    mine = tokens[2 * RANK: 2 * RANK + 2]
+    torch.manual_seed(0)
+    single = GPT2(cfg)
+    ref = DistributedDataParallel(single, None, bucket_mb=0.25)
+    for _ in range(3):
+        loss = ddp(mine[:, :-1], mine[:, 1:]); loss.backward(); ddp.step(lr=1e-3)
+        l2 = ref(tokens[:, :-1], tokens[:, 1:]); l2.backward(); ref.step(lr=1e-3)
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), single.named_parameters()):
+        assert (p1 - p2).abs().max().item() < 1.5e-3, (n1, (p1 - p2).abs().max().item())
+        assert (p1 - p2).abs().mean().item() < 5e-5, (n1, (p1 - p2).abs().mean().item())
+        assert p1.grad.abs().max().item() == 0.0, n1                 # cleared for the next accumulation
+    # every rank holds the same parameters, bit for bit
+    import hashlib
+    h = hashlib.sha256()
+    for b in ddp.buckets:
+        h.update(b.param.numpy().tobytes())
+    digests = comm.host_all_gather(h.digest())
+    assert all(d == digests[0] for d in digests)
+    comm.finalize(); comm.destroy()
+
+
 def ddp_accumulate():
     """Two micro-batches (the first under no_sync) give the gradient of the concatenated batch."""
     import torch

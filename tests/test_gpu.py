@@ -394,6 +394,11 @@ def test_forced_ring_and_tree_for_other_collectives():
 
 
 @unverified
+def test_ddp_sharded_optimizer_on_gpus():
+    assert_all_ok(run_ranks(min(NGPU, 4), "ddp_sharded", worker="_gpu_worker.py", timeout=600))
+
+
+@unverified
 def test_collectives_replay_from_a_cuda_graph():
     assert_all_ok(run_ranks(2, "graph_capture", worker="_gpu_worker.py", timeout=300))
 
