@@ -226,6 +226,46 @@ def ddp_sharded():
     comm.finalize(); comm.destroy()
 
 
+def c10d_backend_gpu():
+    """The "mccl" torch.distributed backend on cuda tensors: plain c10d calls, then torch's DistributedDataParallel
+    (bucket hooks use the work's future) against single-process training on the whole batch."""
+    import torch.distributed as dist
+    import mccl_b200.c10d  # noqa: F401
+    dist.init_process_group("mccl", rank=RANK, world_size=WORLD, init_method="file://" + ARGS["rendezvous"])
+    n = WORLD
+    t = torch.full((1 << 20,), RANK + 1.0, device=DEV)
+    dist.all_reduce(t)
+    assert torch.all(t == n * (n + 1) / 2)
+    w = dist.all_reduce(t, op=dist.ReduceOp.AVG, async_op=True)
+    w.wait()
+    assert torch.all(t == n * (n + 1) / 2)
+    b = torch.arange(1000, device=DEV, dtype=torch.int64) * (1 if RANK == n - 1 else 0)
+    dist.broadcast(b, src=n - 1)
+    assert torch.equal(b, torch.arange(1000, device=DEV, dtype=torch.int64))
+    out = torch.empty(4096 * n, device=DEV, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(out, torch.full((4096,), float(RANK), device=DEV, dtype=torch.bfloat16))
+    assert torch.equal(out.float(), torch.arange(n, device=DEV, dtype=torch.float32).repeat_interleave(4096))
+    rs = torch.empty(512, device=DEV)
+    dist.reduce_scatter_tensor(rs, torch.arange(512 * n, device=DEV, dtype=torch.float32))
+    assert torch.equal(rs, n * torch.arange(512 * RANK, 512 * RANK + 512, device=DEV, dtype=torch.float32))
+    dist.barrier()
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.Tanh(), torch.nn.Linear(256, 8)).to(DEV)
+    ref = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.Tanh(), torch.nn.Linear(256, 8)).to(DEV)
+    ref.load_state_dict(net.state_dict())
+    ddp = torch.nn.parallel.DistributedDataParallel(net, device_ids=[RANK], bucket_cap_mb=0.01)
+    g = torch.Generator().manual_seed(3)
+    x, y = torch.randn(8 * n, 64, generator=g).to(DEV), torch.randn(8 * n, 8, generator=g).to(DEV)
+    o1, o2 = torch.optim.SGD(ddp.parameters(), lr=0.1), torch.optim.SGD(ref.parameters(), lr=0.1)
+    for _ in range(3):
+        o1.zero_grad(); torch.nn.functional.mse_loss(ddp(x[8 * RANK:8 * RANK + 8]), y[8 * RANK:8 * RANK + 8]).backward(); o1.step()
+        o2.zero_grad(); torch.nn.functional.mse_loss(ref(x), y).backward(); o2.step()
+    torch.cuda.synchronize()
+    for p1, p2 in zip(net.parameters(), ref.parameters()):
+        assert torch.allclose(p1, p2, atol=1e-5, rtol=1e-4), (p1 - p2).abs().max().item()
+    dist.destroy_process_group()
+
+
 def device_timeout():
     """Rank 1 sits out one collective (between steps, nothing of its own in flight).  The others' kernels
     give up after the device time budget, record why in the status word and return; the host reads it."""

@@ -397,6 +397,81 @@ def ddp_zero():
     comm.finalize(); comm.destroy()
 
 
+def c10d_backend():
+    """The "mccl" torch.distributed backend on cpu tensors (tcp transport): the c10d calls torch code makes, then
+    torch's own DistributedDataParallel on top of it against single-process training."""
+    import torch
+    import torch.distributed as dist
+    import mccl_b200.c10d  # noqa: F401  (registers the backend)
+    dist.init_process_group("mccl", rank=RANK, world_size=WORLD, init_method="file://" + ARGS["rendezvous"])
+    assert dist.get_backend() == "mccl"
+    n = WORLD
+    t = torch.full((1000,), RANK + 1.0)
+    dist.all_reduce(t)
+    assert torch.all(t == n * (n + 1) / 2)
+    t = torch.full((7,), RANK + 1.0, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    assert torch.all(t == n)
+    w = dist.all_reduce(torch.ones(5), async_op=True)
+    w.wait()
+    assert w.is_completed()
+    b = torch.arange(10, dtype=torch.int64) * (1 if RANK == 1 else 0)
+    dist.broadcast(b, src=1)
+    assert torch.equal(b, torch.arange(10, dtype=torch.int64))
+    out = torch.empty(4 * n)
+    dist.all_gather_into_tensor(out, torch.full((4,), float(RANK)))
+    assert torch.equal(out, torch.arange(n, dtype=torch.float32).repeat_interleave(4))
+    outs = [torch.empty(3, 2) for _ in range(n)]
+    dist.all_gather(outs, torch.full((3, 2), float(RANK)))
+    assert all(torch.all(o == r) for r, o in enumerate(outs))
+    rs = torch.empty(5)
+    dist.reduce_scatter_tensor(rs, torch.arange(5 * n, dtype=torch.float32), op=dist.ReduceOp.SUM)
+    assert torch.equal(rs, n * torch.arange(5 * RANK, 5 * RANK + 5, dtype=torch.float32))
+    r = torch.full((6,), RANK + 1.0)
+    dist.reduce(r, dst=0, op=dist.ReduceOp.SUM)
+    assert RANK != 0 or torch.all(r == n * (n + 1) / 2)
+    a2a = torch.empty(2 * n)
+    dist.all_to_all_single(a2a, torch.arange(2 * n, dtype=torch.float32) + 100 * RANK)
+    assert torch.equal(a2a, torch.cat([torch.arange(2 * RANK, 2 * RANK + 2, dtype=torch.float32) + 100 * s for s in range(n)]))
+    if RANK == 0:
+        dist.send(torch.full((9,), 3.5), dst=1)
+    elif RANK == 1:
+        got = torch.zeros(9)
+        dist.recv(got, src=0)
+        assert torch.all(got == 3.5)
+    dist.barrier()
+    with pytest_raises(ValueError):
+        dist.all_reduce(torch.ones(3, dtype=torch.int32), op=dist.ReduceOp.BXOR)
+
+    # torch DDP on top of the backend
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+    ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+    ref.load_state_dict(net.state_dict())
+    ddp = torch.nn.parallel.DistributedDataParallel(net, bucket_cap_mb=0.001)
+    g = torch.Generator().manual_seed(3)
+    x, y = torch.randn(4 * n, 16, generator=g), torch.randn(4 * n, 4, generator=g)
+    o1, o2 = torch.optim.SGD(ddp.parameters(), lr=0.1), torch.optim.SGD(ref.parameters(), lr=0.1)
+    for _ in range(3):
+        o1.zero_grad(); torch.nn.functional.mse_loss(ddp(x[4 * RANK:4 * RANK + 4]), y[4 * RANK:4 * RANK + 4]).backward(); o1.step()
+        o2.zero_grad(); torch.nn.functional.mse_loss(ref(x), y).backward(); o2.step()
+    for p1, p2 in zip(net.parameters(), ref.parameters()):
+        assert torch.allclose(p1, p2, atol=1e-6, rtol=1e-5), (p1 - p2).abs().max().item()
+    dist.destroy_process_group()
+
+
+class pytest_raises:
+    def __init__(self, exc):
+        self.exc = exc
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, et, ev, tb):
+        assert et is not None and issubclass(et, self.exc), f"expected {self.exc}, got {et}"
+        return True
+
+
 def ddp_accumulate():
     """Two micro-batches (the first under no_sync) give the gradient of the concatenated batch."""
     import torch

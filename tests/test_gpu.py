@@ -394,6 +394,11 @@ def test_forced_ring_and_tree_for_other_collectives():
 
 
 @unverified
+def test_torch_distributed_backend_on_gpus(tmp_path):
+    assert_all_ok(run_ranks(2, "c10d_backend_gpu", worker="_gpu_worker.py", args={"rendezvous": str(tmp_path / "rdv")}, timeout=300))
+
+
+@unverified
 def test_ddp_sharded_optimizer_on_gpus():
     assert_all_ok(run_ranks(min(NGPU, 4), "ddp_sharded", worker="_gpu_worker.py", timeout=600))
 
