@@ -249,6 +249,18 @@ class MCCLBackend(dist.ProcessGroup):
             torch.cuda.current_stream(dev).synchronize()
         return w
 
+    # ---- symmetric memory (no c10d counterpart at this level: reach it through dist.group.WORLD)
+    def empty_symmetric(self, shape, dtype=torch.float32, device: Optional[torch.device] = None) -> torch.Tensor:
+        """Collective: a cuda tensor in symmetric memory (peer-mapped, multicast-bound), which the collectives use in
+        place; tensors from torch's allocator are staged through the communicator's scratch instead."""
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        return self._comm(dev).empty(shape, dtype)
+
+    def communicator(self, device_type: str = "cuda") -> Communicator:
+        """The library's communicator behind this process group (split, register, tuning knobs, ...)."""
+        dev = torch.device("cuda", torch.cuda.current_device()) if device_type == "cuda" else torch.device("cpu")
+        return self._comm(dev)
+
     def shutdown(self) -> None:
         for comm in self._comms.values():
             try:

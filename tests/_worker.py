@@ -440,6 +440,8 @@ def c10d_backend():
         dist.recv(got, src=0)
         assert torch.all(got == 3.5)
     dist.barrier()
+    comm = dist.group.WORLD.communicator("cpu")
+    assert comm.size == n and comm.rank == RANK and comm.transport == "tcp"
     with pytest_raises(ValueError):
         dist.all_reduce(torch.ones(3, dtype=torch.int32), op=dist.ReduceOp.BXOR)
 
