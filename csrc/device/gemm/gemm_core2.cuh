@@ -12,7 +12,7 @@
 //   warp 2  allocates / frees tensor memory (cta_group::2: one warp of each CTA takes part)
 //   warps 4-7 epilogue of the CTA's own 128 rows; both CTAs release the accumulator on the leader's barrier
 //
-// TMA loads carry no cluster multicast: each CTA fetches what it needs itself.  Every wait is bounded, as in
+// Each CTA fetches what it needs itself: no load is shared between the CTAs of a pair.  Every wait is bounded, as in
 // the one-SM kernel; a CTA that gives up leaves its loops, and its partner then runs into its own time limit
 // before both meet at the closing cluster barrier.  No counterpart in the reference.
 #pragma once
@@ -55,7 +55,7 @@ __device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" :: "r"(clusterAddr) : "memory");
 }
 // 2-D tiled load into this CTA's shared memory whose completion bytes are counted on a barrier of either CTA
-// of the pair (shared::cluster address).  No multicast.
+// of the pair (shared::cluster address).
 __device__ __forceinline__ void tmaLoad2dPair(void* smemDst, const CUtensorMap* map, uint32_t barClusterAddr, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -75,11 +75,16 @@ __device__ __forceinline__ void mmaBf16(uint32_t tmemD, uint64_t descA, uint64_t
       " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
       :: "r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
 }
-// Arrive on the barrier at this offset in both CTAs once every MMA issued so far has completed.
+// Arrive on the barrier at this offset in both CTAs once every MMA issued so far has completed: one commit per
+// CTA, each naming that CTA's barrier by its shared::cluster address (a commit tracks all earlier MMAs of the
+// issuing thread, so the two are independent observers of the same work).
+__device__ __forceinline__ void mmaCommitTo(uint32_t barClusterAddr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(barClusterAddr) : "memory");
+}
 __device__ __forceinline__ void mmaCommitBoth(uint64_t* bar) {
-  const uint16_t mask = 3;
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               :: "r"(umma::smemAddr(bar)), "h"(mask) : "memory");
+  const uint32_t local = umma::smemAddr(bar);
+  mmaCommitTo(mapToCta(local, 0));
+  mmaCommitTo(mapToCta(local, 1));
 }
 
 }  // namespace umma2
