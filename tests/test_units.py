@@ -362,3 +362,20 @@ def test_gemm_tile_order_visits_every_tile_once(lib):
                 assert blocks == [(rank + i) % n for i in range(n)]     # own shard first, then in arrival order
             if mode == 2:
                 assert blocks == [(rank + 1 + i) % n for i in range(n)]  # peers' blocks first, own block last
+
+
+def test_tuner_model_tracks_measured_times(lib):
+    """The cost model's constants were fitted on 8 B200; these are times measured there (us, bf16 sum, forced
+    algorithm).  A change of the constants that moves a prediction by more than 35 % should be a deliberate one."""
+    measured = {  # algorithm -> {bytes: us}
+        "nvls":    {1 << 20: 32.7, 4 << 20: 38.8, 16 << 20: 71.4, 64 << 20: 173.4, 256 << 20: 585.8},
+        "twoshot": {1 << 10: 55.0, 256 << 20: 761.0},
+        "oneshot": {1 << 10: 26.0, 1 << 20: 76.0},
+        "ring":    {1 << 10: 148.0, 256 << 20: 2292.0},
+        "tree":    {1 << 10: 94.0, 256 << 20: 12477.0},
+    }
+    for algo, cells in measured.items():
+        for nbytes, us in cells.items():
+            _, times = _pick(lib, 8, 1, 1, nbytes, dt=L.BFLOAT16)
+            model = times[L.ALGOS[algo]]
+            assert 0.65 * us <= model <= 1.35 * us, (algo, nbytes, model, us)
