@@ -266,6 +266,16 @@ def c10d_backend_gpu():
     dist.destroy_process_group()
 
 
+def parallel_layers_gpu():
+    """The model-parallel layers and the pipeline schedule on cuda tensors (fp32, collectives through the kernels)."""
+    from _parallel_cases import layers_case, pipeline_case
+    comm = make_comm()
+    layers_case(comm, RANK, WORLD, DEV, atol=2e-4)
+    pipeline_case(comm, RANK, WORLD, DEV, atol=1e-5)
+    assert canary_ok(comm)
+    comm.finalize(); comm.destroy()
+
+
 def device_timeout():
     """Rank 1 sits out one collective (between steps, nothing of its own in flight).  The others' kernels
     give up after the device time budget, record why in the status word and return; the host reads it."""

@@ -474,6 +474,22 @@ class pytest_raises:
         return True
 
 
+def parallel_layers():
+    import torch
+    from _parallel_cases import layers_case
+    comm = make_comm()
+    layers_case(comm, RANK, WORLD, torch.device("cpu"))
+    comm.finalize(); comm.destroy()
+
+
+def pipeline_1f1b():
+    import torch
+    from _parallel_cases import pipeline_case
+    comm = make_comm()
+    pipeline_case(comm, RANK, WORLD, torch.device("cpu"), atol=1e-6)
+    comm.finalize(); comm.destroy()
+
+
 def ddp_accumulate():
     """Two micro-batches (the first under no_sync) give the gradient of the concatenated batch."""
     import torch

@@ -76,6 +76,16 @@ def test_torch_distributed_backend(world, tmp_path):
     assert_all_ok(run_ranks(world, "c10d_backend", args={"rendezvous": str(tmp_path / "rdv")}))
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_model_parallel_layers(world):
+    assert_all_ok(run_ranks(world, "parallel_layers"))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_pipeline_schedule(world):
+    assert_all_ok(run_ranks(world, "pipeline_1f1b"))
+
+
 def test_distributed_probes_on_loopback():
     """The bootstrap, m2m and discover probes (MCCL_BOOTSTRAP_MAIN, MCCL_M2M_MAIN, MCCL_DISCOVER_MAIN of the
     reference) as separate processes that find each other through MCCL_RANK / MCCL_WORLD_SIZE / MCCL_BOOTSTRAP_PORT."""
