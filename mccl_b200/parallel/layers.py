@@ -5,6 +5,8 @@
                                                                    (Megatron-style sequence parallelism)
     UlyssesAttention                                               sequence parallel attention: all-to-all from
                                                                    token shards to head shards and back
+    RingAttention                                                  context parallel attention: key / value blocks
+                                                                   travel around the ring of ranks
     ExpertParallelMoE                                              top-1 routed experts spread over the ranks,
                                                                    dispatch and combine by all-to-all
 
@@ -128,6 +130,19 @@ class UlyssesAttention(nn.Module):
         return self._to_tokens(o.squeeze(0).transpose(0, 1).contiguous())
 
 
+class RingAttention(nn.Module):
+    """Context-parallel self-attention: the sequence stays sharded over the ranks and the key / value blocks travel
+    around the ring (`functional.ring_attention`); memory per rank is independent of the number of ranks, and any
+    number of heads works (Ulysses needs heads divisible by the ranks)."""
+
+    def __init__(self, comm: Communicator, causal: bool = True):
+        super().__init__()
+        self.comm, self.causal = comm, causal
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        return PF.ring_attention(q, k, v, self.comm, self.causal)
+
+
 class ExpertParallelMoE(nn.Module):
     """Top-1 routed mixture of experts, `experts_per_rank` experts on each of the n ranks.  A token goes to the
     expert with the largest router probability and is weighted by it.  Every (source rank, expert) pair has
@@ -188,5 +203,5 @@ def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causa
     return o.squeeze(0).transpose(0, 1)
 
 
-__all__ = ["ColumnParallelLinear", "RowParallelLinear", "TensorParallelMLP", "UlyssesAttention", "ExpertParallelMoE",
+__all__ = ["ColumnParallelLinear", "RowParallelLinear", "TensorParallelMLP", "UlyssesAttention", "RingAttention", "ExpertParallelMoE",
            "moe_reference", "attention_reference"]

@@ -53,6 +53,19 @@ def layers_case(comm, RANK, WORLD, dev, atol=2e-5):
     for name, a, b in (("dq", ql, qf), ("dk", kl, kf), ("dv", vl, vf)):
         close(a.grad, b.grad[r * sb:(r + 1) * sb], "ulysses " + name)
 
+    # ring (context parallel) attention on the same tensors, with and without the causal mask, odd head count allowed
+    for causal in (True, False):
+        q3, k3, v3 = (t[:, :3].contiguous() for t in (q, k, v))
+        qf, kf, vf = (t.clone().requires_grad_(True) for t in (q3, k3, v3))
+        of = PL.attention_reference(qf, kf, vf, causal=causal)
+        (of * tg[:, :3]).sum().backward()
+        ql, kl, vl = (t[r * sb:(r + 1) * sb].clone().requires_grad_(True) for t in (q3, k3, v3))
+        o = PL.RingAttention(comm, causal=causal)(ql, kl, vl)
+        (o * tg[r * sb:(r + 1) * sb, :3]).sum().backward()
+        close(o, of[r * sb:(r + 1) * sb], ("ring out", causal))
+        for name, a, b in (("dq", ql, qf), ("dk", kl, kf), ("dv", vl, vf)):
+            close(a.grad, b.grad[r * sb:(r + 1) * sb], ("ring " + name, causal))
+
     # expert parallel mixture of experts
     e_loc, cap = 2, 2
     E = e_loc * n
