@@ -440,6 +440,11 @@ def c10d_backend():
         dist.recv(got, src=0)
         assert torch.all(got == 3.5)
     dist.barrier()
+    sub = dist.new_group([0, n - 1])                       # a subgroup gets its own communicator
+    if RANK in (0, n - 1):
+        t = torch.full((11,), RANK + 1.0)
+        dist.all_reduce(t, group=sub)
+        assert torch.all(t == (1.0 + n if n > 1 else 1.0)), t
     comm = dist.group.WORLD.communicator("cpu")
     assert comm.size == n and comm.rank == RANK and comm.transport == "tcp"
     with pytest_raises(ValueError):
