@@ -128,3 +128,44 @@ def pipeline_case(comm, RANK, WORLD, dev, atol=2e-5):
             assert abs(loss.item() - ref) < 10 * atol, (n_micro, loss.item(), ref)
         for g, p in zip(got, mine.parameters()):
             assert torch.allclose(g, p.grad, atol=atol, rtol=50 * atol), (n_micro, (g - p.grad).abs().max().item())
+
+
+def llama_case(comm, RANK, WORLD, dev, atol=2e-5):
+    """The tensor-parallel Llama-style decoder (replicated and sequence-parallel residual stream) against the same
+    model on a communicator of size 1: loss and every gradient."""
+    import torch
+    import mccl_b200 as mccl
+    from mccl_b200.models.llama import Llama, LlamaConfig
+    cfg = LlamaConfig.tiny()
+    cfg.d_ff = 32 * WORLD
+    cfg.n_head = 2 * WORLD
+    cfg.d_model = 16 * cfg.n_head
+    one = mccl.Communicator(1, mccl.get_unique_id(), 0, transport=comm.transport)
+    torch.manual_seed(0)
+    ref = Llama(cfg, one).to(dev)
+    state = {k: v.detach().clone() for k, v in ref.named_parameters()}
+    g = torch.Generator().manual_seed(4)
+    tokens = torch.randint(0, cfg.vocab_size, (2 * WORLD, cfg.seq_len + 1), generator=g).to(dev)
+    idx, tgt = tokens[:, :-1], tokens[:, 1:]
+    lref = ref(idx, tgt)
+    lref.backward()
+    n, r = WORLD, RANK
+    for sp in (False, True):
+        model = Llama(cfg, comm, sequence_parallel=sp).to(dev)
+        model.load_full(state)
+        loss = model(idx, tgt)
+        loss.backward()
+        model.reduce_replicated_grads()
+        assert abs(loss.item() - lref.item()) < 10 * atol, (sp, loss.item(), lref.item())
+        full = dict(ref.named_parameters())
+        for name, p in model.named_parameters():
+            want = full[name].grad
+            leaf = name.split(".")[-2]
+            if leaf in ("q", "k", "v", "gate", "up"):
+                m = want.shape[0] // n
+                want = want[r * m:(r + 1) * m]
+            elif leaf in ("o", "down"):
+                m = want.shape[1] // n
+                want = want[:, r * m:(r + 1) * m]
+            assert torch.allclose(p.grad, want, atol=atol, rtol=50 * atol), (sp, name, (p.grad - want).abs().max().item())
+    one.destroy()

@@ -487,6 +487,14 @@ def parallel_layers():
     comm.finalize(); comm.destroy()
 
 
+def llama_tp():
+    import torch
+    from _parallel_cases import llama_case
+    comm = make_comm()
+    llama_case(comm, RANK, WORLD, torch.device("cpu"))
+    comm.finalize(); comm.destroy()
+
+
 def pipeline_1f1b():
     import torch
     from _parallel_cases import pipeline_case

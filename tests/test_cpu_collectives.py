@@ -81,6 +81,11 @@ def test_model_parallel_layers(world):
     assert_all_ok(run_ranks(world, "parallel_layers"))
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_tensor_parallel_llama(world):
+    assert_all_ok(run_ranks(world, "llama_tp"))
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_pipeline_schedule(world):
     assert_all_ok(run_ranks(world, "pipeline_1f1b"))
