@@ -495,6 +495,50 @@ def llama_tp():
     comm.finalize(); comm.destroy()
 
 
+def tp_dp_2d():
+    """Four ranks as tensor parallel 2 x data parallel 2 (two splits of the world communicator): the Llama-style model
+    on the tensor-parallel group inside the bucketed DDP wrapper on the data-parallel group reproduces the
+    single-process gradient of the whole batch."""
+    import torch
+    import mccl_b200 as mccl
+    from mccl_b200.models.llama import Llama, LlamaConfig
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    world = make_comm()
+    assert WORLD == 4
+    tp = world.split(RANK // 2, RANK)            # ranks {0,1} and {2,3}
+    dp = world.split(RANK % 2, RANK)             # ranks {0,2} and {1,3}
+    assert tp.size == 2 and dp.size == 2 and tp.rank == RANK % 2 and dp.rank == RANK // 2
+    cfg = LlamaConfig.tiny()
+    one = mccl.Communicator(1, mccl.get_unique_id(), 0, transport="tcp")
+    torch.manual_seed(0)
+    ref = Llama(cfg, one)
+    state = {k: v.detach().clone() for k, v in ref.named_parameters()}
+    g = torch.Generator().manual_seed(4)
+    tokens = torch.randint(0, cfg.vocab_size, (4, cfg.seq_len + 1), generator=g)
+    ref(tokens[:, :-1], tokens[:, 1:]).backward()
+    model = Llama(cfg, tp)
+    model.load_full(state)
+    ddp = DistributedDataParallel(model, dp, bucket_mb=0.05)
+    mine = tokens[2 * dp.rank: 2 * dp.rank + 2]  # each data-parallel replica takes half of the batch
+    ddp(mine[:, :-1], mine[:, 1:]).backward()
+    ddp.finish_backward()
+    full = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        want = full[name].grad
+        leaf = name.split(".")[-2]
+        if leaf in ("q", "k", "v", "gate", "up"):
+            m = want.shape[0] // 2
+            want = want[tp.rank * m:(tp.rank + 1) * m]
+        elif leaf in ("o", "down"):
+            m = want.shape[1] // 2
+            want = want[:, tp.rank * m:(tp.rank + 1) * m]
+        assert torch.allclose(p.grad, want, atol=2e-5, rtol=1e-3), (name, (p.grad - want).abs().max().item())
+    for c in (tp, dp):
+        c.finalize(); c.destroy()
+    one.destroy()
+    world.finalize(); world.destroy()
+
+
 def pipeline_1f1b():
     import torch
     from _parallel_cases import pipeline_case

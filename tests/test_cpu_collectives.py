@@ -86,6 +86,10 @@ def test_tensor_parallel_llama(world):
     assert_all_ok(run_ranks(world, "llama_tp"))
 
 
+def test_tensor_parallel_times_data_parallel():
+    assert_all_ok(run_ranks(4, "tp_dp_2d"))
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_pipeline_schedule(world):
     assert_all_ok(run_ranks(world, "pipeline_1f1b"))
