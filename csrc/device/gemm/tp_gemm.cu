@@ -7,6 +7,7 @@
 #include "../../comm/comm.h"
 #include "../../transport/cuda_mem.h"
 #include "gemm_core.cuh"
+#include "mccl_ops.h"
 #include "gemm_core2.cuh"
 
 using namespace mccl;

@@ -4,6 +4,7 @@
 #include "../core/core.h"
 #include "grad_norm.cuh"
 #include "mccl.h"
+#include "mccl_ops.h"
 
 using namespace mccl;
 

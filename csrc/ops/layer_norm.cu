@@ -12,6 +12,7 @@
 #include <stdint.h>
 
 #include "mccl.h"
+#include "mccl_ops.h"
 
 namespace {
 

@@ -149,9 +149,14 @@ class ExpertParallelMoE(nn.Module):
     `capacity` slots per step; tokens beyond it are dropped (their output is zero), so the dispatch and the combine
     are all-to-alls of equal blocks."""
 
-    def __init__(self, comm: Communicator, hidden: int, ffn: int, experts_per_rank: int, capacity: int, device=None, dtype=None):
+    def __init__(self, comm: Communicator, hidden: int, ffn: int, experts_per_rank: int, capacity: int, device=None, dtype=None,
+                 fused: bool = False):
         super().__init__()
         self.comm, self.hidden, self.capacity = comm, hidden, capacity
+        # fused: on cuda tensors the dispatch and the combine are single kernels that move each token row straight
+        # between the activation tensor and its slot on the expert's rank (ops/moe.py) instead of pack + all-to-all + unpack
+        self.fused = fused
+        self._buf = self._grad_buf = None
         self.local, self.experts = experts_per_rank, experts_per_rank * comm.size
         self.router = nn.Linear(hidden, self.experts, bias=False, device=device, dtype=dtype)
         self.w_in = nn.Parameter(torch.empty(experts_per_rank, ffn, hidden, device=device, dtype=dtype))
@@ -171,6 +176,18 @@ class ExpertParallelMoE(nn.Module):
         n, e, c, d = self.comm.size, self.local, self.capacity, self.hidden
         expert, gate, slot, keep = self.route(x)
         flat = expert * c + slot                                               # slot in the [experts, capacity] grid
+        if self.fused and x.is_cuda:
+            from ..ops import moe as M
+            if self._buf is None:                                              # collective allocations, first call
+                self._buf = M.ExchangeBuffer(self.comm, e, c, d, x.dtype)
+                self._grad_buf = M.ExchangeBuffer(self.comm, e, c, d, x.dtype)
+            flat32 = torch.where(keep, flat, torch.full_like(flat, -1)).to(torch.int32)
+            recv = M.dispatch(x, flat32, self._buf, self._grad_buf)            # [n (source), e, c, d]
+            tokens = recv.transpose(0, 1).reshape(e, n * c, d)
+            hidden = F.silu(torch.einsum("etd,efd->etf", tokens, self.w_in))
+            out = torch.einsum("etf,edf->etd", hidden, self.w_out)
+            back = out.view(e, n, c, d).transpose(0, 1).contiguous()
+            return M.combine(back, flat32, gate, self._buf, self._grad_buf)
         send = x.new_zeros(self.experts * c, d)
         send = send.index_put((flat[keep],), x[keep])
         recv = PF.all_to_all_rows(send, self.comm)                             # [n (source), e, c, d]

@@ -277,6 +277,36 @@ def parallel_layers_gpu():
     comm.finalize(); comm.destroy()
 
 
+def moe_fused():
+    """The fused dispatch / combine kernels against the pack + all-to-all + unpack form of the same layer: outputs and
+    the gradients of the tokens, the router and the experts, fp32 and bf16, with dropped tokens."""
+    from mccl_b200.parallel import layers as PL
+    comm = make_comm()
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+        hid, ffn, e_loc, cap = 64, 128, 2, 3
+        T = e_loc * WORLD * cap + 5
+        torch.manual_seed(0)
+        a = PL.ExpertParallelMoE(comm, hid, ffn, e_loc, cap, device=DEV, dtype=dtype, fused=False)
+        b = PL.ExpertParallelMoE(comm, hid, ffn, e_loc, cap, device=DEV, dtype=dtype, fused=True)
+        b.load_state_dict(a.state_dict())
+        g = torch.Generator(device="cuda").manual_seed(50 + RANK)
+        x = torch.randn(T, hid, device=DEV, generator=g).to(dtype)
+        tgt = torch.randn(T, hid, device=DEV, generator=g).to(dtype)
+        outs = []
+        for m in (a, b):
+            xi = x.clone().requires_grad_(True)
+            y = m(xi)
+            (y.float() * tgt.float()).sum().backward()
+            outs.append((y.detach().float(), xi.grad.float(), m.router.weight.grad.float(), m.w_in.grad.float(), m.w_out.grad.float()))
+        torch.cuda.synchronize()
+        assert (outs[0][0].abs().sum(-1) == 0).any(), "nothing was dropped"
+        for name, u, v in zip(("y", "dx", "d router", "d w_in", "d w_out"), outs[0], outs[1]):
+            err = ((u - v).abs().max() / (u.abs().max() + 1e-6)).item()
+            assert err < tol, (dtype, name, err)
+    assert canary_ok(comm)
+    comm.finalize(); comm.destroy()
+
+
 def device_timeout():
     """Rank 1 sits out one collective (between steps, nothing of its own in flight).  The others' kernels
     give up after the device time budget, record why in the status word and return; the host reads it."""
