@@ -17,6 +17,7 @@ import torch
 from .. import _lib as L
 from ..comm import Communicator
 from ..ops import gemm as G
+from . import functional as PF
 
 
 class TensorParallelFFN:
@@ -70,3 +71,50 @@ class TensorParallelFFN:
             acc += (hcol @ wd.float().t()).to(torch.bfloat16).float()      # partial sums travel as bf16
         blk = self.tokens // self.n
         return acc[self.comm.rank * blk:(self.comm.rank + 1) * blk]
+
+
+class _FusedMLPFunction(torch.autograd.Function):
+    """Forward through the two fused kernels; backward with the collectives and plain matrix products.  The
+    pre-activation is not kept: the backward pass recomputes it from the gathered input (one extra GEMM) instead of
+    storing a [tokens, ffn / n] tensor per layer."""
+
+    @staticmethod
+    def forward(ctx, x_shard, w_up, w_down, layer):
+        out = layer.forward(x_shard).clone()                       # the layer's buffers are reused by the next call
+        ctx.layer = layer
+        ctx.save_for_backward(layer.x_full.clone(), w_up, w_down)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, w_up, w_down = ctx.saved_tensors
+        comm = ctx.layer.comm
+        dy_full = PF._ag(comm, dy.contiguous())                    # [tokens, hidden]
+        u = (x_full @ w_up.t()).float()
+        sig = torch.sigmoid(u)
+        h = (u * sig).to(x_full.dtype)
+        d_w_down = dy_full.t() @ h
+        dh = (dy_full @ w_down).float()
+        du = (dh * (sig * (1.0 + u * (1.0 - sig)))).to(x_full.dtype)
+        d_w_up = du.t() @ x_full
+        dx = PF._rs(comm, du @ w_up)                               # this rank's rows of the input gradient
+        return dx, d_w_up, d_w_down, None
+
+
+class FusedTensorParallelMLP(torch.nn.Module):
+    """Trainable sequence-parallel SiLU MLP whose forward pass is the pair of fused kernels of TensorParallelFFN
+    (all-gather -> GEMM -> SiLU, GEMM -> reduce-scatter).  Shapes are fixed at construction (the symmetric buffers
+    are sized for them): x [tokens / n, hidden] -> [tokens / n, hidden], bf16, cuda."""
+
+    def __init__(self, comm: Communicator, tokens: int, hidden: int, ffn: int, device=None):
+        super().__init__()
+        n = comm.size
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.w_up = torch.nn.Parameter(torch.randn(ffn // n, hidden, device=dev).mul_(hidden ** -0.5).to(torch.bfloat16))
+        self.w_down = torch.nn.Parameter(torch.randn(hidden, ffn // n, device=dev).mul_(ffn ** -0.5).to(torch.bfloat16))
+        self.layer = TensorParallelFFN(comm, tokens, hidden, ffn, self.w_up.data, self.w_down.data)
+
+    def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
+        # the kernels read the parameters' current storage (an optimizer may have re-pointed .data)
+        self.layer.w_up, self.layer.w_down = self.w_up.data, self.w_down.data
+        return _FusedMLPFunction.apply(x_shard, self.w_up, self.w_down, self.layer)

@@ -307,6 +307,38 @@ def moe_fused():
     comm.finalize(); comm.destroy()
 
 
+def tp_mlp_trainable():
+    """FusedTensorParallelMLP (fused forward kernels, collective backward) against the unfused sequence-parallel MLP
+    with the same weights: output and the gradients of the input and both weight shards."""
+    from mccl_b200.parallel.layers import TensorParallelMLP
+    from mccl_b200.parallel.tp import FusedTensorParallelMLP
+    comm = make_comm()
+    tokens, hidden, ffn = 128 * WORLD * 2, 512, 256 * WORLD
+    torch.manual_seed(5 + RANK)
+    fused = FusedTensorParallelMLP(comm, tokens, hidden, ffn, device=DEV)
+    plain = TensorParallelMLP(comm, hidden, ffn, bias=False, sequence_parallel=True, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        plain.up.weight.copy_(fused.w_up); plain.down.weight.copy_(fused.w_down)
+    g = torch.Generator(device="cuda").manual_seed(70 + RANK)
+    x = torch.randn(tokens // WORLD, hidden, device=DEV, generator=g).to(torch.bfloat16)
+    tgt = torch.randn(tokens // WORLD, hidden, device=DEV, generator=g).to(torch.bfloat16)
+    res = []
+    for m, wu, wd in ((plain, plain.up.weight, plain.down.weight), (fused, fused.w_up, fused.w_down)):
+        for it in range(2):                                     # the second pass reuses flags and buffers
+            wu.grad = wd.grad = None
+            xi = x.clone().requires_grad_(True)
+            y = m(xi)
+            (y.float() * tgt.float()).sum().backward()
+        res.append((y.detach().float(), xi.grad.float(), wu.grad.float(), wd.grad.float()))
+    torch.cuda.synchronize()
+    from mccl_b200.ops import gemm as G
+    assert G.last_error() == 0 and comm.async_error() == L.SUCCESS
+    for name, u, v in zip(("y", "dx", "d w_up", "d w_down"), res[0], res[1]):
+        err = ((u - v).abs().max() / (u.abs().max() + 1e-6)).item()
+        assert err < 3e-2, (name, err)
+    comm.finalize(); comm.destroy()
+
+
 def device_timeout():
     """Rank 1 sits out one collective (between steps, nothing of its own in flight).  The others' kernels
     give up after the device time budget, record why in the status word and return; the host reads it."""
