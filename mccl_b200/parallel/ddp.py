@@ -264,5 +264,31 @@ class DistributedDataParallel(nn.Module):
                     b.gather_event = None
         self._reset()
 
+    # ---- checkpointing
+    def optimizer_state_dict(self) -> dict:
+        """The optimizer's state as host tensors: the step count and, per bucket, the fp32 master weights and the two
+        Adam moments (this rank's slice of them when the optimizer is sharded).  Together with the module's own
+        state_dict it resumes training exactly."""
+        return {"step": self.step_count, "world": self.world, "sharded": self.sharded,
+                "buckets": [{"numel": b.numel, "lo": b.lo, "hi": b.hi, "master": b.master.detach().cpu().clone(),
+                             "exp_avg": b.exp_avg.detach().cpu().clone(), "exp_avg_sq": b.exp_avg_sq.detach().cpu().clone()}
+                            for b in self.buckets]}
+
+    def load_optimizer_state_dict(self, state: dict) -> None:
+        """Restore what optimizer_state_dict returned (same model, bucket size, world size and sharding).  The bf16
+        parameters are rewritten from the master weights, so the module needs no separate load."""
+        if len(state["buckets"]) != len(self.buckets) or state["sharded"] != self.sharded or \
+                (self.sharded and state["world"] != self.world):
+            raise ValueError("the checkpoint was written with a different bucket layout, world size or sharding")
+        self.step_count = int(state["step"])
+        for b, sb in zip(self.buckets, state["buckets"]):
+            if (sb["numel"], sb["lo"], sb["hi"]) != (b.numel, b.lo, b.hi):
+                raise ValueError("bucket layout mismatch")
+            b.master.copy_(sb["master"]); b.exp_avg.copy_(sb["exp_avg"]); b.exp_avg_sq.copy_(sb["exp_avg_sq"])
+            b.param[b.lo:b.hi].copy_(b.master.to(b.param.dtype))
+            if self.sharded:
+                self.comm.all_gather(b.param[b.lo:b.hi], b.param)
+        self._reset()
+
     def bucket_sizes_mb(self) -> List[float]:
         return [b.numel * b.grad.element_size() / (1 << 20) for b in self.buckets]

@@ -66,6 +66,10 @@ def test_ddp_gradient_accumulation():
     assert_all_ok(run_ranks(2, "ddp_accumulate"))
 
 
+def test_ddp_checkpoint_and_resume():
+    assert_all_ok(run_ranks(2, "ddp_checkpoint"))
+
+
 @pytest.mark.parametrize("world", [2, 3])
 def test_ddp_sharded_optimizer(world):
     assert_all_ok(run_ranks(world, "ddp_zero"))
