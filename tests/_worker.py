@@ -297,6 +297,49 @@ def peer_dies():
     comm.abort(); comm.destroy()
 
 
+def recover_smaller():
+    """Recovery as the library defines it (abort, destroy, initialise again): the last rank leaves between two steps,
+    the survivors' next collective fails instead of hanging, they drop the communicator, meet again as a smaller world
+    on a second rendezvous port, restore the optimizer state saved before the failure and keep training in step."""
+    import io
+    import torch
+    from mccl_b200.models.gpt2 import GPT2, GPT2Config
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    comm = make_comm()
+    cfg = GPT2Config.tiny()
+    torch.manual_seed(0)
+    ddp = DistributedDataParallel(GPT2(cfg), comm, bucket_mb=0.25)
+    g = torch.Generator().manual_seed(31 + RANK)
+    t = torch.randint(0, cfg.vocab_size, (2, cfg.seq_len + 1), generator=g)
+    ddp(t[:, :-1], t[:, 1:]).backward(); ddp.step(lr=1e-3)
+    blob = io.BytesIO()
+    torch.save(ddp.optimizer_state_dict(), blob)                   # the checkpoint every rank keeps
+    comm.host_barrier()
+    if RANK == WORLD - 1:
+        os._exit(0)                                                # leaves between steps, nothing in flight
+    time.sleep(0.3)
+    try:
+        ddp(t[:, :-1], t[:, 1:]).backward(); ddp.step(lr=1e-3)
+        raise SystemExit("a step with a dead peer returned success")
+    except mccl.MCCLError as e:
+        assert e.code in (L.SYSTEM_ERROR, L.REMOTE_ERROR), e.code
+    comm.abort(); comm.destroy()
+    small = mccl.Communicator(WORLD - 1, mccl.unique_id_from_env("127.0.0.1", ARGS["port2"]), RANK, transport="tcp")
+    torch.manual_seed(99)
+    again = DistributedDataParallel(GPT2(cfg), small, bucket_mb=0.25)
+    blob.seek(0)
+    again.load_optimizer_state_dict(torch.load(blob))
+    for _ in range(2):
+        again(t[:, :-1], t[:, 1:]).backward(); again.step(lr=1e-3)
+    import hashlib
+    h = hashlib.sha256()
+    for b in again.buckets:
+        h.update(b.param.numpy().tobytes())
+    digests = small.host_all_gather(h.digest())
+    assert all(d == digests[0] for d in digests), "survivors diverged after the restart"
+    small.finalize(); small.destroy()
+
+
 def never_joins():
     """Rank WORLD-1 never calls init: everyone else fails the rendezvous within the deadline."""
     if RANK == WORLD - 1:
