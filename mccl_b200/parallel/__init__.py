@@ -2,6 +2,7 @@
 
     ddp         DistributedDataParallel: gradient buckets in symmetric memory reduced during backward, fused optimizer
                 step, gradient accumulation, sharded optimizer (ZeRO-1), checkpointing
+    fsdp        FullyShardedStack: parameters, gradients and optimizer state sharded per block (ZeRO-3)
     tp          TensorParallelFFN / FusedTensorParallelMLP: the fused all-gather -> GEMM and GEMM -> reduce-scatter kernels
     functional  the collectives as differentiable functions, ring attention
     layers      column / row parallel linear, sequence-parallel MLP, Ulysses and ring attention, expert-parallel MoE

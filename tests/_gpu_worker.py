@@ -268,8 +268,9 @@ def c10d_backend_gpu():
 
 def parallel_layers_gpu():
     """The model-parallel layers and the pipeline schedule on cuda tensors (fp32, collectives through the kernels)."""
-    from _parallel_cases import layers_case, llama_case, pipeline_case
+    from _parallel_cases import fsdp_case, layers_case, llama_case, pipeline_case
     comm = make_comm()
+    fsdp_case(comm, RANK, WORLD, DEV, atol=2e-4)
     layers_case(comm, RANK, WORLD, DEV, atol=2e-4)
     pipeline_case(comm, RANK, WORLD, DEV, atol=1e-5)
     llama_case(comm, RANK, WORLD, DEV, atol=2e-4)

@@ -169,3 +169,29 @@ def llama_case(comm, RANK, WORLD, dev, atol=2e-5):
                 want = want[:, r * m:(r + 1) * m]
             assert torch.allclose(p.grad, want, atol=atol, rtol=50 * atol), (sp, name, (p.grad - want).abs().max().item())
     one.destroy()
+
+
+def fsdp_case(comm, RANK, WORLD, dev, atol=2e-5):
+    """Fully sharded blocks (parameters gathered just in time, gradients reduce-scattered, optimizer on the shards)
+    follow single-process training on the concatenated batch; the state per rank is 1/world."""
+    import torch
+    import torch.nn as nn
+    from mccl_b200.parallel.fsdp import FullyShardedStack
+    def make():
+        torch.manual_seed(0)
+        return [m.to(dev) for m in [nn.Sequential(nn.Linear(24, 40), nn.Tanh(), nn.Linear(40, 24)) for _ in range(3)] + [nn.Sequential(nn.Linear(24, 7))]]
+    fsdp = FullyShardedStack(make(), comm)
+    ref = nn.Sequential(*make())
+    assert sum(p.numel() for p in fsdp.shard_parameters()) * WORLD <= sum(p.numel() for p in ref.parameters()) + 4 * 8 * WORLD * 8
+    o1, o2 = torch.optim.Adam(fsdp.shard_parameters(), lr=1e-2), torch.optim.Adam(ref.parameters(), lr=1e-2)
+    g = torch.Generator().manual_seed(8)
+    for step in range(4):
+        x, y = torch.randn(3 * WORLD, 24, generator=g).to(dev), torch.randn(3 * WORLD, 7, generator=g).to(dev)
+        o1.zero_grad(); o2.zero_grad()
+        torch.nn.functional.mse_loss(fsdp(x[3 * RANK:3 * RANK + 3]), y[3 * RANK:3 * RANK + 3]).backward()
+        torch.nn.functional.mse_loss(ref(x), y).backward()
+        o1.step(); o2.step()
+    for flat, block in zip(fsdp.full_state(), ref):
+        want = torch.cat([torch.nn.functional.pad(p.detach().reshape(-1), (0, (-p.numel()) % 8)) for p in block.parameters()])
+        got = flat[: want.numel()]
+        assert torch.allclose(got, want, atol=atol, rtol=50 * atol), (got - want).abs().max().item()

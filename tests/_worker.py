@@ -622,6 +622,14 @@ def ddp_checkpoint():
     comm.finalize(); comm.destroy()
 
 
+def fsdp_stack():
+    import torch
+    from _parallel_cases import fsdp_case
+    comm = make_comm()
+    fsdp_case(comm, RANK, WORLD, torch.device("cpu"))
+    comm.finalize(); comm.destroy()
+
+
 def ddp_accumulate():
     """Two micro-batches (the first under no_sync) give the gradient of the concatenated batch."""
     import torch

@@ -66,6 +66,11 @@ def test_ddp_gradient_accumulation():
     assert_all_ok(run_ranks(2, "ddp_accumulate"))
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_fully_sharded_stack(world):
+    assert_all_ok(run_ranks(world, "fsdp_stack"))
+
+
 def test_ddp_checkpoint_and_resume():
     assert_all_ok(run_ranks(2, "ddp_checkpoint"))
 
