@@ -55,6 +55,7 @@ class ExchangeBuffer:
 
 def _scatter(buf: ExchangeBuffer, x: torch.Tensor, flat: torch.Tensor, scale: Optional[torch.Tensor]) -> None:
     assert x.is_cuda and x.is_contiguous() and x.dtype == buf.dtype and flat.dtype == torch.int32 and flat.is_contiguous()
+    assert x.dim() == 2 and x.shape[1] == buf.d and flat.numel() == x.shape[0] and (scale is None or (scale.numel() == x.shape[0] and scale.dtype == torch.float32))
     sp = scale.data_ptr() if scale is not None else None
     L.check(_lib().mcclMoeScatter(C.c_void_p(buf.comm.handle), x.data_ptr(), flat.data_ptr(), sp, buf.data.data_ptr(), x.shape[0],
                                   buf.row_bytes, buf.e, buf.c, _DT[buf.dtype], _stream(x)), "mcclMoeScatter")
@@ -62,6 +63,8 @@ def _scatter(buf: ExchangeBuffer, x: torch.Tensor, flat: torch.Tensor, scale: Op
 
 
 def _gather(buf: ExchangeBuffer, flat: torch.Tensor, scale: Optional[torch.Tensor], n_tokens: int) -> torch.Tensor:
+    assert flat.dtype == torch.int32 and flat.is_contiguous() and flat.numel() == n_tokens
+    assert scale is None or (scale.numel() == n_tokens and scale.dtype == torch.float32 and scale.is_contiguous())
     out = torch.empty(n_tokens, buf.d, device=buf.data.device, dtype=buf.dtype)
     sp = scale.data_ptr() if scale is not None else None
     L.check(_lib().mcclMoeGather(C.c_void_p(buf.comm.handle), buf.data.data_ptr(), flat.data_ptr(), sp, out.data_ptr(), n_tokens,
