@@ -2,9 +2,9 @@
 every token row straight between its place in the local activation tensor and its slot in the expert's rank, over
 NVLink, instead of packing a send buffer, running an all-to-all and unpacking.
 
-    buf = ExchangeBuffer(comm, experts_per_rank, capacity, hidden, dtype)       # symmetric memory, collective
-    tokens_at_experts = dispatch(x, flat, buf)                                   # [n, e, c, d] view of the buffer
-    y = combine(expert_out, flat, gate, buf2)                                    # [T, d]
+    buf, gbuf = (ExchangeBuffer(comm, experts_per_rank, capacity, hidden, dtype) for _ in range(2))   # symmetric, collective
+    tokens_at_experts = dispatch(x, flat, buf, gbuf)                             # [n, e, c, d]: a copy of the filled buffer
+    y = combine(expert_out, flat, gate, buf, gbuf)                               # [T, d]; gbuf carries gradients in backward
 
 Both are differentiable: the backward pass of a dispatch is a combine of the gradient buffer and vice versa (the
 gate's gradient is the dot product of the output gradient with the unscaled expert row).
