@@ -33,7 +33,9 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="mccl", choices=["mccl", "reference", "nccl"])
+    ap.add_argument("--impl", default="mccl", choices=["mccl", "reference", "nccl", "c10d"],
+                    help="mccl: this library's DDP wrapper; nccl: torch DDP over NCCL; c10d: torch DDP over this library's "
+                         "torch.distributed backend; reference: the reference library (unavailable here)")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "tiny"])
@@ -101,7 +103,10 @@ def main() -> int:
             return loss
     else:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev) if world > 1 else None
+        if args.impl == "c10d":
+            import mccl_b200.c10d  # noqa: F401  (registers the "mccl" backend)
+        if world > 1:
+            dist.init_process_group("mccl" if args.impl == "c10d" else "nccl", **({} if args.impl == "c10d" else {"device_id": dev}))
         net = model
         if world > 1:
             net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
@@ -126,7 +131,7 @@ def main() -> int:
         torch.cuda.synchronize()
         if comm is not None:
             comm.host_barrier()
-        elif args.impl == "nccl" and world > 1:
+        elif args.impl in ("nccl", "c10d") and world > 1:
             import torch.distributed as dist
             dist.barrier()
         torch.cuda.synchronize()
@@ -158,7 +163,7 @@ def main() -> int:
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     clocks = sampler.stop() if sampler is not None else {}
 
-    if args.impl == "nccl" and world > 1:
+    if args.impl in ("nccl", "c10d") and world > 1:
         import torch.distributed as dist
         t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -214,7 +219,7 @@ def main() -> int:
         comm.destroy()
     if rank == 0:
         print(json.dumps(out), flush=True)
-    if args.impl == "nccl" and world > 1:
+    if args.impl in ("nccl", "c10d") and world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
     return 0
