@@ -4,6 +4,7 @@
 // is recorded in comm->lastAlgo.  Inside a group the call is recorded and issued by GroupEnd.
 // Parity: src/coll/coll.cc:16-106 of the reference.
 #include <cstring>
+#include <mutex>
 
 #include <nvtx3/nvToolsExt.h>
 
@@ -18,9 +19,16 @@ namespace {
 
 // An NVTX range around the host side of every collective ("mcclAllReduce", ...), visible to any attached
 // profiler; with none attached the header-only NVTX stubs return at once.  MCCL_NVTX=0 removes the calls.
+// The header-only NVTX layer installs its entry points on first use without synchronisation; doing that first use
+// once, under call_once, keeps concurrent first calls from different threads from racing on its table.
+void nvtxWarmUp() {
+  static std::once_flag once;
+  std::call_once(once, [] { nvtxRangePushA("mcclInit"); nvtxRangePop(); });
+}
+
 struct NvtxRange {
   bool on;
-  explicit NvtxRange(const char* name) : on(mcclParamNvtx() != 0) { if (on) nvtxRangePushA(name); }
+  explicit NvtxRange(const char* name) : on(mcclParamNvtx() != 0) { if (on) { nvtxWarmUp(); nvtxRangePushA(name); } }
   ~NvtxRange() { if (on) nvtxRangePop(); }
 };
 
