@@ -76,6 +76,9 @@ class _Work(_WorkBase):
 
 
 class MCCLBackend(dist.ProcessGroup):
+    """The c10d process group: every method maps one torch.distributed call onto the library's collective of the same
+    name and returns a work object whose wait() / future carry the stream dependency."""
+
     def __init__(self, store, rank: int, size: int, timeout=None):
         super().__init__(rank, size)
         self._store = store

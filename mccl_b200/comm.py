@@ -62,6 +62,7 @@ def _stream_of(buf, stream):
 
 
 def get_unique_id() -> bytes:
+    """mcclGetUniqueId: 128 bytes to create on one rank and hand to the others (it names a listener of this process)."""
     uid = L.UniqueId()
     L.check(L.load().mcclGetUniqueId(C.byref(uid)), "mcclGetUniqueId")
     return C.string_at(C.byref(uid), 128)      # the raw 128 bytes (a c_char array would stop at the first NUL)
@@ -74,12 +75,14 @@ def unique_id_from_env(ip: str, port: int) -> bytes:
 
 
 def set_forced_algo(algo) -> None:
+    """Force one algorithm ("ring", "tree", "oneshot", "twoshot", "nvls") for this thread's next calls; "auto" restores the tuner."""
     a = L.ALGOS[algo] if isinstance(algo, str) else int(algo)
     L.check(L.load().mcclSetForcedAlgo(a), "mcclSetForcedAlgo")
 
 
 @contextmanager
 def forced_algo(algo):
+    """`with forced_algo("ring"): ...` — set_forced_algo for the duration of the block."""
     set_forced_algo(algo)
     try:
         yield
@@ -89,6 +92,7 @@ def forced_algo(algo):
 
 @contextmanager
 def group():
+    """mcclGroupStart / mcclGroupEnd around the block: the calls inside are recorded and issued together at its end."""
     lib = L.load()
     L.check(lib.mcclGroupStart())
     try:
@@ -133,6 +137,7 @@ class Communicator:
     # ---- queries
     @property
     def handle(self) -> int:
+        """The mcclComm_t as an integer (for ctypes calls into the C API)."""
         return self._h.value
 
     def _q(self, fn) -> int:
@@ -142,52 +147,65 @@ class Communicator:
 
     @property
     def rank(self) -> int:
+        """This process's rank in the communicator."""
         return self._q(self._lib.mcclCommUserRank)
 
     @property
     def size(self) -> int:
+        """Number of ranks."""
         return self._q(self._lib.mcclCommCount)
 
     @property
     def device(self) -> int:
+        """CUDA device ordinal of the cuda transport (-1 on tcp)."""
         return self._q(self._lib.mcclCommDevice)
 
     @property
     def transport(self) -> str:
+        """"tcp" or "cuda"."""
         return self._lib.mcclCommTransport(self._h).decode()
 
     @property
     def nvls(self) -> bool:
+        """Whether NVSwitch multicast (NVLS) is mapped for this communicator."""
         return bool(self._q(self._lib.mcclCommNvlsEnabled))
 
     @property
     def last_algo(self) -> str:
+        """Algorithm the most recent collective ran with ("ring", "tree", "oneshot", "twoshot", "nvls")."""
         return L.ALGO_NAMES.get(self._q(self._lib.mcclCommLastAlgo), "none")
 
     @property
     def launch_count(self) -> int:
+        """Device kernels this communicator has launched so far."""
         v = C.c_uint64()
         L.check(self._lib.mcclCommLaunchCount(self._h, C.byref(v)))
         return v.value
 
     def guards_intact(self) -> bool:
+        """Debug aid: the guard word behind the device flag arrays is untouched."""
         return bool(self._q(self._lib.mcclCommCheckGuards))
 
     def async_error(self) -> int:
+        """mcclCommGetAsyncError: 0, mcclInProgress while non-blocking tcp work runs, or the latched fatal error."""
         return self._q(self._lib.mcclCommGetAsyncError)
 
     def pick_algo(self, coll: str, nbytes: int, dtype: int = L.FLOAT32, op: str = "sum") -> str:
+        """The algorithm the tuner would choose for this call."""
         a = C.c_int()
         L.check(self._lib.mcclCommPickAlgo(self._h, L.COLLS[coll], nbytes, dtype, L.OPS[op], C.byref(a)))
         return L.ALGO_NAMES[a.value]
 
     def set_max_ctas(self, n: int) -> None:
+        """Cap the CTAs of every collective kernel (0 = tuner default), leaving SMs to overlapped compute."""
         L.check(self._lib.mcclCommSetMaxCtas(self._h, n))
 
     def set_ctas(self, n: int) -> None:
+        """Tuning aid: exactly n CTAs for every collective kernel (0 = planner's choice)."""
         L.check(self._lib.mcclCommSetCtas(self._h, n))
 
     def topo_xml(self) -> str:
+        """Topology, per-algorithm plans and tuner constants as XML."""
         p = C.c_void_p()
         L.check(self._lib.mcclCommTopoXml(self._h, C.byref(p)))
         s = C.string_at(p).decode()
@@ -196,6 +214,8 @@ class Communicator:
 
     # ---- lifecycle
     def split(self, color: int, key: int = 0, blocking: Optional[bool] = None) -> Optional["Communicator"]:
+        """mcclCommSplit: collective over this communicator; ranks with one color form a new communicator ordered by
+        (key, rank); color mccl_b200.SPLIT_NOCOLOR returns None."""
         h = C.c_void_p()
         cfg = None
         if blocking is not None:
@@ -206,15 +226,19 @@ class Communicator:
         return Communicator(0, b"", 0, _handle=h.value)
 
     def synchronize(self) -> None:
+        """Wait for queued non-blocking tcp work (the cuda transport is synchronised through its stream)."""
         L.check(self._lib.mcclCommSynchronize(self._h), "mcclCommSynchronize")
 
     def finalize(self) -> None:
+        """Drain outstanding work and pass a barrier; call before destroy on a healthy communicator."""
         L.check(self._lib.mcclCommFinalize(self._h), "mcclCommFinalize")
 
     def abort(self) -> None:
+        """Unblock every thread parked in this communicator and refuse further work; frees nothing."""
         L.check(self._lib.mcclCommAbort(self._h), "mcclCommAbort")
 
     def destroy(self) -> None:
+        """Free the communicator and its symmetric memory."""
         _live.discard(self)
         if self._h:
             self._sym.clear()
@@ -222,9 +246,11 @@ class Communicator:
             self._h = C.c_void_p()
 
     def host_barrier(self) -> None:
+        """Barrier over the control plane (host side only; says nothing about GPU work)."""
         L.check(self._lib.mcclCommHostBarrier(self._h), "mcclCommHostBarrier")
 
     def host_all_gather(self, payload: bytes) -> list:
+        """All-gather of equal-size byte strings over the control plane."""
         n = self.size
         out = C.create_string_buffer(len(payload) * n)
         L.check(self._lib.mcclCommHostAllGather(self._h, payload, out, len(payload)), "mcclCommHostAllGather")
@@ -233,46 +259,55 @@ class Communicator:
 
     # ---- collectives
     def all_reduce(self, send, recv=None, op: str = "sum", dtype: Optional[int] = None, stream=None) -> None:
+        """recv (default: in place) = op over the ranks' `send`; torch tensors, numpy arrays, or raw pointers with `dtype`."""
         recv = send if recv is None else recv
         sp, cnt, dt, _ = _describe(send, dtype)
         rp, _, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclAllReduce(self._h, sp, rp, cnt, dt, L.OPS[op], _stream_of(send, stream)), "mcclAllReduce")
 
     def all_gather(self, send, recv, dtype: Optional[int] = None, stream=None) -> None:
+        """recv = the ranks' `send` concatenated in rank order (`send` may be this rank's slot of `recv`)."""
         sp, cnt, dt, _ = _describe(send, dtype)
         rp, _, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclAllGather(self._h, sp, rp, cnt, dt, _stream_of(send, stream)), "mcclAllGather")
 
     def reduce_scatter(self, send, recv, op: str = "sum", dtype: Optional[int] = None, stream=None) -> None:
+        """recv = block `rank` of op over the ranks' `send` (n blocks of recv's size)."""
         sp, _, dt, _ = _describe(send, dtype)
         rp, cnt, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclReduceScatter(self._h, sp, rp, cnt, dt, L.OPS[op], _stream_of(send, stream)),
                 "mcclReduceScatter")
 
     def broadcast(self, send, recv, root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
+        """recv on every rank = the root's `send` (may be None elsewhere)."""
         rp, cnt, dt, _ = _describe(recv, dtype)
         sp = _describe(send, dtype)[0] if send is not None else None
         L.check(self._lib.mcclBroadcast(self._h, sp, rp, cnt, dt, root, _stream_of(recv, stream)), "mcclBroadcast")
 
     def reduce(self, send, recv, op: str = "sum", root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
+        """The root's recv = op over the ranks' `send` (`recv` may be None elsewhere)."""
         sp, cnt, dt, _ = _describe(send, dtype)
         rp = _describe(recv, dtype)[0] if recv is not None else None
         L.check(self._lib.mcclReduce(self._h, sp, rp, cnt, dt, L.OPS[op], root, _stream_of(send, stream)), "mcclReduce")
 
     def all_to_all(self, send, recv, dtype: Optional[int] = None, stream=None) -> None:
+        """Block j of `send` goes to rank j; block i of `recv` came from rank i (equal blocks)."""
         sp, cnt, dt, _ = _describe(send, dtype)
         rp, _, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclAllToAll(self._h, sp, rp, cnt // self.size, dt, _stream_of(send, stream)), "mcclAllToAll")
 
     def send(self, buf, peer: int, dtype: Optional[int] = None, stream=None) -> None:
+        """Send `buf` to `peer`; inside `with mccl_b200.group():` it is batched with the other calls."""
         p, cnt, dt, _ = _describe(buf, dtype)
         L.check(self._lib.mcclSend(self._h, p, cnt, dt, peer, _stream_of(buf, stream)), "mcclSend")
 
     def recv(self, buf, peer: int, dtype: Optional[int] = None, stream=None) -> None:
+        """Receive into `buf` from `peer`."""
         p, cnt, dt, _ = _describe(buf, dtype)
         L.check(self._lib.mcclRecv(self._h, p, cnt, dt, peer, _stream_of(buf, stream)), "mcclRecv")
 
     def recv_any(self, buf, dtype: Optional[int] = None, stream=None) -> int:
+        """Receive into `buf` from whichever rank sends first; returns its rank."""
         p, cnt, dt, _ = _describe(buf, dtype)
         src = C.c_int(-1)
         L.check(self._lib.mcclRecvAny(self._h, p, cnt, dt, C.byref(src), _stream_of(buf, stream)), "mcclRecvAny")

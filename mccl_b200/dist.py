@@ -36,41 +36,50 @@ def init_process_group(transport: Optional[str] = None, port_offset: int = 23, b
 
 
 def default_group() -> Communicator:
+    """The communicator init_process_group created."""
     if _default is None:
         raise RuntimeError("call mccl_b200.dist.init_process_group() first")
     return _default
 
 
 def get_rank() -> int:
+    """Rank in the default communicator."""
     return default_group().rank
 
 
 def get_world_size() -> int:
+    """Size of the default communicator."""
     return default_group().size
 
 
 def all_reduce(tensor, op: str = "sum") -> None:
+    """In-place all-reduce on the default communicator."""
     default_group().all_reduce(tensor, op=op)
 
 
 def broadcast(tensor, src: int = 0) -> None:
+    """In-place broadcast from rank `src`."""
     g = default_group()
     g.broadcast(tensor if g.rank == src else None, tensor, root=src)
 
 
 def all_gather_into_tensor(out, inp) -> None:
+    """out = every rank's `inp`, concatenated in rank order."""
     default_group().all_gather(inp, out)
 
 
 def reduce_scatter_tensor(out, inp, op: str = "sum") -> None:
+    """out = block `rank` of the reduction of every rank's `inp`."""
     default_group().reduce_scatter(inp, out, op=op)
 
 
 def barrier() -> None:
+    """Host-side barrier over the control plane."""
     default_group().host_barrier()
 
 
 def destroy_process_group() -> None:
+    """Finalize and destroy the default communicator."""
     global _default
     if _default is not None:
         _default.finalize()

@@ -77,6 +77,9 @@ class Block(nn.Module):
 
 
 class GPT2(nn.Module):
+    """Decoder-only transformer with learned positions, pre-LayerNorm blocks and a tied output projection;
+    forward(idx, targets) returns the mean cross-entropy, forward(idx) the logits."""
+
     def __init__(self, cfg: GPT2Config, fused_loss: bool = True):
         super().__init__()
         self.cfg = cfg

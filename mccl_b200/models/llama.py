@@ -45,6 +45,8 @@ class LlamaConfig:
 
 
 class RMSNorm(nn.Module):
+    """x / rms(x) * weight, statistics in fp32."""
+
     def __init__(self, dim: int, eps: float):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(dim))
@@ -67,6 +69,8 @@ def rope(x: torch.Tensor, theta: float) -> torch.Tensor:
 
 
 class Block(nn.Module):
+    """Pre-norm attention + SwiGLU block holding 1/n of every projection."""
+
     def __init__(self, cfg: LlamaConfig, comm: Communicator, sp: bool):
         super().__init__()
         n = comm.size
@@ -100,6 +104,9 @@ class Block(nn.Module):
 
 
 class Llama(nn.Module):
+    """Tensor-parallel Llama-style decoder on `comm`; forward(idx, targets) returns the mean cross-entropy over all
+    tokens (the same value on every rank), forward(idx) the logits of this rank's tokens."""
+
     def __init__(self, cfg: LlamaConfig, comm: Communicator, sequence_parallel: bool = False):
         super().__init__()
         self.cfg, self.comm, self.sp = cfg, comm, sequence_parallel and comm.size > 1

@@ -54,6 +54,9 @@ class _Bucket:
 
 
 class DistributedDataParallel(nn.Module):
+    """Wraps a module for data-parallel training over `comm`: gradients live in bucket buffers that are averaged over the
+    ranks while backward runs; `step()` applies the fused (optionally sharded, optionally norm-clipped) AdamW update."""
+
     def __init__(self, module: nn.Module, comm: Optional[Communicator] = None, bucket_mb: Optional[float] = None,
                  overlap: bool = True, comm_ctas: int = 16, weight_decay: float = 0.1, betas=(0.9, 0.95), eps: float = 1e-8,
                  shard_optimizer: bool = False):
@@ -291,4 +294,5 @@ class DistributedDataParallel(nn.Module):
         self._reset()
 
     def bucket_sizes_mb(self) -> List[float]:
+        """Size of every gradient bucket in MB, in launch order."""
         return [b.numel * b.grad.element_size() / (1 << 20) for b in self.buckets]

@@ -81,6 +81,8 @@ class _ShardedBlock:
 
 
 class FullyShardedStack(nn.Module):
+    """A stack of blocks whose parameters, gradients and optimizer state are sharded over the ranks (ZeRO stage 3)."""
+
     def __init__(self, blocks: Iterable[nn.Module], comm: Communicator):
         super().__init__()
         self.blocks = nn.ModuleList(list(blocks))

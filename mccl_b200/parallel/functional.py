@@ -113,6 +113,7 @@ def reduce_scatter_rows(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
 
 
 def all_reduce_sum(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
+    """Sum over the ranks; the gradient passes through unchanged (every rank uses the result)."""
     return x if comm.size == 1 else _AllReduceSum.apply(x, comm)
 
 

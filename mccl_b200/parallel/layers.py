@@ -44,6 +44,7 @@ class ColumnParallelLinear(nn.Module):
 
     @torch.no_grad()
     def load_full(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        """Copy this rank's rows of a full [out_features, in_features] weight (and bias)."""
         r, m = self.comm.rank, self.out_features // self.comm.size
         self.weight.copy_(weight[r * m:(r + 1) * m])
         if self.bias is not None and bias is not None:
@@ -72,6 +73,7 @@ class RowParallelLinear(nn.Module):
 
     @torch.no_grad()
     def load_full(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        """Copy this rank's columns of a full [out_features, in_features] weight (and the whole bias)."""
         r, m = self.comm.rank, self.in_features // self.comm.size
         self.weight.copy_(weight[:, r * m:(r + 1) * m])
         if self.bias is not None and bias is not None:

@@ -24,6 +24,8 @@ from ..comm import Communicator, group
 
 
 class PipelineStage:
+    """This rank's stage of a pipeline-parallel model and the 1F1B schedule that drives it."""
+
     def __init__(self, comm: Communicator, module: nn.Module, act_shape: Sequence[int], dtype=torch.float32, device=None):
         self.comm, self.module = comm, module
         self.stage, self.stages = comm.rank, comm.size

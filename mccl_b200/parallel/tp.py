@@ -21,6 +21,9 @@ from . import functional as PF
 
 
 class TensorParallelFFN:
+    """Forward-only SiLU FFN on the two fused kernels (all-gather -> GEMM -> SiLU, GEMM -> reduce-scatter); owns the
+    symmetric buffers for one fixed (tokens, hidden, ffn) shape."""
+
     def __init__(self, comm: Communicator, tokens: int, hidden: int, ffn: int, w_up: torch.Tensor, w_down: torch.Tensor):
         n = comm.size
         if not G.supported(tokens, ffn // n, hidden, n) or not G.supported(tokens, hidden, ffn // n, n):
