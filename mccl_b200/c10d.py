@@ -207,10 +207,17 @@ class MCCLBackend(dist.ProcessGroup):
         return self._done(outputs, outputs[0], s)
 
     def alltoall_base(self, out: torch.Tensor, inp: torch.Tensor, out_splits, in_splits, opts=None) -> _Work:
-        if out_splits or in_splits:
-            raise NotImplementedError("the mccl backend exchanges equal blocks (no split sizes)")
         comm, s = self._enter(inp)
-        comm.all_to_all(self._flat(inp), self._flat(out), stream=s)
+        if out_splits or in_splits:
+            # split sizes count rows of dim 0
+            row_in = inp.numel() // max(inp.shape[0], 1) if inp.dim() else 1
+            row_out = out.numel() // max(out.shape[0], 1) if out.dim() else 1
+            n = self._size
+            ins = list(in_splits) if in_splits else [inp.shape[0] // n] * n
+            outs = list(out_splits) if out_splits else [out.shape[0] // n] * n
+            comm.all_to_all_v(self._flat(inp), [c * row_in for c in ins], self._flat(out), [c * row_out for c in outs], stream=s)
+        else:
+            comm.all_to_all(self._flat(inp), self._flat(out), stream=s)
         return self._done(out, out, s)
 
     def alltoall(self, outputs: List[torch.Tensor], inputs: List[torch.Tensor], opts=None) -> _Work:

@@ -296,6 +296,30 @@ class Communicator:
         rp, _, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclAllToAll(self._h, sp, rp, cnt // self.size, dt, _stream_of(send, stream)), "mcclAllToAll")
 
+    def all_to_all_v(self, send, send_counts, recv, recv_counts, stream=None) -> None:
+        """All-to-all with a different element count per peer: `send_counts[j]` elements of flat `send` (consecutive
+        segments, rank order) go to rank j, `recv_counts[i]` elements arrive from rank i into consecutive segments of
+        flat `recv`.  Issued as one group of Send / Recv pairs (plus a local copy of the own segment)."""
+        n, r = self.size, self.rank
+        if len(send_counts) != n or len(recv_counts) != n:
+            raise ValueError("one count per rank is required")
+        so = [0] * (n + 1)
+        ro = [0] * (n + 1)
+        for i in range(n):
+            so[i + 1] = so[i] + int(send_counts[i])
+            ro[i + 1] = ro[i] + int(recv_counts[i])
+        if int(send_counts[r]) != int(recv_counts[r]):
+            raise ValueError("the segment a rank keeps must have the same size on both sides")
+        if send_counts[r]:
+            recv[ro[r]:ro[r + 1]] = send[so[r]:so[r + 1]]
+        with group():
+            for i in range(1, n):
+                dst, src = (r + i) % n, (r - i) % n
+                if send_counts[dst]:
+                    self.send(send[so[dst]:so[dst + 1]], dst, stream=stream)
+                if recv_counts[src]:
+                    self.recv(recv[ro[src]:ro[src + 1]], src, stream=stream)
+
     def send(self, buf, peer: int, dtype: Optional[int] = None, stream=None) -> None:
         """Send `buf` to `peer`; inside `with mccl_b200.group():` it is batched with the other calls."""
         p, cnt, dt, _ = _describe(buf, dtype)

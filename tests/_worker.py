@@ -476,6 +476,11 @@ def c10d_backend():
     a2a = torch.empty(2 * n)
     dist.all_to_all_single(a2a, torch.arange(2 * n, dtype=torch.float32) + 100 * RANK)
     assert torch.equal(a2a, torch.cat([torch.arange(2 * RANK, 2 * RANK + 2, dtype=torch.float32) + 100 * s for s in range(n)]))
+    # unequal splits: rank r sends (j + 1) rows to rank j and receives (r + 1) rows from everyone
+    rows_in = torch.cat([torch.full((j + 1, 3), float(100 * RANK + j)) for j in range(n)])
+    rows_out = torch.empty(n * (RANK + 1), 3)
+    dist.all_to_all_single(rows_out, rows_in, output_split_sizes=[RANK + 1] * n, input_split_sizes=[j + 1 for j in range(n)])
+    assert torch.equal(rows_out, torch.cat([torch.full((RANK + 1, 3), float(100 * s + RANK)) for s in range(n)]))
     if RANK == 0:
         dist.send(torch.full((9,), 3.5), dst=1)
     elif RANK == 1:
