@@ -236,6 +236,54 @@ class MCCLBackend(dist.ProcessGroup):
             flat_in.record_stream(s); flat_out.record_stream(s)
         return self._done(outputs, inputs[0], s)
 
+    def gather(self, outputs: List[List[torch.Tensor]], inputs: List[torch.Tensor], opts=None) -> _Work:
+        root = opts.rootRank if opts is not None else 0
+        inp = inputs[0]
+        comm, s = self._enter(inp)
+        if self._rank == root:
+            bufs = [torch.empty_like(inp) for _ in range(self._size)]
+            from .comm import group
+            with group():
+                for p in range(self._size):
+                    if p != root:
+                        comm.recv(self._flat(bufs[p]), p, stream=s)
+            ctx = torch.cuda.stream(s) if s is not None else _NullCtx()
+            with ctx:
+                for p, o in enumerate(outputs[0]):
+                    o.copy_(inp if p == root else bufs[p])
+            if s is not None:
+                for b in bufs:
+                    b.record_stream(s)
+        else:
+            comm.send(self._flat(inp.contiguous()), root, stream=s)
+        return self._done(outputs, inp, s)
+
+    def scatter(self, outputs: List[torch.Tensor], inputs: List[List[torch.Tensor]], opts=None) -> _Work:
+        root = opts.rootRank if opts is not None else 0
+        out = outputs[0]
+        comm, s = self._enter(out)
+        if self._rank == root:
+            from .comm import group
+            srcs = [t.contiguous() for t in inputs[0]]
+            with group():
+                for p in range(self._size):
+                    if p != root:
+                        comm.send(self._flat(srcs[p]), p, stream=s)
+            ctx = torch.cuda.stream(s) if s is not None else _NullCtx()
+            with ctx:
+                out.copy_(srcs[root])
+            if s is not None:
+                for t in srcs:
+                    t.record_stream(s)
+        else:
+            comm.recv(self._flat(out), root, stream=s)
+        return self._done(outputs, out, s)
+
+    def reduce_scatter_tensor_coalesced(self, outputs, inputs, opts=None) -> _Work:
+        for o, i in zip(outputs, inputs):
+            w = self._reduce_scatter_base(o, i, opts)
+        return w
+
     def send(self, tensors: List[torch.Tensor], dst: int, tag: int = 0) -> _Work:
         for t in tensors:
             comm, s = self._enter(t)

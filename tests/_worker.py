@@ -476,6 +476,12 @@ def c10d_backend():
     a2a = torch.empty(2 * n)
     dist.all_to_all_single(a2a, torch.arange(2 * n, dtype=torch.float32) + 100 * RANK)
     assert torch.equal(a2a, torch.cat([torch.arange(2 * RANK, 2 * RANK + 2, dtype=torch.float32) + 100 * s for s in range(n)]))
+    got = [torch.empty(5) for _ in range(n)] if RANK == n - 1 else None
+    dist.gather(torch.full((5,), float(RANK)), got, dst=n - 1)
+    assert RANK != n - 1 or all(torch.all(t == float(p)) for p, t in enumerate(got))
+    piece = torch.empty(4)
+    dist.scatter(piece, [torch.full((4,), 10.0 + p) for p in range(n)] if RANK == 0 else None, src=0)
+    assert torch.all(piece == 10.0 + RANK)
     # unequal splits: rank r sends (j + 1) rows to rank j and receives (r + 1) rows from everyone
     rows_in = torch.cat([torch.full((j + 1, 3), float(100 * RANK + j)) for j in range(n)])
     rows_out = torch.empty(n * (RANK + 1), 3)
