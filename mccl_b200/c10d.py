@@ -332,6 +332,22 @@ class MCCLBackend(dist.ProcessGroup):
         for comm in self._comms.values():
             comm.abort()
 
+    # The base class keeps a group's name inside its registered C++ backends; a process group written in Python has
+    # none, so the name torch assigns is kept here (DeviceMesh and the functional collectives look groups up by it).
+    def _set_group_name(self, name: str) -> None:
+        self._name = name
+
+    @property
+    def group_name(self) -> str:
+        return getattr(self, "_name", "")
+
+    def _set_group_desc(self, desc: str) -> None:
+        self._desc = desc
+
+    @property
+    def group_desc(self) -> str:
+        return getattr(self, "_desc", "")
+
     def _get_backend_name(self) -> str:
         return "mccl"
 

@@ -504,6 +504,16 @@ def c10d_backend():
     with pytest_raises(ValueError):
         dist.all_reduce(torch.ones(3, dtype=torch.int32), op=dist.ReduceOp.BXOR)
 
+    # DTensor on a device mesh over the backend: redistribution (all-gather) and a sharded matmul (partial sums reduced)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Replicate, Shard, distribute_tensor
+    mesh = init_device_mesh("cpu", (n,))
+    torch.manual_seed(0)
+    full, w = torch.randn(4 * n, 2 * n), torch.randn(2 * n, 5)
+    assert torch.equal(distribute_tensor(full, mesh, [Shard(0)]).redistribute(mesh, [Replicate()]).to_local(), full)
+    y = torch.matmul(distribute_tensor(full, mesh, [Shard(1)]), distribute_tensor(w, mesh, [Shard(0)]))
+    assert torch.allclose(y.redistribute(mesh, [Replicate()]).to_local(), full @ w, atol=1e-5)
+
     # torch DDP on top of the backend
     torch.manual_seed(0)
     net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
