@@ -528,6 +528,22 @@ def c10d_backend():
         o2.zero_grad(); torch.nn.functional.mse_loss(ref(x), y).backward(); o2.step()
     for p1, p2 in zip(net.parameters(), ref.parameters()):
         assert torch.allclose(p1, p2, atol=1e-6, rtol=1e-5), (p1 - p2).abs().max().item()
+
+    # torch FSDP2 (fully_shard: parameters as DTensors, all-gather / reduce-scatter per layer) on top of the backend
+    from torch.distributed.fsdp import fully_shard
+    torch.manual_seed(1)
+    fs = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+    ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+    ref.load_state_dict(fs.state_dict())
+    for layer in (fs[0], fs[2]):
+        fully_shard(layer, mesh=mesh)
+    fully_shard(fs, mesh=mesh)
+    o1, o2 = torch.optim.SGD(fs.parameters(), lr=0.1), torch.optim.SGD(ref.parameters(), lr=0.1)
+    for _ in range(3):
+        o1.zero_grad(); torch.nn.functional.mse_loss(fs(x[4 * RANK:4 * RANK + 4]), y[4 * RANK:4 * RANK + 4]).backward(); o1.step()
+        o2.zero_grad(); torch.nn.functional.mse_loss(ref(x), y).backward(); o2.step()
+    for p1, p2 in zip(fs.parameters(), ref.parameters()):
+        assert torch.allclose(p1.full_tensor(), p2, atol=1e-5, rtol=1e-4), (p1.full_tensor() - p2).abs().max().item()
     dist.destroy_process_group()
 
 
