@@ -263,6 +263,24 @@ def c10d_backend_gpu():
     torch.cuda.synchronize()
     for p1, p2 in zip(net.parameters(), ref.parameters()):
         assert torch.allclose(p1, p2, atol=1e-5, rtol=1e-4), (p1 - p2).abs().max().item()
+    # torch FSDP2 on cuda: its own all-gather / reduce-scatter streams wait on this backend's work objects
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+    mesh = init_device_mesh("cuda", (n,))
+    torch.manual_seed(1)
+    fs = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.Tanh(), torch.nn.Linear(256, 8)).to(DEV)
+    ref = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.Tanh(), torch.nn.Linear(256, 8)).to(DEV)
+    ref.load_state_dict(fs.state_dict())
+    for layer in (fs[0], fs[2]):
+        fully_shard(layer, mesh=mesh)
+    fully_shard(fs, mesh=mesh)
+    o1, o2 = torch.optim.SGD(fs.parameters(), lr=0.1), torch.optim.SGD(ref.parameters(), lr=0.1)
+    for _ in range(3):
+        o1.zero_grad(); torch.nn.functional.mse_loss(fs(x[8 * RANK:8 * RANK + 8]), y[8 * RANK:8 * RANK + 8]).backward(); o1.step()
+        o2.zero_grad(); torch.nn.functional.mse_loss(ref(x), y).backward(); o2.step()
+    torch.cuda.synchronize()
+    for p1, p2 in zip(fs.parameters(), ref.parameters()):
+        assert torch.allclose(p1.full_tensor(), p2, atol=1e-5, rtol=1e-4), (p1.full_tensor() - p2).abs().max().item()
     dist.destroy_process_group()
 
 
