@@ -379,3 +379,86 @@ def test_tuner_model_tracks_measured_times(lib):
             _, times = _pick(lib, 8, 1, 1, nbytes, dt=L.BFLOAT16)
             model = times[L.ALGOS[algo]]
             assert 0.65 * us <= model <= 1.35 * us, (algo, nbytes, model, us)
+
+
+def test_fused_mlp_backward_formulas_on_cpu():
+    """The hand-written backward of FusedTensorParallelMLP (recomputed pre-activation, SiLU derivative, weight and input
+    gradients) against autograd, with the fused forward kernels replaced by their plain PyTorch meaning."""
+    import torch
+    from mccl_b200.parallel.tp import _FusedMLPFunction
+    comm = mccl.Communicator(1, mccl.get_unique_id(), 0, transport="tcp")
+
+    class FakeLayer:                      # what TensorParallelFFN.forward computes, without the kernels
+        def __init__(self, w_up, w_down):
+            self.comm, self.w_up, self.w_down, self.x_full = comm, w_up, w_down, None
+
+        def forward(self, x):
+            self.x_full = x.detach().clone()
+            return torch.nn.functional.silu(self.x_full @ self.w_up.t()) @ self.w_down.t()
+
+    torch.manual_seed(0)
+    x = torch.randn(12, 8, dtype=torch.float64, requires_grad=True)
+    w_up = torch.randn(20, 8, dtype=torch.float64, requires_grad=True)
+    w_down = torch.randn(8, 20, dtype=torch.float64, requires_grad=True)
+    tgt = torch.randn(12, 8, dtype=torch.float64)
+    y = _FusedMLPFunction.apply(x, w_up, w_down, FakeLayer(w_up.detach(), w_down.detach()))
+    (y * tgt).sum().backward()
+    got = [t.grad.clone() for t in (x, w_up, w_down)]
+    for t in (x, w_up, w_down):
+        t.grad = None
+    ref = torch.nn.functional.silu(x @ w_up.t()) @ w_down.t()
+    (ref * tgt).sum().backward()
+    assert torch.allclose(y, ref.detach(), atol=1e-12)
+    for g, t in zip(got, (x, w_up, w_down)):
+        assert torch.allclose(g, t.grad, atol=1e-5, rtol=1e-5), (g - t.grad).abs().max().item()
+    comm.destroy()
+
+
+def test_moe_dispatch_combine_autograd_on_cpu(monkeypatch):
+    """The autograd wiring of the fused dispatch / combine (a dispatch's backward is a gather of the slot gradients, a
+    combine's backward scatters gate * dy and gives the gate <dy, row>) with the two kernels replaced by one-rank
+    PyTorch stand-ins of what they do."""
+    import torch
+    from mccl_b200.ops import moe as M
+
+    class Buf:
+        def __init__(self, e, c, d):
+            self.e, self.c, self.d = e, c, d
+            self.data = torch.zeros(1, e, c, d, dtype=torch.float64)
+
+    def scatter(buf, x, flat, scale):
+        buf.data.zero_()
+        keep = flat >= 0
+        rows = x[keep] if scale is None else x[keep] * scale[keep].unsqueeze(-1).to(x.dtype)
+        buf.data.view(-1, buf.d)[flat[keep].long()] = rows
+
+    def gather(buf, flat, scale, n_tokens):
+        out = torch.zeros(n_tokens, buf.d, dtype=buf.data.dtype)
+        keep = flat >= 0
+        rows = buf.data.view(-1, buf.d)[flat[keep].long()]
+        out[keep] = rows if scale is None else rows * scale[keep].unsqueeze(-1).to(rows.dtype)
+        return out
+
+    monkeypatch.setattr(M, "_scatter", scatter)
+    monkeypatch.setattr(M, "_gather", gather)
+    torch.manual_seed(0)
+    e, c, d, T = 3, 2, 5, 9
+    flat = torch.tensor([0, 2, -1, 3, 5, -1, 1, 4, -1], dtype=torch.int32)          # three dropped tokens
+    x = torch.randn(T, d, dtype=torch.float64, requires_grad=True)
+    gate = torch.rand(T, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(d, d, dtype=torch.float64, requires_grad=True)                   # a stand-in "expert"
+    tgt = torch.randn(T, d, dtype=torch.float64)
+    buf, gbuf = Buf(e, c, d), Buf(e, c, d)
+    recv = M.dispatch(x, flat, buf, gbuf)
+    y = M.combine(recv @ w, flat, gate, buf, gbuf)
+    (y * tgt).sum().backward()
+    got = [t.grad.clone() for t in (x, gate, w)]
+    for t in (x, gate, w):
+        t.grad = None
+    keep = flat >= 0
+    ref = torch.zeros(T, d, dtype=torch.float64)
+    ref[keep] = (x[keep] @ w) * gate[keep].float().double().unsqueeze(-1)
+    (ref * tgt).sum().backward()
+    assert torch.allclose(y, ref.detach(), atol=1e-6)
+    for g, t, name in zip(got, (x, gate, w), ("dx", "dgate", "dw")):
+        assert torch.allclose(g, t.grad, atol=1e-5, rtol=1e-5), (name, (g - t.grad).abs().max().item())
