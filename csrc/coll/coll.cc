@@ -6,6 +6,7 @@
 #include <cstring>
 #include <mutex>
 
+#include <cuda_runtime_api.h>
 #include <nvtx3/nvToolsExt.h>
 
 #include "../comm/comm.h"
@@ -150,6 +151,68 @@ mcclResult_t mcclAllToAll(mcclComm_t comm, const void* sendbuff, void* recvbuff,
     mcclSend(comm, static_cast<const char*>(sendbuff) + (size_t)p * blk, count, dt, p, stream);
     mcclRecv(comm, static_cast<char*>(recvbuff) + (size_t)p * blk, count, dt, p, stream);
   }
+  return mcclGroupEnd();
+}
+
+// ---- compositions of grouped Send / Recv (no counterpart in the reference; NCCL has the same three) ---------------
+static mcclResult_t localCopy(mcclComm_t comm, const void* src, void* dst, size_t bytes, mcclStream_t stream) {
+  if (bytes == 0 || src == dst) return mcclSuccess;
+  if (!comm->cuda) { memmove(dst, src, bytes); return mcclSuccess; }
+  return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? mcclSuccess : mcclSystemError;
+}
+
+// Segment j of sendbuff (sendcounts[j] elements at element offset sdispls[j]) goes to rank j; segment i of recvbuff
+// receives recvcounts[i] elements from rank i.  Counts and displacements are host arrays of nRanks entries.
+mcclResult_t mcclAllToAllv(mcclComm_t comm, const void* sendbuff, const size_t* sendcounts, const size_t* sdispls, void* recvbuff,
+                           const size_t* recvcounts, const size_t* rdispls, mcclDataType_t dt, mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if (sendcounts == nullptr || sdispls == nullptr || recvcounts == nullptr || rdispls == nullptr) MCCLFAIL(mcclInvalidArgument);
+  const size_t es = mcclDataSize(dt);
+  const int n = comm->nRanks, r = comm->rank;
+  if (sendcounts[r] != recvcounts[r]) MCCLFAIL(mcclInvalidArgument);
+  for (int p = 0; p < n; ++p)
+    if ((sendcounts[p] && sendbuff == nullptr) || (recvcounts[p] && recvbuff == nullptr)) MCCLFAIL(mcclInvalidArgument);
+  MCCLCHECK(localCopy(comm, static_cast<const char*>(sendbuff) + sdispls[r] * es, static_cast<char*>(recvbuff) + rdispls[r] * es,
+                      sendcounts[r] * es, stream));
+  MCCLCHECK(mcclGroupStart());
+  for (int i = 1; i < n; ++i) {
+    const int dst = (r + i) % n, src = (r - i + n) % n;
+    if (sendcounts[dst]) mcclSend(comm, static_cast<const char*>(sendbuff) + sdispls[dst] * es, sendcounts[dst], dt, dst, stream);
+    if (recvcounts[src]) mcclRecv(comm, static_cast<char*>(recvbuff) + rdispls[src] * es, recvcounts[src], dt, src, stream);
+  }
+  return mcclGroupEnd();
+}
+
+// recvbuff at the root = the ranks' sendbuff (count elements each) in rank order; recvbuff is ignored elsewhere.
+mcclResult_t mcclGather(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count, mcclDataType_t dt, int root,
+                        mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if (root < 0 || root >= comm->nRanks) MCCLFAIL(mcclInvalidArgument);
+  if (count == 0) return mcclSuccess;
+  if (sendbuff == nullptr || (comm->rank == root && recvbuff == nullptr)) MCCLFAIL(mcclInvalidArgument);
+  const size_t blk = count * mcclDataSize(dt);
+  if (comm->rank != root) return mcclSend(comm, sendbuff, count, dt, root, stream);
+  MCCLCHECK(localCopy(comm, sendbuff, static_cast<char*>(recvbuff) + (size_t)root * blk, blk, stream));
+  MCCLCHECK(mcclGroupStart());
+  for (int p = 0; p < comm->nRanks; ++p)
+    if (p != root) mcclRecv(comm, static_cast<char*>(recvbuff) + (size_t)p * blk, count, dt, p, stream);
+  return mcclGroupEnd();
+}
+
+// recvbuff on rank p = block p (count elements) of the root's sendbuff; sendbuff is ignored elsewhere.
+mcclResult_t mcclScatter(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count, mcclDataType_t dt, int root,
+                         mcclStream_t stream) {
+  MCCLCHECK(checkCommon(comm, dt));
+  if (root < 0 || root >= comm->nRanks) MCCLFAIL(mcclInvalidArgument);
+  if (count == 0) return mcclSuccess;
+  if (recvbuff == nullptr || (comm->rank == root && sendbuff == nullptr)) MCCLFAIL(mcclInvalidArgument);
+  const size_t blk = count * mcclDataSize(dt);
+  if (comm->rank != root) return mcclRecv(comm, recvbuff, count, dt, root, stream);
+  MCCLCHECK(localCopy(comm, static_cast<const char*>(sendbuff) + (size_t)root * blk, recvbuff, blk, stream));
+  MCCLCHECK(mcclGroupStart());
+  for (int p = 0; p < comm->nRanks; ++p)
+    if (p != root) mcclSend(comm, static_cast<const char*>(sendbuff) + (size_t)p * blk, count, dt, p, stream);
   return mcclGroupEnd();
 }
 

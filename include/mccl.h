@@ -147,6 +147,16 @@ mcclResult_t mcclReduce(mcclComm_t comm, const void* sendbuff, void* recvbuff, s
 mcclResult_t mcclAllToAll(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count,
                           mcclDataType_t dt, mcclStream_t stream);
 
+/* Compositions of grouped Send / Recv (not in the reference).  Counts and displacements are in elements, host arrays
+ * of one entry per rank. */
+mcclResult_t mcclAllToAllv(mcclComm_t comm, const void* sendbuff, const size_t* sendcounts, const size_t* sdispls,
+                           void* recvbuff, const size_t* recvcounts, const size_t* rdispls, mcclDataType_t dt,
+                           mcclStream_t stream);
+mcclResult_t mcclGather(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count, mcclDataType_t dt, int root,
+                        mcclStream_t stream);
+mcclResult_t mcclScatter(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t count, mcclDataType_t dt, int root,
+                         mcclStream_t stream);
+
 /* ---- point to point and grouping ------------------------------------------------------------- */
 mcclResult_t mcclSend(mcclComm_t comm, const void* sendbuff, size_t count, mcclDataType_t dt, int peer,
                       mcclStream_t stream);

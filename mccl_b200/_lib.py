@@ -85,6 +85,10 @@ def _declare(lib: C.CDLL) -> None:
     fn("mcclBroadcast", i, vp, vp, vp, sz, i, i, vp)
     fn("mcclReduce", i, vp, vp, vp, sz, i, i, i, vp)
     fn("mcclAllToAll", i, vp, vp, vp, sz, i, vp)
+    psz = C.POINTER(C.c_size_t)
+    fn("mcclAllToAllv", i, vp, vp, psz, psz, vp, psz, psz, i, vp)
+    fn("mcclGather", i, vp, vp, vp, sz, i, i, vp)
+    fn("mcclScatter", i, vp, vp, vp, sz, i, i, vp)
     fn("mcclSend", i, vp, vp, sz, i, i, vp)
     fn("mcclRecv", i, vp, vp, sz, i, i, vp)
     fn("mcclRecvAny", i, vp, vp, sz, i, P(i), vp)

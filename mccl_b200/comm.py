@@ -300,25 +300,29 @@ class Communicator:
         """All-to-all with a different element count per peer: `send_counts[j]` elements of flat `send` (consecutive
         segments, rank order) go to rank j, `recv_counts[i]` elements arrive from rank i into consecutive segments of
         flat `recv`.  Issued as one group of Send / Recv pairs (plus a local copy of the own segment)."""
-        n, r = self.size, self.rank
+        n = self.size
         if len(send_counts) != n or len(recv_counts) != n:
             raise ValueError("one count per rank is required")
-        so = [0] * (n + 1)
-        ro = [0] * (n + 1)
-        for i in range(n):
-            so[i + 1] = so[i] + int(send_counts[i])
-            ro[i + 1] = ro[i] + int(recv_counts[i])
-        if int(send_counts[r]) != int(recv_counts[r]):
-            raise ValueError("the segment a rank keeps must have the same size on both sides")
-        if send_counts[r]:
-            recv[ro[r]:ro[r + 1]] = send[so[r]:so[r + 1]]
-        with group():
-            for i in range(1, n):
-                dst, src = (r + i) % n, (r - i) % n
-                if send_counts[dst]:
-                    self.send(send[so[dst]:so[dst + 1]], dst, stream=stream)
-                if recv_counts[src]:
-                    self.recv(recv[ro[src]:ro[src + 1]], src, stream=stream)
+        sp, _, dt, _ = _describe(send)
+        rp, _, _, _ = _describe(recv)
+        arr = C.c_size_t * n
+        sc, rc = arr(*[int(c) for c in send_counts]), arr(*[int(c) for c in recv_counts])
+        sd, rd = arr(), arr()
+        for i in range(1, n):
+            sd[i], rd[i] = sd[i - 1] + sc[i - 1], rd[i - 1] + rc[i - 1]
+        L.check(self._lib.mcclAllToAllv(self._h, sp, sc, sd, rp, rc, rd, dt, _stream_of(send, stream)), "mcclAllToAllv")
+
+    def gather(self, send, recv, root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
+        """The root's `recv` = every rank's `send` in rank order (`recv` may be None elsewhere)."""
+        sp, cnt, dt, _ = _describe(send, dtype)
+        rp = _describe(recv, dtype)[0] if recv is not None else None
+        L.check(self._lib.mcclGather(self._h, sp, rp, cnt, dt, root, _stream_of(send, stream)), "mcclGather")
+
+    def scatter(self, send, recv, root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
+        """`recv` on rank p = block p of the root's `send` (`send` may be None elsewhere)."""
+        rp, cnt, dt, _ = _describe(recv, dtype)
+        sp = _describe(send, dtype)[0] if send is not None else None
+        L.check(self._lib.mcclScatter(self._h, sp, rp, cnt, dt, root, _stream_of(recv, stream)), "mcclScatter")
 
     def send(self, buf, peer: int, dtype: Optional[int] = None, stream=None) -> None:
         """Send `buf` to `peer`; inside `with mccl_b200.group():` it is batched with the other calls."""

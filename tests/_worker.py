@@ -667,6 +667,32 @@ def fsdp_stack():
     comm.finalize(); comm.destroy()
 
 
+def rooted_and_ragged():
+    """mcclGather, mcclScatter and mcclAllToAllv (compositions of grouped Send / Recv) on the tcp transport."""
+    comm = make_comm()
+    n, r = WORLD, RANK
+    for root in (0, n - 1):
+        out = np.zeros(5 * n, np.float32) if r == root else None
+        comm.gather(np.full(5, float(r), np.float32), out, root=root)
+        if r == root:
+            assert np.array_equal(out, np.repeat(np.arange(n, dtype=np.float32), 5))
+        piece = np.zeros(3, np.int64)
+        comm.scatter(np.arange(3 * n, dtype=np.int64) if r == root else None, piece, root=root)
+        assert np.array_equal(piece, np.arange(3 * r, 3 * r + 3))
+    # rank r sends j + 1 elements to rank j (value 100 r + j) and receives r + 1 from everyone
+    send = np.concatenate([np.full(j + 1, 100.0 * r + j) for j in range(n)]).astype(np.float64)
+    recv = np.zeros(n * (r + 1), np.float64)
+    comm.all_to_all_v(send, [j + 1 for j in range(n)], recv, [r + 1] * n)
+    assert np.array_equal(recv, np.concatenate([np.full(r + 1, 100.0 * s + r) for s in range(n)]))
+    # zero-length segments
+    send = np.full(4, float(r), np.float32)
+    recv = np.zeros(4 if r == 0 else 0, np.float32) if n == 1 else np.zeros(4 * n if r == 0 else 0, np.float32)
+    comm.all_to_all_v(send, [4] + [0] * (n - 1), recv, [4] * n if r == 0 else [0] * n)
+    if r == 0:
+        assert np.array_equal(recv, np.repeat(np.arange(n, dtype=np.float32), 4))
+    comm.finalize(); comm.destroy()
+
+
 def ddp_accumulate():
     """Two micro-batches (the first under no_sync) give the gradient of the concatenated batch."""
     import torch

@@ -71,6 +71,11 @@ def test_fully_sharded_stack(world):
     assert_all_ok(run_ranks(world, "fsdp_stack"))
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_gather_scatter_alltoallv(world):
+    assert_all_ok(run_ranks(world, "rooted_and_ragged"))
+
+
 def test_ddp_checkpoint_and_resume():
     assert_all_ok(run_ranks(2, "ddp_checkpoint"))
 
