@@ -358,6 +358,27 @@ def tp_mlp_trainable():
     comm.finalize(); comm.destroy()
 
 
+def rooted_and_ragged_gpu():
+    """mcclGather, mcclScatter and mcclAllToAllv on cuda tensors (the batched Send / Recv kernel underneath)."""
+    comm = make_comm()
+    n, r = WORLD, RANK
+    for root in (0, n - 1):
+        out = torch.zeros(5000 * n, device=DEV) if r == root else None
+        comm.gather(torch.full((5000,), float(r), device=DEV), out, root=root); torch.cuda.synchronize()
+        if r == root:
+            assert torch.equal(out, torch.arange(n, device=DEV, dtype=torch.float32).repeat_interleave(5000))
+        piece = torch.zeros(3001, device=DEV, dtype=torch.int64)
+        comm.scatter(torch.arange(3001 * n, device=DEV, dtype=torch.int64) if r == root else None, piece, root=root); torch.cuda.synchronize()
+        assert torch.equal(piece, torch.arange(3001 * r, 3001 * r + 3001, device=DEV, dtype=torch.int64))
+    k = 70_001                                                    # odd segment sizes, several FIFO chunks
+    send = torch.cat([torch.full(((j + 1) * k,), 100.0 * r + j, device=DEV) for j in range(n)])
+    recv = torch.zeros(n * (r + 1) * k, device=DEV)
+    comm.all_to_all_v(send, [(j + 1) * k for j in range(n)], recv, [(r + 1) * k] * n); torch.cuda.synchronize()
+    assert torch.equal(recv, torch.cat([torch.full(((r + 1) * k,), 100.0 * s + r, device=DEV) for s in range(n)]))
+    assert canary_ok(comm)
+    comm.finalize(); comm.destroy()
+
+
 def device_timeout():
     """Rank 1 sits out one collective (between steps, nothing of its own in flight).  The others' kernels
     give up after the device time budget, record why in the status word and return; the host reads it."""

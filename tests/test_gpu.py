@@ -399,6 +399,11 @@ def test_torch_distributed_backend_on_gpus(tmp_path):
 
 
 @unverified
+def test_gather_scatter_alltoallv_on_gpus():
+    assert_all_ok(run_ranks(min(NGPU, 4), "rooted_and_ragged_gpu", worker="_gpu_worker.py", timeout=300))
+
+
+@unverified
 def test_trainable_fused_tensor_parallel_mlp():
     assert_all_ok(run_ranks(2, "tp_mlp_trainable", worker="_gpu_worker.py", timeout=600))
 
