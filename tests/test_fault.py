@@ -8,7 +8,8 @@ def test_abort_unblocks_parked_receive():
 
 
 def test_peer_exit_is_an_error_not_a_hang():
-    res = run_ranks(3, "peer_dies", timeout=90)
+    # short data-path deadlines: the survivors' connection attempts to the dead rank give up in seconds
+    res = run_ranks(3, "peer_dies", env={"MCCL_ACCEPT_TIMEOUT_MS": "3000", "MCCL_CONNECT_TIMEOUT_MS": "1500"}, timeout=90)
     assert_all_ok([r for r in res if r[0] != 1])
 
 
@@ -22,5 +23,6 @@ def test_injected_send_fault_surfaces():
 
 
 def test_survivors_restart_as_a_smaller_world():
-    res = run_ranks(3, "recover_smaller", args={"port2": free_port()}, timeout=180)
+    res = run_ranks(3, "recover_smaller", args={"port2": free_port()},
+                    env={"MCCL_ACCEPT_TIMEOUT_MS": "3000", "MCCL_CONNECT_TIMEOUT_MS": "1500"}, timeout=180)
     assert_all_ok([r for r in res if r[0] != 2])
