@@ -140,6 +140,7 @@ const char* mcclResultStr(mcclResult_t r) {
   return ((unsigned)r < (unsigned)mcclNumResults) ? names[r] : "invalid result";
 }
 const char* mcclGetErrorString(mcclResult_t r) { return mcclResultStr(r); }
+int mcclResultFatal(mcclResult_t r) { return mccl::resultFatal(r) ? 1 : 0; }
 
 const char* mcclAlgoStr(int algo) {
   static const char* names[] = {"ring", "tree", "oneshot", "twoshot", "nvls"};

@@ -109,6 +109,8 @@ const char*  mcclCollStr(int coll);
 size_t       mcclDataSize(mcclDataType_t t);
 mcclResult_t mcclGetLastError(mcclComm_t comm);   /* thread-local last non-success result */
 mcclResult_t mcclSetLastError(mcclResult_t r);
+/* 1 for the results that latch on a communicator (system, internal and remote errors), 0 for the rest. */
+int          mcclResultFatal(mcclResult_t r);
 
 /* ---- communicator lifecycle ------------------------------------------------------------------ */
 mcclResult_t mcclGetUniqueId(mcclUniqueId* id);

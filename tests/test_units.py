@@ -462,3 +462,11 @@ def test_moe_dispatch_combine_autograd_on_cpu(monkeypatch):
     assert torch.allclose(y, ref.detach(), atol=1e-6)
     for g, t, name in zip(got, (x, gate, w), ("dx", "dgate", "dw")):
         assert torch.allclose(g, t.grad, atol=1e-5, rtol=1e-5), (name, (g - t.grad).abs().max().item())
+
+
+def test_result_fatal_matches_the_latching_rule(lib):
+    """System, internal and remote errors latch on a communicator (src/include/comm.h:106-108 of the reference); usage
+    errors and mcclInProgress do not."""
+    fatal = {L.SYSTEM_ERROR, L.INTERNAL_ERROR, L.REMOTE_ERROR}
+    for code in range(8):
+        assert bool(lib.mcclResultFatal(code)) == (code in fatal)
