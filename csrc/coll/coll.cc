@@ -45,7 +45,12 @@ mcclResult_t checkCommon(mcclComm_t comm, mcclDataType_t dt) {
 mcclResult_t issue(mcclComm_t comm, const char* what, size_t bytes, mcclStream_t stream, std::function<mcclResult_t()> fn) {
   auto traced = [=]() -> mcclResult_t {
     NvtxRange range(what);
-    if (!traceEnabled()) return fn();
+    if (!traceEnabled()) {
+      const mcclResult_t rc = fn();
+      MCCL_TRACE("%s %zu bytes on %s rank %d/%d: algo %s -> %s", what, bytes, comm->transport.c_str(), comm->rank, comm->nRanks,
+                 mcclAlgoStr(comm->lastAlgo.load()), mcclResultStr(rc));
+      return rc;
+    }
     TraceSpan span = traceBegin(comm, what, bytes, comm->lastAlgo.load(), stream);
     const mcclResult_t rc = fn();
     traceEnd(comm, span, stream);
