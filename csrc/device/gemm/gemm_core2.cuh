@@ -1,7 +1,7 @@
 // Two-SM form of the bf16 GEMM: a cluster of two CTAs works on one 256 x BN output tile with
 // tcgen05.mma.cta_group::2 (M = 256).  Each CTA stages its own 128 rows of A and its own half of the B tile
 // (BN/2 rows), so a pair moves half the B bytes through shared memory per FLOP that two independent CTAs
-// would, and the stage is small enough for a six-deep ring.
+// would, and the stage is small enough for a ring of seven or eight stages.
 //
 //   CTA 0 of the pair ("leader")            CTA 1
 //   warp 0  TMA: A rows [0,128), B rows      TMA: A rows [128,256), B rows [BN/2, BN) of the tile; all four
@@ -28,7 +28,9 @@ constexpr int kThreadsGemm2 = 256;
 template <int BN> struct Smem2 {
   static constexpr int A_BYTES = BM * BK * 2;              // this CTA's 128 rows
   static constexpr int B_BYTES = (BN / 2) * BK * 2;        // this CTA's half of the B tile
-  static constexpr int STAGES = (A_BYTES + B_BYTES) * 8 <= 200 * 1024 ? 8 : 6;
+  // as many stages as fit beside the barriers in the 227 KB a CTA may use, eight at most (BN 256 and 224: seven)
+  static constexpr int FIT = (232448 - 1536) / (A_BYTES + B_BYTES);
+  static constexpr int STAGES = FIT > 8 ? 8 : FIT;
   static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
   static constexpr int TOTAL = TILE_BYTES + 512 + 1024;    // barriers + alignment slack
 };
