@@ -60,6 +60,7 @@ def main() -> int:
     ap.add_argument("--elems", type=int, default=0)
     ap.add_argument("--mbytes", type=int, default=512)
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--cublas", action="store_true", help="gemm: also time torch.matmul (cuBLAS) on the same operands")
     ap.add_argument("--two-sm", action="store_true", help="gemm: the form in which pairs of SMs share a 256-row tile")
     args = ap.parse_args()
     torch.cuda.set_device(0)
@@ -75,6 +76,11 @@ def main() -> int:
         fl = 2.0 * args.m * args.n * args.k
         out.update({"shape": [args.m, args.n, args.k], "two_sm": args.two_sm, "us": round(ms * 1e3, 1), "tflops": round(fl / ms / 1e9, 1),
                     "frac_of_cublas_peak": round(fl / ms / 1e9 / tflops, 3), "kernel_error": G.last_error()})
+        if args.cublas:
+            # the library GEMM on the same operands, timed the same way (no activation: it has none to fuse)
+            ref_ms = timed(lambda: torch.matmul(x, w.t(), out=y), args.launches)
+            out.update({"cublas_us": round(ref_ms * 1e3, 1), "cublas_tflops": round(fl / ref_ms / 1e9, 1),
+                        "speedup_vs_cublas": round(ref_ms / ms, 3)})
     elif args.case == "adamw":
         from mccl_b200.ops.optim import fused_adamw_
         n = args.elems or (64 << 20)

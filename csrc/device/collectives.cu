@@ -207,7 +207,7 @@ mcclResult_t arOneShot(const Call& k, const void* send, void* recv, size_t bytes
   OneShotArgs a;
   memset(&a, 0, sizeof(a));
   a.peers = k.st->peers;
-  a.nCtas = pickCtas(k.c, bytes, mcclAlgoOneShot);
+  a.nCtas = std::min(pickCtas(k.c, bytes, mcclAlgoOneShot), MCCL_ONESHOT_MAX_CTAS);
   a.op = (k.op == mcclAvg) ? mcclSum : k.op;
   a.divisor = k.divisor;
   a.send = static_cast<const char*>(send);

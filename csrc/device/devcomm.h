@@ -11,6 +11,7 @@
 #define MCCL_MAX_RANKS 16      // ranks of one NVSwitch domain a kernel can address
 #define MCCL_MAX_CTAS 160      // upper bound on CTAs ("channels") of one collective kernel
 #define MCCL_COLL_THREADS 512
+#define MCCL_ONESHOT_MAX_CTAS 8   // the one-shot kernel never runs more CTAs: its call counters are kept equal over this many
 
 #ifdef __CUDACC__
 #define MCCL_HD __host__ __device__
@@ -40,6 +41,8 @@ struct CtrlFlags {
   uint64_t epoch[MCCL_MAX_CTAS];
   // one-shot: ready[cta][src] = number of one-shot calls whose data from `src` has fully arrived.
   uint64_t oneShotReady[MCCL_MAX_CTAS][MCCL_MAX_RANKS];
+  // oneShotCalls[cta]: one-shot calls made so far.  Every launch leaves the first MCCL_ONESHOT_MAX_CTAS entries
+  // equal, whatever its grid, so the slot half a call uses (its parity) is the same for every CTA.
   uint64_t oneShotCalls[MCCL_MAX_CTAS];
   // Send/Recv FIFOs: head[src] = chunks rank `src` has written into my slot; tail[dst] = chunks rank
   // `dst` has drained from its slot for me.  sent/recvd are this rank's own running totals.

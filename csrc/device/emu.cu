@@ -132,6 +132,8 @@ extern "C" mcclResult_t mcclEmuPhases(int nRanks, void* const* bufs, uint64_t co
       a.peers = emuPeers(r); a.nCtas = ctas; a.op = redOp; a.divisor = divisor;
       a.send = static_cast<const char*>(bufs[r]); a.recv = static_cast<char*>(bufs[r]); a.bytes = bytes;
     }
+    if (ctas > MCCL_ONESHOT_MAX_CTAS) ctas = MCCL_ONESHOT_MAX_CTAS;
+    for (OneShotArgs& a : args) a.nCtas = ctas;
     rc = emuLaunch(EMU_KERNEL(dt, oneShotKernelEmu), args, ctas, s);
   } else if (algo == mcclAlgoRing) {
     if (bytes % 16 || bytes / 16 < (uint64_t)2 * n) return mcclInvalidArgument;
@@ -169,6 +171,15 @@ extern "C" mcclResult_t mcclEmuAllReduce(int nRanks, void* const* bufs, uint64_t
 }
 
 extern "C" void mcclEmuDestroy(void) { mccl::emuDestroy(); }
+
+// The one-shot call counters of emulated rank `rank` (the first `cap` CTAs), for tests of their lockstep.
+extern "C" mcclResult_t mcclEmuOneShotCounters(int rank, uint64_t* out, int cap) {
+  using namespace mccl;
+  if (rank < 0 || rank >= gEmu.n || out == nullptr || cap < 1 || cap > MCCL_MAX_CTAS) return mcclInvalidArgument;
+  const CtrlFlags* f = reinterpret_cast<const CtrlFlags*>(gEmu.ctrl[rank] + gEmu.layout.flagsOff);
+  CUDACHECK(cudaMemcpy(out, f->oneShotCalls, (size_t)cap * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+  return mcclSuccess;
+}
 
 // ---- index-arithmetic probes (host only): the work splits the kernels rely on, for exhaustive CPU tests ----------------
 

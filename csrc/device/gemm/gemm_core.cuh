@@ -59,6 +59,8 @@ struct GemmArgs {
   __nv_bfloat16* out;          // RS: [M/n, N]
   float* accum;                // RS: [M/n, N] fp32 running sum of the partials that have arrived
   int panel;                   // stripes per rasterisation panel (divides the stripes of a row block)
+  int debug;                   // tuning aid of the two-SM kernel (MCCL_GEMM_DEBUG): bit 0 = skip the loads after the
+                               // first ring fill, bit 1 = skip the epilogue's global stores; results are then meaningless
 };
 
 template <int BN> struct Smem {
@@ -68,7 +70,7 @@ template <int BN> struct Smem {
   static constexpr int TOTAL = TILE_BYTES + 256 + 1024;     // barriers + alignment slack
 };
 
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 __device__ __forceinline__ uint64_t ldAcquireGpu(const uint64_t* p) {
   uint64_t v;

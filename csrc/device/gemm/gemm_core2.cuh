@@ -77,11 +77,28 @@ __device__ __forceinline__ void mmaBf16(uint32_t tmemD, uint64_t descA, uint64_t
       " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
       :: "r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the descriptors given as (low word, high word): stepping along K only changes the low word,
+// which saves the 64-bit additions in the one thread that issues every MMA of the pair.
+__device__ __forceinline__ void mmaBf16Split(uint32_t tmemD, uint32_t aLo, uint32_t bLo, uint32_t descHi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n .reg .b64 da, db;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n setp.ne.b32 p, %5, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n}"
+      :: "r"(tmemD), "r"(aLo), "r"(bLo), "r"(descHi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mmaCommitMaskAddr(uint32_t barAddr, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               :: "r"(barAddr), "h"(mask) : "memory");
+}
 // Arrive on the barrier at this offset in both CTAs once every MMA issued so far has completed: one commit per
 // CTA, each naming that CTA's barrier by its shared::cluster address (a commit tracks all earlier MMAs of the
 // issuing thread, so the two are independent observers of the same work).
 __device__ __forceinline__ void mmaCommitTo(uint32_t barClusterAddr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(barClusterAddr) : "memory");
+}
+// One instruction that arrives on the barrier at this offset in every CTA of `mask` (a commit, not a load).
+__device__ __forceinline__ void mmaCommitMask(uint64_t* bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               :: "r"(umma::smemAddr(bar)), "h"(mask) : "memory");
 }
 __device__ __forceinline__ void mmaCommitBoth(uint64_t* bar) {
   const uint32_t local = umma::smemAddr(bar);
@@ -93,7 +110,9 @@ __device__ __forceinline__ void mmaCommitBoth(uint64_t* bar) {
 
 // Launched as clusters of two CTAs (cluster dimension attribute of the launch).  Threads: 256 in the plain
 // mode, 384 (communication warps 8-11) in the fused modes.
-template <int BN, int MODE>
+// VAR selects how the MMA thread is written (bit 0: one commit instruction for both CTAs' barriers instead of
+// two; bit 1: wait for the next stage between the MMAs of the current one).
+template <int BN, int MODE, int VAR>
 __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsGemm, 1) tpGemm2Kernel(const __grid_constant__ GemmArgs a) {
   using S = Smem2<BN>;
   constexpr int STAGES2 = S::STAGES;
@@ -136,6 +155,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer (both CTAs)
     int stage = 0; uint32_t phase = 0;
+    const bool noLoads = a.debug & 1;
     for (int t = pair; t < totalTiles && *sFail == 0; t += numPairs) {
       int stripe, nt;
       tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
@@ -145,7 +165,12 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
         umma::fenceProxyAsyncGlobal();
       }
       for (int kb = 0; kb < kBlocks; ++kb) {
-        if (!umma::mbarWait(&empty[stage], phase ^ 1, budget)) { *sFail = 1; atomicExch(a.errFlag, 21); break; }
+        if (!umma::mbarWaitParked(&empty[stage], phase ^ 1, budget)) { *sFail = 1; atomicExch(a.errFlag, 21); break; }
+        if (noLoads && (t != pair || kb >= STAGES2)) {       // tuning aid: the whole handshake, no data
+          if (ctaRank == 0) umma::mbarArrive(&full[stage]);
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+          continue;
+        }
         if (ctaRank == 0) umma::mbarExpectTx(&full[stage], 2 * (S::A_BYTES + S::B_BYTES));
         const uint32_t leaderFull = umma2::mapToCta(umma::smemAddr(&full[stage]), 0);
         umma2::tmaLoad2dPair(sA + stage * S::A_BYTES, &a.mapA, leaderFull, kb * BK, stripe * BM2 + (int)ctaRank * BM);
@@ -155,25 +180,55 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
     }
   } else if (warp == 1 && lane == 0 && ctaRank == 0) {
     // ---------------- MMA issuer (leader only)
+    // This one thread feeds the tensor cores of both SMs, and what it executes between two MMAs is time in
+    // which nothing new gets queued, so the loop is kept short: one flat count of (tile, k block) steps, the ring
+    // of stages unrolled so that every barrier and descriptor is the base plus a constant, descriptors stepped
+    // in their low word only, and (VAR bit 1) the wait for the NEXT stage placed between the second and the
+    // third MMA of the current one, where two queued MMAs hide the barrier's round trip.
     constexpr uint32_t idesc = umma::instrDescBf16(BM2, BN);
-    int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t accPhase = 0;
-    for (int t = pair; t < totalTiles && *sFail == 0; t += numPairs) {
-      if (!umma::mbarWait(&tmemEmpty[acc], accPhase ^ 1, budget)) { *sFail = 1; atomicExch(a.errFlag, 22); break; }
-      umma::tcFenceAfter();
-      const uint32_t d = tmemBase + (uint32_t)acc * 256u;
-      for (int kb = 0; kb < kBlocks; ++kb) {
-        if (!umma::mbarWait(&full[stage], phase, budget)) { *sFail = 1; atomicExch(a.errFlag, 23); break; }
-        umma::tcFenceAfter();
-        const uint64_t da = umma::smemDescSw128(sA + stage * S::A_BYTES), db = umma::smemDescSw128(sB + stage * S::B_BYTES);
+    constexpr bool kMcCommit = (VAR & 1) != 0, kEarlyWait = (VAR & 2) != 0;
+    const uint64_t descA0 = umma::smemDescSw128(sA), descB0 = umma::smemDescSw128(sB);
+    const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0, descHi = (uint32_t)(descA0 >> 32);
+    const uint32_t emptyAddr = umma::smemAddr(empty), tmemFullAddr = umma::smemAddr(tmemFull);
+    const uint32_t emptyPeer = umma2::mapToCta(emptyAddr, 1), tmemFullPeer = umma2::mapToCta(tmemFullAddr, 1);
+    const int myTiles = pair < totalTiles ? (totalTiles - pair + numPairs - 1) / numPairs : 0;
+    int remaining = myTiles * kBlocks;
+    int kb = 0, acc = 0; uint32_t phase = 0, accPhase = 0;
+    uint32_t d = tmemBase;
+    bool fail = false;
+    if (kEarlyWait && remaining > 0 && !umma::mbarWait(&full[0], 0, budget)) { fail = true; *sFail = 1; atomicExch(a.errFlag, 23); }
+    while (remaining > 0 && !fail) {
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma2::mmaBf16(d, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc, (kb | k) != 0);
-        umma2::mmaCommitBoth(&empty[stage]);
-        if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+      for (int s = 0; s < STAGES2; ++s) {
+        if (remaining == 0) break;
+        if (kb == 0) {
+          if (*sFail != 0) { fail = true; break; }
+          if (!umma::mbarWait(&tmemEmpty[acc], accPhase ^ 1, budget)) { fail = true; *sFail = 1; atomicExch(a.errFlag, 22); break; }
+          d = tmemBase + (uint32_t)acc * 256u;
+        }
+        if (!kEarlyWait && !umma::mbarWait(&full[s], phase, budget)) { fail = true; *sFail = 1; atomicExch(a.errFlag, 23); break; }
+        umma::tcFenceAfter();
+        const uint32_t aLo = aLo0 + (uint32_t)(s * (S::A_BYTES >> 4)), bLo = bLo0 + (uint32_t)(s * (S::B_BYTES >> 4));
+        umma2::mmaBf16Split(d, aLo, bLo, descHi, idesc, (uint32_t)kb);
+        umma2::mmaBf16Split(d, aLo + 2, bLo + 2, descHi, idesc, 1);
+        if (kEarlyWait && remaining > 1) {
+          const int ns = (s + 1) % STAGES2;
+          if (!umma::mbarWait(&full[ns], ns == 0 ? phase ^ 1 : phase, budget)) { fail = true; *sFail = 1; atomicExch(a.errFlag, 23); }
+        }
+        umma2::mmaBf16Split(d, aLo + 4, bLo + 4, descHi, idesc, 1);
+        umma2::mmaBf16Split(d, aLo + 6, bLo + 6, descHi, idesc, 1);
+        if (kMcCommit) umma2::mmaCommitMaskAddr(emptyAddr + 8u * s, 3);
+        else { umma2::mmaCommitTo(emptyAddr + 8u * s); umma2::mmaCommitTo(emptyPeer + 8u * s); }
+        --remaining;
+        if (++kb == kBlocks) {
+          kb = 0;
+          if (kMcCommit) umma2::mmaCommitMaskAddr(tmemFullAddr + 8u * acc, 3);
+          else { umma2::mmaCommitTo(tmemFullAddr + 8u * acc); umma2::mmaCommitTo(tmemFullPeer + 8u * acc); }
+          acc ^= 1; if (acc == 0) accPhase ^= 1;
+        }
+        if (fail) break;
       }
-      if (*sFail) break;
-      umma2::mmaCommitBoth(&tmemFull[acc]);
-      acc ^= 1; if (acc == 0) accPhase ^= 1;
+      phase ^= 1;
     }
   } else if (warp >= 4 && warp < 8) {
     // ---------------- epilogue (both CTAs, own 128 rows)
@@ -182,7 +237,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
     for (int t = pair; t < totalTiles; t += numPairs) {
       int stripe, nt;
       tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
-      bool good = *sFail == 0 && umma::mbarWait(&tmemFull[acc], accPhase, budget);
+      bool good = *sFail == 0 && umma::mbarWaitParked(&tmemFull[acc], accPhase, budget);
       if (!good && *sFail == 0) { *sFail = 1; atomicExch(a.errFlag, 24); }
       if (MODE == MODE_RS) good = !namedBarrierOr(1, 128, !good);     // the four warps meet at a barrier below
       if (!good) break;
@@ -204,6 +259,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
           o2[j] = __floats2bfloat162_rn(x0, x1);
         }
         uint4* dst = reinterpret_cast<uint4*>(dstRow + c * 32);
+        if (a.debug & 2) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) dst[j] = outv[j];
       }

@@ -117,15 +117,30 @@ bool twoSmWanted() {
   return on;
 }
 
-template <int MODE>
-bool pairKernel(int bn, const void** fn, int* smem) {
-#define MCCL_GEMM2_CASE(BN_) case BN_: *fn = reinterpret_cast<const void*>(&tpGemm2Kernel<BN_, MODE>); *smem = Smem2<BN_>::TOTAL; return true;
+// Form of the MMA thread the two-SM kernels are built with (see tpGemm2Kernel); the plain GEMM can be switched
+// to the others with MCCL_GEMM_VAR for timing comparisons.
+constexpr int kGemm2Var = 1;
+
+template <int MODE, int VAR>
+bool pairKernelVar(int bn, const void** fn, int* smem) {
+#define MCCL_GEMM2_CASE(BN_) case BN_: *fn = reinterpret_cast<const void*>(&tpGemm2Kernel<BN_, MODE, VAR>); *smem = Smem2<BN_>::TOTAL; return true;
   switch (bn) {
     MCCL_GEMM2_CASE(256) MCCL_GEMM2_CASE(224) MCCL_GEMM2_CASE(192) MCCL_GEMM2_CASE(160) MCCL_GEMM2_CASE(128) MCCL_GEMM2_CASE(96)
     MCCL_GEMM2_CASE(64)
     default: return false;
   }
 #undef MCCL_GEMM2_CASE
+}
+
+template <int MODE>
+bool pairKernel(int bn, const void** fn, int* smem) {
+  if (MODE == MODE_PLAIN) {
+    static const int var = (int)envInt("MCCL_GEMM_VAR", kGemm2Var);
+    if (var == 0) return pairKernelVar<MODE_PLAIN, 0>(bn, fn, smem);
+    if (var == 2) return pairKernelVar<MODE_PLAIN, 2>(bn, fn, smem);
+    if (var == 3) return pairKernelVar<MODE_PLAIN, 3>(bn, fn, smem);
+  }
+  return pairKernelVar<MODE, kGemm2Var>(bn, fn, smem);
 }
 
 void pairConfig(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int pairs, int threads, int smem, cudaStream_t s) {
@@ -244,7 +259,9 @@ mcclResult_t mcclTpGemm2(const void* A, const void* B, void* C, int M, int N, in
     return mcclInvalidArgument;
   }
   const int pairsMax = std::max(1, (maxCtas > 0 ? maxCtas : smCount()) / 2);
-  const int bn = pickBN(M / 2, N, pairsMax);          // M / 2: pickBN counts 128-row stripes, a pair takes 256 rows
+  int bn = pickBN(M / 2, N, pairsMax);                // M / 2: pickBN counts 128-row stripes, a pair takes 256 rows
+  const int forcedBn = (int)envInt("MCCL_GEMM_BN", 0);          // tuning aid: a tile width that divides N
+  if (forcedBn > 0 && N % forcedBn == 0) bn = forcedBn;
   const void* fn = nullptr;
   int smem = 0;
   if (bn == 0 || !pairKernel<MODE_PLAIN>(bn, &fn, &smem)) return mcclInvalidArgument;
@@ -261,7 +278,9 @@ mcclResult_t mcclTpGemm2(const void* A, const void* B, void* C, int M, int N, in
   int* hostFlag = errFlagFor(dev);
   if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
   a.budgetNs = 2000000000ull;
+  a.debug = (int)envInt("MCCL_GEMM_DEBUG", 0);
   a.panel = pickPanel(M / BM2);
+  if (envInt("MCCL_GEMM_PANEL", 0) > 0) a.panel = (int)envInt("MCCL_GEMM_PANEL", 0);
   const int tiles = (M / BM2) * (N / bn);
   return launchPairs(fn, kThreadsGemm2, smem, tiles < pairsMax ? tiles : pairsMax, a, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -42,6 +42,23 @@ __device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, uint64_
     }
   }
 }
+// The same for roles with slack (producer, epilogue): each probe lets the hardware park the thread for up to
+// about a microsecond (it resumes as soon as the phase completes), so a waiting warp takes next to no issue
+// slots from the MMA-issuing warp on its scheduler.
+__device__ __forceinline__ bool mbarWaitParked(uint64_t* bar, uint32_t parity, uint64_t budgetNs) {
+  uint64_t t0 = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.b32 %0, 1, 0, p;\n}"
+        : "=r"(done) : "r"(smemAddr(bar)), "r"(parity), "r"(1000u) : "memory");
+    if (done) return true;
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    if (spins == 0) t0 = t;
+    else if (t - t0 > budgetNs) return false;
+  }
+}
 __device__ __forceinline__ void fenceBarrierInit() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // Make generic-proxy writes to global memory visible to the async proxy (TMA) of this thread.
 __device__ __forceinline__ void fenceProxyAsyncGlobal() { asm volatile("fence.proxy.async.global;" ::: "memory"); }

@@ -181,7 +181,10 @@ __device__ __forceinline__ void oneShotBody(const OneShotArgs& a) {
       stLocal128(a.recv + i * 16, accFinish<T>(acc, a.divisor));
     }
   }
-  if (tid == 0) mine->oneShotCalls[cta] = call;
+  // Calls of different sizes run different grids.  The counters of the CTAs that sat this call out advance too:
+  // were they to lag, a CTA could come back with the parity of a call whose slots a slower peer is still
+  // folding (no barrier closes this kernel) and overwrite them.
+  if (tid == 0) for (int b = cta; b < MCCL_ONESHOT_MAX_CTAS; b += G) mine->oneShotCalls[b] = call;
 }
 
 template <typename T>

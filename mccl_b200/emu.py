@@ -40,5 +40,16 @@ def phases(tensors: Sequence[torch.Tensor], algo: str, phase_mask: int, shift: i
               C.c_void_p(s)), "mcclEmuPhases")
 
 
+def one_shot_counters(rank: int, ctas: int = 8) -> list[int]:
+    """One-shot call counters of the first `ctas` CTAs of emulated rank `rank` (equal after every call)."""
+    lib = L.load()
+    f = lib.mcclEmuOneShotCounters
+    f.restype = C.c_int
+    f.argtypes = [C.c_int, C.POINTER(C.c_uint64), C.c_int]
+    out = (C.c_uint64 * ctas)()
+    L.check(f(rank, out, ctas), "mcclEmuOneShotCounters")
+    return list(out)
+
+
 def destroy() -> None:
     L.load().mcclEmuDestroy()

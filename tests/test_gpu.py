@@ -314,6 +314,29 @@ def test_emulated_ranks_all_reduce_on_one_gpu(algo):
     emu.destroy()
 
 
+def test_emulated_one_shot_calls_of_mixed_sizes_stay_in_step():
+    """Small and large one-shot calls run different grids; every CTA's call counter (which picks the half of the
+    exchange slots a call uses) must advance all the same, or a later call could overwrite slots a peer still reads."""
+    _require_cuda()
+    from mccl_b200 import emu
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n = 4
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for it, (kb, ctas) in enumerate([(32, 2), (128, 8), (64, 2), (72, 8), (64, 2), (16, 1), (128, 8), (32, 3)]):
+        numel = kb * 1024 // 4
+        xs = [torch.rand(numel, generator=g, device=dev) * 2 - 1 for _ in range(n)]
+        ref = torch.stack([x.double() for x in xs]).sum(0)
+        emu.all_reduce(xs, op="sum", algo="oneshot", ctas=ctas)
+        torch.cuda.synchronize()
+        for x in xs:
+            assert ((x.double() - ref).abs() / (ref.abs() + 1.0)).max().item() <= 1e-5, (it, kb, ctas)
+            assert torch.equal(x, xs[0])
+        for r in range(n):
+            assert emu.one_shot_counters(r) == [it + 1] * 8, (it, r, emu.one_shot_counters(r))
+    emu.destroy()
+
+
 def test_emulated_ranks_misaligned_buffers():
     """Buffers that do not start on a 16-byte boundary take the element-granular path of the two-shot kernel."""
     _require_cuda()
