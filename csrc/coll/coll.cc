@@ -42,7 +42,8 @@ mcclResult_t checkCommon(mcclComm_t comm, mcclDataType_t dt) {
 
 // `what`, `bytes`, `stream` feed the optional trace (MCCL_TRACE); the span covers the launch on the
 // caller's stream (cuda) or the whole blocking call (tcp).
-mcclResult_t issue(mcclComm_t comm, const char* what, size_t bytes, mcclStream_t stream, std::function<mcclResult_t()> fn) {
+mcclResult_t issue(mcclComm_t comm, const char* what, size_t bytes, mcclStream_t stream, std::function<mcclResult_t()> fn,
+                   const CollCall& call = CollCall()) {
   auto traced = [=]() -> mcclResult_t {
     NvtxRange range(what);
     if (!traceEnabled()) {
@@ -56,7 +57,11 @@ mcclResult_t issue(mcclComm_t comm, const char* what, size_t bytes, mcclStream_t
     traceEnd(comm, span, stream);
     return rc;
   };
-  if (groupActive()) return groupRecordColl(comm, [=]() { return commLaunch(comm, traced); });
+  if (groupActive()) {
+    CollCall c = call;
+    c.stream = stream;
+    return groupRecordColl(comm, [=]() { return commLaunch(comm, traced); }, c);
+  }
   return commLaunch(comm, traced);
 }
 
@@ -75,7 +80,7 @@ mcclResult_t mcclAllReduce(mcclComm_t comm, const void* sendbuff, void* recvbuff
     comm->lastAlgo.store(algo);
     if (comm->cuda) return cudaCollective(comm, mcclCollAllReduce, sendbuff, recvbuff, count, dt, op, 0, algo, stream);
     return cpuAllReduce(comm, sendbuff, recvbuff, count, dt, op, algo);
-  });
+  }, [&] { CollCall c; c.coll = mcclCollAllReduce; c.send = sendbuff; c.recv = recvbuff; c.count = count; c.dt = dt; c.op = op; c.algo = algo; return c; }());
 }
 
 mcclResult_t mcclAllGather(mcclComm_t comm, const void* sendbuff, void* recvbuff, size_t sendcount, mcclDataType_t dt,

@@ -82,7 +82,18 @@ mcclResult_t cpuRunP2pBatch(mcclComm* c, const std::vector<P2pOp>& ops);
 mcclResult_t cpuRecvAny(mcclComm* c, void* buf, size_t bytes, int* src);
 bool         groupActive();
 mcclResult_t groupRecord(const P2pOp& op);                         // queue a Send/Recv inside a group
-mcclResult_t groupRecordColl(mcclComm* comm, std::function<mcclResult_t()> launch);   // queue a collective
+// What a recorded collective was called with; lets GroupEnd fuse the all-reduce calls of a group into one launch.
+struct CollCall {
+  int coll = -1;
+  const void* send = nullptr;
+  void* recv = nullptr;
+  size_t count = 0;
+  mcclDataType_t dt = mcclFloat32;
+  mcclRedOp_t op = mcclSum;
+  int algo = -1;
+  mcclStream_t stream = nullptr;
+};
+mcclResult_t groupRecordColl(mcclComm* comm, std::function<mcclResult_t()> launch, const CollCall& call);   // queue a collective
 
 // ---- cuda transport: implemented in the .cu files ----------------------------------------------------
 mcclResult_t cudaCommInit(mcclComm* c);                            // heap, control block, peer mappings, NVLS
@@ -91,6 +102,9 @@ void         cudaCommDestroy(mcclComm* c);
 mcclResult_t cudaCommAsyncError(mcclComm* c, mcclResult_t* out);
 mcclResult_t cudaCollective(mcclComm* c, int coll, const void* send, void* recv, size_t count, mcclDataType_t dt,
                             mcclRedOp_t op, int root, int algo, mcclStream_t stream);
+// Launch the all-reduce calls among `calls` that can share one kernel (symmetric, 16-byte aligned buffers of at
+// least 16 bytes per rank) and set done[i] for them; the others are left to their own launches.
+mcclResult_t cudaGroupAllReduce(mcclComm* c, const std::vector<CollCall>& calls, std::vector<char>* done);
 mcclResult_t cudaP2pBatch(mcclComm* c, const std::vector<P2pOp>& ops, mcclStream_t stream);
 mcclResult_t cudaRecvAny(mcclComm* c, void* buf, size_t bytes, int* src, mcclStream_t stream);
 mcclResult_t cudaBarrier(mcclComm* c, mcclStream_t stream);

@@ -1,8 +1,10 @@
 // Send / Recv / RecvAny and call grouping.
 // Inside mcclGroupStart/End nothing runs: Send/Recv and collectives are recorded per thread and issued
-// by the outermost GroupEnd.  Per communicator the recorded collectives run first, in program order, then
-// all Send/Recv as one batch in which every (peer, direction) flow progresses concurrently, so a rank may
-// post Send(p) and Recv(p) in either order without deadlock.  Batches of different communicators are
+// by the outermost GroupEnd.  Per communicator: first the all-reduce calls that can share a kernel, as ONE
+// launch (cuda transport); then the other recorded collectives, in program order; then all Send/Recv as one
+// batch in which every (peer, direction) flow progresses concurrently, so a rank may post Send(p) and Recv(p)
+// in either order without deadlock.  The calls of a group are independent of one another by contract (none may
+// consume another's result), and on the cuda transport they must all name the same stream.  Batches of different communicators are
 // issued concurrently so that two ranks that order their communicators differently cannot block each
 // other.  Errors raised while recording are latched and returned by GroupEnd.
 // Parity: src/p2p.cc:20-321 of the reference (which defers only Send/Recv; collectives there run at once).
@@ -25,6 +27,7 @@ struct GroupEntry {
   bool isColl;
   P2pOp op;
   std::function<mcclResult_t()> launch;
+  CollCall call;
 };
 struct GroupState {
   int depth = 0;
@@ -37,11 +40,11 @@ thread_local GroupState g_group;
 bool groupActive() { return g_group.depth > 0; }
 
 mcclResult_t groupRecord(const P2pOp& op) {
-  g_group.entries.push_back(GroupEntry{op.comm, false, op, nullptr});
+  g_group.entries.push_back(GroupEntry{op.comm, false, op, nullptr, CollCall()});
   return mcclSuccess;
 }
-mcclResult_t groupRecordColl(mcclComm* comm, std::function<mcclResult_t()> launch) {
-  g_group.entries.push_back(GroupEntry{comm, true, P2pOp{}, std::move(launch)});
+mcclResult_t groupRecordColl(mcclComm* comm, std::function<mcclResult_t()> launch, const CollCall& call) {
+  g_group.entries.push_back(GroupEntry{comm, true, P2pOp{}, std::move(launch), call});
   return mcclSuccess;
 }
 
@@ -112,8 +115,38 @@ static mcclResult_t issueComm(mcclComm* comm, std::vector<GroupEntry>& entries) 
   mcclResult_t first = mcclSuccess;
   std::vector<P2pOp> batch;
   mcclStream_t stream = nullptr;
-  for (GroupEntry& e : entries) {
-    if (e.comm != comm) continue;
+  // On the cuda transport a group is issued on ONE stream: its fused launches cannot honour an order between
+  // streams, so a group that names several is refused rather than silently reordered.
+  if (comm->cuda) {
+    bool have = false;
+    mcclStream_t seen = nullptr;
+    for (GroupEntry& e : entries) {
+      if (e.comm != comm) continue;
+      const mcclStream_t s = e.isColl ? e.call.stream : e.op.stream;
+      if (have && s != seen) {
+        MCCL_WARN("the calls of one group on one communicator must use one stream");
+        return noteFailure(mcclInvalidUsage, __FILE__, __LINE__);
+      }
+      have = true; seen = s;
+    }
+  }
+  // The all-reduce calls of the group that can share a kernel go out as one launch, at the place of the first.
+  std::vector<CollCall> calls;
+  std::vector<size_t> callEntry;
+  if (comm->cuda && comm->nRanks > 1) {
+    for (size_t i = 0; i < entries.size(); ++i)
+      if (entries[i].comm == comm && entries[i].isColl && entries[i].call.coll == mcclCollAllReduce) { calls.push_back(entries[i].call); callEntry.push_back(i); }
+  }
+  std::vector<char> fused(entries.size(), 0);
+  if (calls.size() > 1) {
+    std::vector<char> done;
+    mcclResult_t rc = commLaunch(comm, [&]() { return cudaGroupAllReduce(comm, calls, &done); });
+    if (rc != mcclSuccess) return rc;
+    for (size_t k = 0; k < done.size(); ++k) if (done[k]) fused[callEntry[k]] = 1;
+  }
+  for (size_t i = 0; i < entries.size(); ++i) {
+    GroupEntry& e = entries[i];
+    if (e.comm != comm || fused[i]) continue;
     if (e.isColl) {
       mcclResult_t rc = e.launch();
       if (rc != mcclSuccess && first == mcclSuccess) first = rc;

@@ -217,7 +217,8 @@ mcclResult_t arOneShot(const Call& k, const void* send, void* recv, size_t bytes
   return launched(k.c, "oneShotKernel");
 }
 
-bool nvlsType(mcclDataType_t dt, mcclRedOp_t op) {
+bool nvlsType(mcclDataType_t dt, mcclRedOp_t op, int n) {
+  if (!nvlsAvgExact(dt, op, n)) return false;
   if (dt == mcclFloat32) return op == mcclSum || op == mcclAvg;
   if (dt == mcclFloat16 || dt == mcclBfloat16) return op == mcclSum || op == mcclAvg || op == mcclMin || op == mcclMax;
   return false;
@@ -388,7 +389,7 @@ mcclResult_t allReduce(const Call& k, const void* send, void* recv, size_t count
   const size_t bytes = count * k.es;
   const bool vecOk = bytes % 16 == 0 && al16(send) && al16(recv);
   if (algo == mcclAlgoOneShot && vecOk && bytes <= k.st->layout.oneShotSlotBytes) return arOneShot(k, send, recv, bytes);
-  if (algo == mcclAlgoNvls && k.st->nvls && nvlsType(k.dt, k.op) && bytes % 16 == 0 && bytes / 16 >= (size_t)k.n)
+  if (algo == mcclAlgoNvls && k.st->nvls && nvlsType(k.dt, k.op, k.n) && bytes % 16 == 0 && bytes / 16 >= (size_t)k.n)
     return arNvls(k, send, recv, bytes);
   if ((algo == mcclAlgoRing || algo == mcclAlgoTree) && bytes % 16 == 0 && bytes / 16 >= (size_t)2 * k.n)
     return arRingTree(k, send, recv, bytes, algo);
@@ -450,7 +451,7 @@ mcclResult_t allGather(const Call& k, const void* send, void* recv, size_t sendc
 mcclResult_t reduceScatter(const Call& k, const void* send, void* recv, size_t recvcount, int algo) {
   const size_t blk = recvcount * k.es;
   const View sv = viewOf(k.st, send, blk * k.n);
-  if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op) && blk % 16 == 0 && al16(send) && al16(recv)) {
+  if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op, k.n) && blk % 16 == 0 && al16(send) && al16(recv)) {
     NvlsArgs a = baseNvls(k, blk);
     a.loadReduce = 1;
     a.mcStore = 0;
@@ -592,7 +593,7 @@ mcclResult_t reduce(const Call& k, const void* send, void* recv, size_t count, i
   const size_t bytes = count * k.es;
   const View sv = viewOf(k.st, send, bytes);
   const bool direct = algo == mcclAlgoOneShot;
-  if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op) && bytes % 16 == 0 && al16(send) &&
+  if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op, k.n) && bytes % 16 == 0 && al16(send) &&
       (k.r != root || al16(recv))) {
     if (nvlsSpread() && bytes >= (size_t)k.n * 16) {
       NvlsRootedArgs a;
@@ -966,6 +967,72 @@ mcclResult_t cudaCollective(mcclComm* c, int coll, const void* send, void* recv,
   return rc;
 }
 
+mcclResult_t cudaGroupAllReduce(mcclComm* c, const std::vector<CollCall>& calls, std::vector<char>* done) {
+  CudaState* st = c->cu;
+  done->assign(calls.size(), 0);
+  if (st == nullptr || c->nRanks < 2) return mcclSuccess;
+  MCCLCHECK(latchedError(c));
+  int dev = -1;
+  CUDACHECK(cudaGetDevice(&dev));
+  if (dev != c->device) CUDACHECK(cudaSetDevice(c->device));
+  const int n = c->nRanks;
+  GroupArgs a;
+  size_t total = 0;
+  int fusedNow = 0;
+  cudaStream_t s = nullptr;
+  auto reset = [&]() { memset(&a, 0, sizeof(a)); a.peers = st->peers; total = 0; };
+  auto flush = [&]() -> mcclResult_t {
+    if (a.nJobs == 0) return mcclSuccess;
+    bool allNvls = !a.anyTwoShot;
+    a.nCtas = pickCtas(c, total, allNvls ? mcclAlgoNvls : mcclAlgoTwoShot);
+    groupAllReduceKernel<<<a.nCtas, kThreads, 0, s>>>(a);
+    c->lastAlgo.store(allNvls ? mcclAlgoNvls : mcclAlgoTwoShot);
+    MCCL_TRACE("group of %d all-reduce calls, %zu bytes, one launch of %d CTAs", a.nJobs, total, a.nCtas);
+    mcclResult_t rc = launched(c, "groupAllReduceKernel");
+    reset();
+    return rc;
+  };
+  reset();
+  // A single fusable call gains nothing from this kernel: count them first.
+  std::vector<char> can(calls.size(), 0);
+  int fusable = 0;
+  for (size_t i = 0; i < calls.size(); ++i) {
+    const CollCall& k = calls[i];
+    const size_t bytes = k.count * mcclDataSize(k.dt);
+    if (k.coll != mcclCollAllReduce || bytes % 16 || bytes / 16 < (size_t)n || !al16(k.send) || !al16(k.recv)) continue;
+    if (!viewOf(st, k.send, bytes).sym() || !viewOf(st, k.recv, bytes).sym()) continue;
+    can[i] = 1;
+    ++fusable;
+  }
+  if (fusable < 2) { if (dev != c->device) cudaSetDevice(dev); return mcclSuccess; }
+  mcclResult_t rc = mcclSuccess;
+  for (size_t i = 0; i < calls.size() && rc == mcclSuccess; ++i) {
+    if (!can[i]) continue;
+    const CollCall& k = calls[i];
+    const size_t bytes = k.count * mcclDataSize(k.dt);
+    const View sv = viewOf(st, k.send, bytes), rv = viewOf(st, k.recv, bytes);
+    s = reinterpret_cast<cudaStream_t>(k.stream);
+    GroupJob& j = a.jobs[a.nJobs++];
+    j.bytes = bytes;
+    j.dt = k.dt;
+    j.op = (k.op == mcclAvg) ? mcclSum : k.op;
+    j.divisor = (k.op == mcclAvg) ? n : 1;
+    j.nvls = k.algo == mcclAlgoNvls && st->nvls && nvlsType(k.dt, k.op, n) && sv.mc() && rv.mc();
+    if (j.nvls) { j.mcIn = sv.mc(); j.mcOut = rv.mc(); }
+    else a.anyTwoShot = 1;
+    for (int p = 0; p < n; ++p) { j.in[p] = sv.peer(p); j.red[p] = rv.peer(p); }
+    j.out = static_cast<char*>(k.recv);
+    total += bytes;
+    (*done)[i] = 1;
+    ++fusedNow;
+    if (a.nJobs == MCCL_MAX_GROUP_JOBS) rc = flush();
+  }
+  if (rc == mcclSuccess) rc = flush();
+  (void)fusedNow;
+  if (dev != c->device) cudaSetDevice(dev);
+  return rc;
+}
+
 mcclResult_t cudaBarrier(mcclComm* c, mcclStream_t stream) {
   CudaState* st = c->cu;
   MCCLCHECK(latchedError(c));
@@ -992,31 +1059,44 @@ mcclResult_t cudaP2pBatch(mcclComm* c, const std::vector<P2pOp>& ops, mcclStream
     if (selfS[i]->bytes != selfR[i]->bytes) MCCLFAIL(mcclInvalidUsage);
     MCCLCHECK(launchCopy(c, selfS[i]->buf, selfR[i]->buf, 1, selfS[i]->bytes, selfS[i]->bytes, selfS[i]->bytes, s));
   }
-  // One CTA per (peer, direction) flow; a batch holds at most MCCL_MAX_P2P_OPS operations per launch.
-  std::vector<const P2pOp*> rest;
-  for (const P2pOp& op : ops) if (op.peer != c->rank && op.bytes > 0) rest.push_back(&op);
-  size_t pos = 0;
-  while (pos < rest.size()) {
-    P2pArgs a;
-    memset(&a, 0, sizeof(a));
-    a.peers = st->peers;
-    int flowOf[MCCL_MAX_RANKS][2];
-    for (auto& f : flowOf) f[0] = f[1] = -1;
-    int flows = 0;
-    while (pos < rest.size() && a.nOps < MCCL_MAX_P2P_OPS) {
-      const P2pOp* op = rest[pos++];
-      int& f = flowOf[op->peer][op->isSend ? 1 : 0];
-      if (f < 0) f = flows++;
-      P2pDesc& d = a.ops[a.nOps++];
-      d.isSend = (f << 1) | (op->isSend ? 1 : 0);
-      d.peer = op->peer;
-      d.buf = static_cast<char*>(op->buf);
-      d.bytes = op->bytes;
-    }
-    p2pKernel<<<flows, kThreads, 0, s>>>(a);
-    MCCLCHECK(launched(c, "p2pKernel"));
+  // One CTA per (peer, direction) flow, all flows of the batch in ONE launch (two launches in a row could wait for
+  // each other across ranks).  The descriptors travel as kernel arguments; a batch longer than that holds goes
+  // through stream-ordered device memory.
+  std::vector<P2pDesc> descs;
+  int flowOf[MCCL_MAX_RANKS][2];
+  for (auto& f : flowOf) f[0] = f[1] = -1;
+  int flows = 0;
+  for (const P2pOp& op : ops) {
+    if (op.peer == c->rank || op.bytes == 0) continue;
+    int& f = flowOf[op.peer][op.isSend ? 1 : 0];
+    if (f < 0) f = flows++;
+    P2pDesc d;
+    d.isSend = (f << 1) | (op.isSend ? 1 : 0);
+    d.peer = op.peer;
+    d.buf = static_cast<char*>(op.buf);
+    d.bytes = op.bytes;
+    descs.push_back(d);
   }
-  return mcclSuccess;
+  if (descs.empty()) return mcclSuccess;
+  P2pArgs a;
+  memset(&a, 0, sizeof(a));
+  a.peers = st->peers;
+  a.nOps = (int)descs.size();
+  void* devDescs = nullptr;
+  if (descs.size() <= MCCL_MAX_P2P_OPS) {
+    memcpy(a.ops, descs.data(), descs.size() * sizeof(P2pDesc));
+  } else {
+    CUDACHECK(cudaMallocAsync(&devDescs, descs.size() * sizeof(P2pDesc), s));
+    CUDACHECK(cudaMemcpyAsync(devDescs, descs.data(), descs.size() * sizeof(P2pDesc), cudaMemcpyHostToDevice, s));
+    a.more = static_cast<const P2pDesc*>(devDescs);
+  }
+  p2pKernel<<<flows, kThreads, 0, s>>>(a);
+  mcclResult_t rc = launched(c, "p2pKernel");
+  if (devDescs) {
+    CUDACHECK(cudaFreeAsync(devDescs, s));
+    CUDACHECK(cudaStreamSynchronize(s));       // `descs` is pageable memory the copy may still be reading
+  }
+  return rc;
 }
 
 mcclResult_t cudaRecvAny(mcclComm* c, void* buf, size_t bytes, int* src, mcclStream_t stream) {

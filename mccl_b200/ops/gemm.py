@@ -43,9 +43,10 @@ def supported(M: int, N: int, K: int, ranks: int = 1) -> bool:
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "none", max_ctas: int = 0,
-         stream=None, two_sm: bool = False) -> torch.Tensor:
+         stream=None, two_sm: bool | None = None) -> torch.Tensor:
     """out[M, N] = act(x[M, K] @ w[N, K].T) in bf16 with fp32 accumulation, by the library's own tcgen05 kernel.
-    `two_sm` selects the form in which pairs of SMs share a 256-row tile (needs M % 256 == 0)."""
+    `two_sm` selects the form in which pairs of SMs share a 256-row tile (needs M % 256 == 0); by default it is
+    used whenever the shape allows it."""
     if not x.is_cuda:
         raise RuntimeError("mccl gemm runs on CUDA (sm_100a) only")
     assert x.dtype == w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
@@ -56,6 +57,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epil
         raise ValueError(f"unsupported GEMM shape {M}x{N}x{K}: M % 128, N % 64 and K % 64 must be 0")
     if out is None:
         out = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+    if two_sm is None:
+        two_sm = M % 256 == 0
     if two_sm and M % 256:
         raise ValueError(f"the two-SM GEMM needs M % 256 == 0 (got {M})")
     fn = _lib().mcclTpGemm2 if two_sm else _lib().mcclTpGemm

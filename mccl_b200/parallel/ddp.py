@@ -58,8 +58,8 @@ class DistributedDataParallel(nn.Module):
     ranks while backward runs; `step()` applies the fused (optionally sharded, optionally norm-clipped) AdamW update."""
 
     def __init__(self, module: nn.Module, comm: Optional[Communicator] = None, bucket_mb: Optional[float] = None,
-                 overlap: bool = True, comm_ctas: int = 16, weight_decay: float = 0.1, betas=(0.9, 0.95), eps: float = 1e-8,
-                 shard_optimizer: bool = False):
+                 overlap: bool = True, comm_ctas: Optional[int] = None, weight_decay: float = 0.1, betas=(0.9, 0.95),
+                 eps: float = 1e-8, shard_optimizer: bool = False, sync_params: bool = True):
         super().__init__()
         self.module = module
         self.comm = comm
@@ -67,6 +67,9 @@ class DistributedDataParallel(nn.Module):
         self.rank = comm.rank if comm is not None else 0
         self.sharded = bool(shard_optimizer) and self.world > 1
         self.overlap = overlap
+        # CTAs a bucket's all-reduce may take while backward is still running (the rest stay with the GEMMs)
+        self.comm_ctas = int(os.environ.get("MCCL_DDP_CTAS", "16")) if comm_ctas is None else int(comm_ctas)
+        self._launched_count = 0
         self.betas, self.eps = betas, eps
         self.step_count = 0
         self._norm_sq = None
@@ -99,19 +102,35 @@ class DistributedDataParallel(nn.Module):
             if cur:
                 self.buckets.append(_Bucket(cur, weight_decay if decay else 0.0, align))
         self._bucket_of = {}
+        if self.world > 1 and sync_params:
+            self._sync_initial_state(module)
         for b in self.buckets:
             self._materialize(b)
             for p in b.params:
                 self._bucket_of[p] = b
         if self.world > 1:
-            if comm_ctas:
-                comm.set_max_ctas(comm_ctas)      # leave the SMs to the backward GEMMs
+            if self.comm_ctas:
+                comm.set_max_ctas(self.comm_ctas)      # leave the SMs to the backward GEMMs
             self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self.device.type == "cuda" else None
             for p in params:
                 p.register_post_accumulate_grad_hook(self._on_grad)
         self._reset()
 
     # ---- construction helpers
+    def _sync_initial_state(self, module: nn.Module) -> None:
+        """Every replica starts from rank 0's parameters and buffers, whatever each rank was seeded with (only
+        gradients are averaged afterwards, so replicas that start apart stay apart)."""
+        with torch.no_grad():
+            for t in list(module.parameters()) + list(module.buffers()):
+                if t.numel() == 0:
+                    continue
+                flat = t.data.contiguous().view(-1)
+                self.comm.broadcast(flat, flat, root=0)
+                if flat.data_ptr() != t.data.data_ptr():
+                    t.data.copy_(flat.view(t.shape))
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
     def _materialize(self, b: _Bucket) -> None:
         dev, dt = self.device, self.dtype
         if self.world > 1 and dev.type == "cuda":
@@ -142,17 +161,26 @@ class DistributedDataParallel(nn.Module):
         for b in self.buckets:
             b.pending = len(b.params)
             b.launched = False
+        self._launched_count = 0
 
     # ---- backward-time communication
     def _launch(self, b: _Bucket) -> None:
         b.launched = True
+        self._launched_count += 1
         if self.world == 1 or not self._sync:
             return
         if self.overlap and self.comm_stream is not None:
             b.ready_event = torch.cuda.Event()
             b.ready_event.record()
             self.comm_stream.wait_event(b.ready_event)
+            # The bucket that closes last has nothing left to overlap with (backward is over when its last
+            # gradient arrives): it gets the whole GPU, the others stay within comm_ctas.
+            tail = self.comm_ctas and self._launched_count == len(self.buckets)
+            if tail:
+                self.comm.set_max_ctas(0)
             self._reduce(b, self.comm_stream)
+            if tail:
+                self.comm.set_max_ctas(self.comm_ctas)
             b.done_event = torch.cuda.Event()
             b.done_event.record(self.comm_stream)
         else:

@@ -615,5 +615,89 @@ def tp_ffn():
     comm.finalize(); comm.destroy()
 
 
+def grouped_allreduce():
+    """A group of all-reduce calls goes out as one launch: results against the oracle, the launch count, a group with
+    a call that cannot be fused, a group that names two streams, and a timing of 8 x 1 MB grouped against one by one."""
+    comm = make_comm()
+    cases = [(torch.float32, 4096, "sum"), (torch.bfloat16, 70000, "avg"), (torch.int32, 1 << 16, "max"),
+             (torch.float16, 8 * WORLD, "min"), (torch.bfloat16, (1 << 20) + 8, "sum"), (torch.float32, 1 << 18, "avg"),
+             (torch.float64, 1024, "sum"), (torch.int64, 2048, "sum")]
+    for rep in range(3):                                  # repeated groups reuse flags and counters
+        bufs = []
+        for dtype, n, op in cases:
+            b = comm.empty(n, dtype)
+            b.copy_(gen(RANK, n, dtype))
+            bufs.append(b)
+        torch.cuda.synchronize(); comm.host_barrier()
+        before = comm.launch_count
+        with mccl.group():
+            for b, (dtype, n, op) in zip(bufs, cases):
+                comm.all_reduce(b, op=op)
+        assert comm.launch_count == before + 1, ("launches for one group", comm.launch_count - before)
+        torch.cuda.synchronize()
+        assert canary_ok(comm)
+        for b, (dtype, n, op) in zip(bufs, cases):
+            check(("grouped", rep, dtype, n, op), b, oracle(n, dtype, op), dtype)
+            comm.free_raw(b.data_ptr())
+    # out of place, plus one call on an ordinary tensor, which takes its own launch after the fused one
+    a_in, a_out = comm.empty(5000, torch.float32), comm.empty(5000, torch.float32)
+    b_sym = comm.empty(3000, torch.bfloat16)
+    plain = torch.empty(777, device=DEV, dtype=torch.float32)
+    a_in.copy_(gen(RANK, 5000, torch.float32)); b_sym.copy_(gen(RANK, 3000, torch.bfloat16)); plain.copy_(gen(RANK, 777, torch.float32))
+    keep = a_in.clone()
+    torch.cuda.synchronize(); comm.host_barrier()
+    before = comm.launch_count
+    with mccl.group():
+        comm.all_reduce(a_in, a_out, op="sum")
+        comm.all_reduce(plain, op="sum")
+        comm.all_reduce(b_sym, op="avg")
+    torch.cuda.synchronize()
+    assert comm.launch_count > before + 1
+    assert torch.equal(a_in, keep)
+    check("grouped out of place", a_out, oracle(5000, torch.float32, "sum"), torch.float32)
+    check("grouped, own launch", plain, oracle(777, torch.float32, "sum"), torch.float32)
+    check("grouped bf16 avg", b_sym, oracle(3000, torch.bfloat16, "avg"), torch.bfloat16)
+    # two streams in one group are refused and leave the communicator usable
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    try:
+        with mccl.group():
+            comm.all_reduce(a_out, op="sum", stream=s1)
+            comm.all_reduce(b_sym, op="sum", stream=s2)
+        raise AssertionError("a group with two streams must be refused")
+    except mccl.MCCLError as exc:
+        assert exc.code == L.INVALID_USAGE, exc.code
+    torch.cuda.synchronize(); comm.host_barrier()
+    # timing: 8 x 1 MB bf16, grouped against one by one
+    k, n = 8, (1 << 20) // 2
+    bufs = [comm.empty(n, torch.bfloat16) for _ in range(k)]
+    for b in bufs:
+        b.normal_()
+
+    def one_by_one():
+        for b in bufs:
+            comm.all_reduce(b, op="sum")
+
+    def grouped():
+        with mccl.group():
+            for b in bufs:
+                comm.all_reduce(b, op="sum")
+
+    times = {}
+    for name, fn in (("one_by_one", one_by_one), ("grouped", grouped)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(); comm.host_barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        times[name] = e0.elapsed_time(e1) / 20 * 1e3
+    if RANK == 0:
+        print(f"GROUP_TIMING world={WORLD} 8x1MB bf16 sum: one by one {times['one_by_one']:.1f} us, grouped {times['grouped']:.1f} us", flush=True)
+    assert canary_ok(comm)
+    comm.finalize(); comm.destroy()
+
+
 if __name__ == "__main__":
     globals()[sys.argv[1]]()

@@ -375,7 +375,7 @@ def ddp_cpu():
     from mccl_b200.models.gpt2 import GPT2, GPT2Config
     from mccl_b200.parallel.ddp import DistributedDataParallel
     comm = make_comm()
-    torch.manual_seed(0)
+    torch.manual_seed(17 * RANK)               # replicas seeded apart: the wrapper must start them from rank 0's weights
     cfg = GPT2Config.tiny()
     model = GPT2(cfg)
     ddp = DistributedDataParallel(model, comm, bucket_mb=0.25)
@@ -386,6 +386,8 @@ def ddp_cpu():
     torch.manual_seed(0)
     single = GPT2(cfg)
     ref = DistributedDataParallel(single, None, bucket_mb=0.25)
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), single.named_parameters()):
+        assert torch.equal(p1, p2), ("initial parameters differ from rank 0's", n1)
     # gradients of the first step: the bucket all-reduce (avg) must reproduce the global-batch gradient
     loss = ddp(mine[:, :-1], mine[:, 1:]); loss.backward(); ddp.finish_backward()
     l2 = ref(tokens[:, :-1], tokens[:, 1:]); l2.backward()

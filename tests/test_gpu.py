@@ -13,12 +13,6 @@ NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
 need2 = pytest.mark.skipif(NGPU < 2, reason="needs two GPUs")
 
 
-# Paths that no run on GPUs has confirmed yet: their tests run only when MCCL_TEST_UNVERIFIED=1, so that an
-# unconfirmed path cannot stop the confirmed tier.
-unverified = pytest.mark.skipif(os.environ.get("MCCL_TEST_UNVERIFIED") != "1" or NGPU < 2,
-                                reason="not yet confirmed on GPUs: set MCCL_TEST_UNVERIFIED=1 (needs two GPUs)")
-
-
 def _require_cuda():
     if NGPU < 1:
         pytest.fail("GPU tests need a CUDA device (run the CPU tier with -m 'not gpu')")
@@ -154,7 +148,7 @@ def test_tcgen05_gemm_matches_fp32_reference():
         x = (torch.randn(M, K, device=dev) * 0.5).to(torch.bfloat16)
         w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
         for epi in ("none", "silu"):
-            y = G.gemm(x, w, epilogue=epi)
+            y = G.gemm(x, w, epilogue=epi, two_sm=False)
             torch.cuda.synchronize()
             assert G.last_error() == 0
             ref = x.float() @ w.float().t()
@@ -166,7 +160,6 @@ def test_tcgen05_gemm_matches_fp32_reference():
         G.gemm(torch.zeros(100, 64, device=dev, dtype=torch.bfloat16), torch.zeros(64, 64, device=dev, dtype=torch.bfloat16))
 
 
-@pytest.mark.skipif(os.environ.get("MCCL_TEST_UNVERIFIED") != "1", reason="not yet confirmed on a GPU: set MCCL_TEST_UNVERIFIED=1")
 def test_two_sm_gemm_matches_fp32_reference():
     _require_cuda()
     from mccl_b200.ops import gemm as G
@@ -186,9 +179,10 @@ def test_two_sm_gemm_matches_fp32_reference():
             assert err < 1e-2, (M, N, K, epi, err)
 
 
-@unverified
-def test_fused_tp_ffn_two_sm_kernels():
-    assert_all_ok(run_ranks(2, "tp_ffn", worker="_gpu_worker.py", env={"MCCL_GEMM_2SM": "1"}, timeout=300))
+@need2
+def test_fused_tp_ffn_one_sm_kernels():
+    # the two-SM kernels are the default; MCCL_GEMM_2SM=0 selects the one-SM form
+    assert_all_ok(run_ranks(2, "tp_ffn", worker="_gpu_worker.py", env={"MCCL_GEMM_2SM": "0"}, timeout=300))
 
 
 @need2
@@ -416,49 +410,54 @@ def test_forced_ring_and_tree_for_other_collectives():
     assert_all_ok(run_ranks(min(NGPU, 4), "forced_ring_tree", worker="_gpu_worker.py", timeout=600))
 
 
-@unverified
+@need2
 def test_torch_distributed_backend_on_gpus(tmp_path):
     assert_all_ok(run_ranks(2, "c10d_backend_gpu", worker="_gpu_worker.py", args={"rendezvous": str(tmp_path / "rdv")}, timeout=300))
 
 
-@unverified
+@need2
 def test_gather_scatter_alltoallv_on_gpus():
     assert_all_ok(run_ranks(min(NGPU, 4), "rooted_and_ragged_gpu", worker="_gpu_worker.py", timeout=300))
 
 
-@unverified
+@need2
 def test_trainable_fused_tensor_parallel_mlp():
     assert_all_ok(run_ranks(2, "tp_mlp_trainable", worker="_gpu_worker.py", timeout=600))
 
 
-@unverified
+@need2
 def test_fused_moe_dispatch_and_combine():
     assert_all_ok(run_ranks(min(NGPU, 4), "moe_fused", worker="_gpu_worker.py", timeout=600))
 
 
-@unverified
+@need2
 def test_model_parallel_layers_on_gpus():
     assert_all_ok(run_ranks(2, "parallel_layers_gpu", worker="_gpu_worker.py", timeout=600))
 
 
-@unverified
+@need2
 def test_ddp_sharded_optimizer_on_gpus():
     assert_all_ok(run_ranks(min(NGPU, 4), "ddp_sharded", worker="_gpu_worker.py", timeout=600))
 
 
-@unverified
+@need2
 def test_collectives_replay_from_a_cuda_graph():
     assert_all_ok(run_ranks(2, "graph_capture", worker="_gpu_worker.py", timeout=300))
 
 
-@unverified
+@need2
 def test_composed_ring_and_tree_forms():
     assert_all_ok(run_ranks(min(NGPU, 4), "forced_ring_tree", worker="_gpu_worker.py", args={"composed": True}, timeout=900))
 
 
-@unverified
+@need2
 def test_rooted_collectives_spread_over_all_ranks():
     assert_all_ok(run_ranks(min(NGPU, 4), "rooted_spread", worker="_gpu_worker.py", env={"MCCL_NVLS_SPREAD": "1"}, timeout=600))
+
+
+@need2
+def test_group_of_all_reduce_calls_is_one_launch():
+    assert_all_ok(run_ranks(min(NGPU, 4), "grouped_allreduce", worker="_gpu_worker.py", timeout=300))
 
 
 @need2

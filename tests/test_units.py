@@ -470,3 +470,41 @@ def test_result_fatal_matches_the_latching_rule(lib):
     fatal = {L.SYSTEM_ERROR, L.INTERNAL_ERROR, L.REMOTE_ERROR}
     for code in range(8):
         assert bool(lib.mcclResultFatal(code)) == (code in fatal)
+
+
+def test_python_wrappers_refuse_mismatched_buffers():
+    """Sizes, dtypes and devices are checked in Python: a short receive buffer must raise, not be overrun."""
+    import numpy as np
+    import torch
+    import mccl_b200 as mccl
+    comm = mccl.Communicator(1, mccl.get_unique_id(), 0, transport="tcp")
+    x = torch.ones(16)
+    with pytest.raises(ValueError):
+        comm.all_reduce(x, torch.empty(15))
+    with pytest.raises(ValueError):
+        comm.all_reduce(x, torch.empty(16, dtype=torch.float64))
+    with pytest.raises(TypeError):
+        comm.all_reduce(x, np.empty(16, dtype=np.float32))
+    with pytest.raises(ValueError):
+        comm.all_gather(x, torch.empty(15))
+    with pytest.raises(ValueError):
+        comm.reduce_scatter(torch.ones(7), torch.empty(8))
+    with pytest.raises(ValueError):
+        comm.broadcast(torch.ones(7), torch.empty(8))
+    with pytest.raises(ValueError):
+        comm.reduce(x, torch.empty(8))
+    with pytest.raises(ValueError):
+        comm.all_to_all(x, torch.empty(8))
+    with pytest.raises(ValueError):
+        comm.gather(x, torch.empty(8))
+    with pytest.raises(ValueError):
+        comm.scatter(torch.ones(4), torch.empty(8))
+    with pytest.raises(ValueError):
+        comm.all_to_all_v(x, [17], torch.empty(32), [17])
+    # well-formed calls still go through
+    y = torch.empty(16)
+    comm.all_reduce(x, y)
+    comm.all_gather(x, y)
+    comm.broadcast(x, y)
+    assert torch.equal(x, y)
+    comm.finalize(); comm.destroy()
