@@ -48,6 +48,9 @@ def parse():
     ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "tiny"])
     ap.add_argument("--no-extras", action="store_true", help="skip the all-reduce bus-bandwidth table")
     ap.add_argument("--no-floor", action="store_true", help="skip the torch-DDP-over-NCCL arm that follows the mccl arm")
+    ap.add_argument("--eager", action="store_true",
+                    help="mccl arm: issue every step kernel by kernel instead of replaying the step recorded in a CUDA graph "
+                         "(DistributedDataParallel.graphed_step)")
     ap.add_argument("--table-max-mb", type=int, default=32768, help="largest all-reduce of the bus-bandwidth table")
     ap.add_argument("--shard-optimizer", action="store_true",
                     help="reduce-scatter gradients, update 1/world of the parameters per rank, all-gather them (ZeRO stage 1)")
@@ -166,8 +169,43 @@ def run_arm(job: Job, impl: str) -> dict:
     dev_tokens = host_tokens.to(dev)
 
     for i in range(args.warmup):
-        loss = train_step(host_tokens[i % pool].to(dev, non_blocking=True))
-        loss.item()
+        train_step(host_tokens[i % pool].to(dev, non_blocking=True)).item()    # no reference to the step's autograd graph is kept
+
+    res_extra = {}
+    graphed = impl == "mccl" and not args.eager
+    if graphed:
+        # The step issued kernel by kernel first (a short device-timed run, for the record), then recorded once in a
+        # CUDA graph through the library's API; the timed regions below replay it.
+        job.barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k_eager = min(args.steps, 10)
+        ev0.record()
+        for i in range(k_eager):
+            train_step(dev_tokens[i % pool])
+        ev1.record()
+        job.barrier()
+        res_extra["eager_ms"] = job.host_max(ev0.elapsed_time(ev1) / k_eager)
+        host_idx = host_tokens[:, :, :-1].contiguous().pin_memory()
+        host_tgt = host_tokens[:, :, 1:].contiguous().pin_memory()
+        dev_idx, dev_tgt = host_idx.to(dev), host_tgt.to(dev)
+        step = ddp.graphed_step((dev_idx[0], dev_tgt[0]), lr=3e-4, max_grad_norm=1.0, warmup=0)
+        per_step = step.launches_per_step
+        replays = [0]
+        launches = lambda: replays[0] * per_step
+
+        def train_step(tokens):          # tokens: an index into the pool (device-resident batch) or a host batch pair
+            replays[0] += 1
+            if isinstance(tokens, int):
+                return step(dev_idx[tokens], dev_tgt[tokens])
+            return step(tokens[0], tokens[1])
+
+        for i in range(args.warmup):
+            train_step(i % pool).item()
+        dev_batch = lambda i: i % pool
+        host_batch = lambda i: (host_idx[i % pool], host_tgt[i % pool])      # copied host -> device inside the step call
+    else:
+        dev_batch = lambda i: dev_tokens[i % pool]
+        host_batch = lambda i: host_tokens[i % pool].to(dev, non_blocking=True)
 
     # ---- device-timed region: K steps, inputs already on the device
     job.barrier()
@@ -175,7 +213,7 @@ def run_arm(job: Job, impl: str) -> dict:
     l0 = launches()
     e0.record()
     for i in range(args.steps):
-        train_step(dev_tokens[i % pool])
+        train_step(dev_batch(i))
     e1.record()
     job.barrier()
     dev_ms = e0.elapsed_time(e1) / args.steps
@@ -185,14 +223,13 @@ def run_arm(job: Job, impl: str) -> dict:
     t0 = time.perf_counter()
     last = 0.0
     for i in range(args.steps):
-        tokens = host_tokens[i % pool].to(dev, non_blocking=True)
-        last = train_step(tokens).item()
+        last = train_step(host_batch(i)).item()
     job.barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     dev_ms, e2e_ms = job.host_max(dev_ms), job.host_max(e2e_ms)
 
     res = {"impl": impl, "dev_ms": dev_ms, "e2e_ms": e2e_ms, "launches": int(my_launches), "final_loss": last,
-           "params": model.num_params(), "cfg": cfg}
+           "params": model.num_params(), "cfg": cfg, "graphed": graphed, **res_extra}
 
     # ---- after the timed steps every replica must hold the same bytes (the all-reduce returns identical results
     # on every rank and the ranks started from the same weights)
@@ -215,10 +252,14 @@ def run_arm(job: Job, impl: str) -> dict:
         ddp.world = 1
         for b in ddp.buckets:
             b.done_event = None
+        if graphed:
+            step = ddp.graphed_step((dev_idx[0], dev_tgt[0]), lr=3e-4, max_grad_norm=1.0, warmup=0)   # recorded without the all-reduce
+            for i in range(3):
+                train_step(i % pool)
         job.barrier()
         e0.record()
         for i in range(args.steps):
-            train_step(dev_tokens[i % pool])
+            train_step(dev_batch(i))
         e1.record()
         job.barrier()
         res["exposed_ms"] = max(0.0, dev_ms - job.host_max(e0.elapsed_time(e1) / args.steps))
@@ -381,10 +422,16 @@ def main() -> int:
                    "l2": "working set per step (0.7 GB weights + activations) exceeds the 126 MB L2; no flush needed"},
         "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", [])},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(res["e2e_ms"], 3),
-                "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": (2 * B * S * 8) if res.get("graphed") else B * (S + 1) * 8, "d2h_bytes_per_step": 4},
         "gpu_launches": res["launches"],
         "final_loss": res["final_loss"],
     }
+    if args.impl == "mccl":
+        out["step_mode"] = ("one CUDA graph per step, recorded by DistributedDataParallel.graphed_step and replayed"
+                            if res["graphed"] else "eager: every kernel issued by the host")
+        if "eager_ms" in res:
+            out["eager"] = {"ms_per_step": round(res["eager_ms"], 3), "value": round(tokens_per_step / (res["eager_ms"] * 1e-3), 1),
+                            "note": "the same step issued kernel by kernel (device-timed, maximum over ranks)"}
     if "replicas_identical" in res:
         out["replicas_identical"] = res["replicas_identical"]
     if "exposed_ms" in res:

@@ -4,7 +4,8 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench/allreduce_sweep.py [--sizes-mb 64,256,1024,4096,32768] [--dtypes bf16,fp32] [--ops sum,avg] [--algos auto]
 
-Buffers are symmetric (mcclMemAlloc) and reduced in place; values ~N(0,1) seeded by rank.  Every number is
+Buffers are symmetric (mcclMemAlloc) and reduced in place (`--plain` adds the same call on an ordinary torch
+tensor, which is staged); values ~N(0,1) seeded by rank.  Every number is
 timed on the device with CUDA events after warm-up and is the maximum over ranks.  bus GB/s =
 bytes / time * 2(n-1)/n.  Rank 0 prints one JSON line per (size, dtype, op).
 """
@@ -34,6 +35,8 @@ def main() -> int:
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--ctas-list", default="", help="tuning aid: run every algorithm with each of these exact CTA counts")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--plain", action="store_true",
+                    help="also time the call on an ordinary torch tensor (staged through the communicator's symmetric scratch)")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     lr = int(os.environ.get("LOCAL_RANK", rank))
@@ -90,6 +93,13 @@ def main() -> int:
                             row[f"mccl_{algo}_ran"] = comm.last_algo
                         buf.normal_(generator=g)      # avg/sum in place would otherwise shrink or overflow the values
                 comm.set_ctas(0)
+                if args.plain:
+                    plain = ref if ref is not None else torch.empty(n, device=dev, dtype=dt)
+                    plain.normal_(generator=g)
+                    ms = timed(lambda: comm.all_reduce(plain, op=op), iters)
+                    row["mccl_plain_us"] = round(ms * 1e3, 1)
+                    row["mccl_plain_busbw"] = round(nbytes / ms / 1e6 * k, 1)
+                    row["plain_vs_symmetric"] = round(row["mccl_auto_us"] / (ms * 1e3), 3) if "mccl_auto_us" in row else None
                 assert comm.async_error() == 0
                 if rank == 0:
                     print(json.dumps(row), flush=True)

@@ -198,10 +198,40 @@ mcclResult_t mcclCommInitRankConfig(mcclComm_t* out, int nRanks, mcclUniqueId id
       goto fail;
     }
   }
+  if (cuda) {
+    // One GPU per rank: the kernels of different ranks wait for one another, and nothing makes two kernels of
+    // different processes run at the same time on one GPU.
+    for (int a = 0; a < nRanks; ++a)
+      for (int b = a + 1; b < nRanks; ++b)
+        if (c->infos[a].hostHash == c->infos[b].hostHash && !strncmp(c->infos[a].busId, c->infos[b].busId, sizeof(c->infos[a].busId))) {
+          MCCL_WARN("ranks %d and %d of this communicator use the same GPU (%s): set one device per rank before creating it", a, b,
+                    c->infos[a].busId);
+          rc = mcclInvalidUsage;
+          goto fail;
+        }
+  }
   MCCLCHECKGOTO(buildPlan(c), rc, fail);
   if (cuda) {
     MCCLCHECKGOTO(cudaCommInit(c), rc, fail);
-    if (envInt("MCCL_CALIBRATE", 0) != 0) MCCLCHECKGOTO(cudaCalibrate(c), rc, fail);
+    // The tuner's constants for this machine: loaded from the cache of an earlier calibration when there is one,
+    // else measured now (a few tens of milliseconds) and cached.  MCCL_CALIBRATE=1 measures afresh, =0 keeps the
+    // built-in constants.  Rank 0 decides, so every rank takes the same path.
+    if (nRanks > 1) {
+      const int mode = (int)envInt("MCCL_CALIBRATE", -1);
+      char gpuTag[48];
+      snprintf(gpuTag, sizeof(gpuTag), "cc%d-sm%d", (int)c->infos[0].cc, (int)c->infos[0].smCount);
+      const std::string path = tunerCachePath(nRanks, gpuTag);
+      int have = 0;
+      if (rank == 0 && mode < 0) { FILE* f = fopen(path.c_str(), "r"); if (f) { have = 1; fclose(f); } }
+      std::vector<int> haves(nRanks, 0);
+      MCCLCHECKGOTO(bootstrapAllGather(c->bs, &have, haves.data(), sizeof(int)), rc, fail);
+      if (haves[0]) {
+        MCCLCHECKGOTO(tunerLoadCache(&c->tuner, path.c_str()), rc, fail);
+      } else if (mode != 0) {
+        MCCLCHECKGOTO(cudaCalibrate(c), rc, fail);
+        if (rank == 0 && c->tuner.measured) tunerSaveCache(c->tuner, path.c_str());
+      }
+    }
   }
   if (rank == 0) {
     const char* dump = envStr("MCCL_TOPO_DUMP_FILE");
@@ -210,8 +240,9 @@ mcclResult_t mcclCommInitRankConfig(mcclComm_t* out, int nRanks, mcclUniqueId id
   if (logLevel() >= LOG_INFO && rank == 0) {
     MCCL_INFO("comm %p: %d ranks, transport %s, nvls %d", (void*)c, nRanks, c->transport.c_str(), (int)c->system.nvls);
     for (int a = 0; a < mcclNumAlgos; ++a)
-      MCCL_INFO("  algo %-8s viable %d bw %.1f GB/s alpha %.1f us step %.2f us channels %d", mcclAlgoStr(a),
-                (int)c->graphs[a].viable, c->tuner.bw[a], c->tuner.alphaUs[a], c->tuner.stepUs[a], c->graphs[a].nChannels);
+      MCCL_INFO("  algo %-8s viable %d bw %.1f GB/s alpha %.1f us step %.2f us channels %d (%s)", mcclAlgoStr(a),
+                (int)c->graphs[a].viable, c->tuner.bw[a], c->tuner.alphaUs[a], c->tuner.stepUs[a], c->graphs[a].nChannels,
+                c->tuner.measured && (a == mcclAlgoOneShot || a == mcclAlgoTwoShot || a == mcclAlgoNvls) ? "measured" : "built in");
   }
   if (!cuda && c->blocking == 0 && nRanks > 1) MCCLCHECKGOTO(workerStart(c), rc, fail);
   *out = c;

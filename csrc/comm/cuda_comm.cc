@@ -13,7 +13,7 @@
 namespace mccl {
 
 DEFINE_MCCL_PARAM(DeviceTimeoutMs, "DEVICE_TIMEOUT_MS", 10000);
-DEFINE_MCCL_PARAM(StageMb, "STAGE_MB", 64);
+DEFINE_MCCL_PARAM(StageMb, "STAGE_MB", 256);
 DEFINE_MCCL_PARAM(OneShotSlotKb, "ONESHOT_SLOT_KB", 1024);
 DEFINE_MCCL_PARAM(P2pSlotKb, "P2P_SLOT_KB", 4096);
 DEFINE_MCCL_PARAM(NvlsEnable, "NVLS_ENABLE", 1);
@@ -85,6 +85,19 @@ mcclResult_t cudaCommInit(mcclComm* c) {
   cudaStream_t s;
   CUDACHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
   st->internalStream = s;
+  {
+    cudaStream_t cs;
+    int lo = 0, hi = 0;
+    CUDACHECK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    CUDACHECK(cudaStreamCreateWithPriority(&cs, cudaStreamNonBlocking, hi));
+    st->copyStream = cs;
+    cudaEvent_t e;
+    CUDACHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming)); st->evStart = e;
+    for (int i = 0; i < 2; ++i) {
+      CUDACHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming)); st->evCopied[i] = e;
+      CUDACHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming)); st->evFree[i] = e;
+    }
+  }
 
   CtrlLayout& L = st->layout;
   L.flagsOff = 0;
@@ -134,6 +147,12 @@ void cudaCommDestroy(mcclComm* c) {
   if (st->statusHost) cudaFreeHost((void*)st->statusHost);
   if (st->probeHost) cudaFreeHost(st->probeHost);
   if (st->internalStream) cudaStreamDestroy((cudaStream_t)st->internalStream);
+  if (st->copyStream) cudaStreamDestroy((cudaStream_t)st->copyStream);
+  if (st->evStart) cudaEventDestroy((cudaEvent_t)st->evStart);
+  for (int i = 0; i < 2; ++i) {
+    if (st->evCopied[i]) cudaEventDestroy((cudaEvent_t)st->evCopied[i]);
+    if (st->evFree[i]) cudaEventDestroy((cudaEvent_t)st->evFree[i]);
+  }
   if (st->udsFd >= 0) sockClose(st->udsFd);
   cudaGetLastError();
   delete st;
@@ -144,10 +163,15 @@ mcclResult_t cudaCommAsyncError(mcclComm* c, mcclResult_t* out) {
   CudaState* st = c->cu;
   const uint32_t code = st->statusHost->code;
   if (code != 0) {
-    const mcclResult_t e = (code == 3) ? mcclInvalidUsage : mcclRemoteError;
-    if (code != 3) c->asyncState.store((int)e);
-    if (logLevel() >= LOG_WARN)
-      MCCL_WARN("device wait gave up: code %u peer %u cta %u step %u", code, st->statusHost->peer, st->statusHost->cta, st->statusHost->step);
+    const mcclResult_t e = (code == 3 || code == 4) ? mcclInvalidUsage : mcclRemoteError;
+    if (code != 3 && code != 4) c->asyncState.store((int)e);
+    if (logLevel() >= LOG_WARN) {
+      if (code == 4)
+        MCCL_WARN("rank %u passed different buffers to a collective than this rank (allocation, offset, count or root): "
+                  "a buffer in symmetric memory must be the same part of the same allocation on every rank", st->statusHost->peer);
+      else
+        MCCL_WARN("device wait gave up: code %u peer %u cta %u step %u", code, st->statusHost->peer, st->statusHost->cta, st->statusHost->step);
+    }
     *out = e;
     return mcclSuccess;
   }

@@ -184,6 +184,63 @@ size_t stageChunk(const Call& k, size_t rows) {
   return per;
 }
 
+// Staged all-reduce of an ordinary buffer, two halves of the stage in flight: while the collective kernel works on
+// one half (on the caller's stream), the communicator's copy stream brings the next chunk into the other half and,
+// where the result lands in the stage (`copyBack`), takes the previous chunk's result out to `recv`.  Order on the
+// copy stream: in(0), in(1), out(0), in(2), out(1), ... so a copy-in never waits for the collective before it.
+// `run(half offset in the stage, offset in the message, length)` launches the collective for one chunk on the
+// caller's stream.  Messages that fit one half take the plain path (copy, collective, copy, one stream).
+template <typename Run>
+mcclResult_t stagedPipeline(const Call& k, const void* send, void* recv, bool copyBack, size_t bytes, size_t align, Run&& run) {
+  CudaState* st = k.st;
+  size_t half = k.stageBytes() / 2 / 256 * 256;
+  if (align > 1) half = half / align * align;
+  if (half == 0) return mcclInternalError;
+  const char* src = static_cast<const char*>(send);
+  char* dst = static_cast<char*>(recv);
+  if (bytes <= half || st->copyStream == nullptr) {
+    const size_t whole = align > 1 ? k.stageBytes() / 256 * 256 / align * align : k.stageBytes() / 256 * 256;
+    for (size_t off = 0; off < bytes; off += whole) {
+      const size_t len = std::min(whole, bytes - off);
+      MCCLCHECK(launchCopy(k.c, src + off, k.stageLocal(), 1, len, len, len, k.s));
+      MCCLCHECK(run((size_t)0, off, len));
+      if (copyBack) MCCLCHECK(launchCopy(k.c, k.stageLocal(), dst + off, 1, len, len, len, k.s));
+    }
+    return mcclSuccess;
+  }
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(st->copyStream);
+  cudaEvent_t evStart = reinterpret_cast<cudaEvent_t>(st->evStart);
+  auto copied = [&](int c) { return reinterpret_cast<cudaEvent_t>(st->evCopied[c & 1]); };
+  auto freed = [&](int c) { return reinterpret_cast<cudaEvent_t>(st->evFree[c & 1]); };
+  const int chunks = (int)((bytes + half - 1) / half);
+  auto copyIn = [&](int c) -> mcclResult_t {
+    const size_t off = (size_t)c * half, len = std::min(half, bytes - off);
+    if (c >= 2 && !copyBack) CUDACHECK(cudaStreamWaitEvent(cs, freed(c), 0));    // the collective that read this half is done
+    MCCLCHECK(launchCopy(k.c, src + off, k.stageLocal() + (size_t)(c & 1) * half, 1, len, len, len, cs));
+    CUDACHECK(cudaEventRecord(copied(c), cs));
+    return mcclSuccess;
+  };
+  CUDACHECK(cudaEventRecord(evStart, k.s));               // whatever produced `send` on the caller's stream comes first
+  CUDACHECK(cudaStreamWaitEvent(cs, evStart, 0));
+  MCCLCHECK(copyIn(0));
+  for (int c = 0; c < chunks; ++c) {
+    const size_t off = (size_t)c * half, len = std::min(half, bytes - off);
+    CUDACHECK(cudaStreamWaitEvent(k.s, copied(c), 0));
+    if (c + 1 < chunks) MCCLCHECK(copyIn(c + 1));
+    MCCLCHECK(run((size_t)(c & 1) * half, off, len));
+    CUDACHECK(cudaEventRecord(freed(c), k.s));
+    if (copyBack) {
+      CUDACHECK(cudaStreamWaitEvent(cs, freed(c), 0));
+      MCCLCHECK(launchCopy(k.c, k.stageLocal() + (size_t)(c & 1) * half, dst + off, 1, len, len, len, cs));
+    }
+  }
+  if (copyBack) {                                         // the caller's stream continues once the last result is out
+    CUDACHECK(cudaEventRecord(evStart, cs));
+    CUDACHECK(cudaStreamWaitEvent(k.s, evStart, 0));
+  }
+  return mcclSuccess;
+}
+
 mcclResult_t arTwoShot(const Call& k, const void* send, void* recv, size_t bytes) {
   const View sv = viewOf(k.st, send, bytes), rv = viewOf(k.st, recv, bytes);
   char* in[MCCL_MAX_RANKS];
@@ -192,15 +249,12 @@ mcclResult_t arTwoShot(const Call& k, const void* send, void* recv, size_t bytes
     for (int p = 0; p < k.n; ++p) { in[p] = sv.peer(p); red[p] = rv.peer(p); }
     return twoShot(k, in, red, static_cast<char*>(recv), bytes, true, mcclAlgoTwoShot);
   }
-  const size_t chunk = stageChunk(k, 1);
-  if (chunk == 0) return mcclInternalError;
-  for (int p = 0; p < k.n; ++p) in[p] = red[p] = k.stagePeer(p);
-  for (size_t off = 0; off < bytes; off += chunk) {
-    const size_t len = std::min(chunk, bytes - off);
-    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
-    MCCLCHECK(twoShot(k, in, red, static_cast<char*>(recv) + off, len, true, mcclAlgoTwoShot));
-  }
-  return mcclSuccess;
+  // Phase A writes the folded shard to the stage (for the peers) and to `recv`; phase B pulls the other shards from
+  // the peers' stages straight into `recv`: no copy back.
+  return stagedPipeline(k, send, recv, false, bytes, k.es, [&](size_t stageOff, size_t off, size_t len) -> mcclResult_t {
+    for (int p = 0; p < k.n; ++p) in[p] = red[p] = k.stagePeer(p) + stageOff;
+    return twoShot(k, in, red, static_cast<char*>(recv) + off, len, true, mcclAlgoTwoShot);
+  });
 }
 
 mcclResult_t arOneShot(const Call& k, const void* send, void* recv, size_t bytes) {
@@ -303,14 +357,15 @@ mcclResult_t arNvls(const Call& k, const void* send, void* recv, size_t bytes) {
   const View sv = viewOf(k.st, send, bytes), rv = viewOf(k.st, recv, bytes);
   if (sv.sym() && rv.sym() && sv.mc() && rv.mc() && al16(send) && al16(recv))
     return arNvlsOn(k, sv.mc(), rv.mc(), bytes);
-  const size_t chunk = stageChunk(k, 1);
-  for (size_t off = 0; off < bytes; off += chunk) {
-    const size_t len = std::min(chunk, bytes - off);
-    MCCLCHECK(launchCopy(k.c, static_cast<const char*>(send) + off, k.stageLocal(), 1, len, len, len, k.s));
-    MCCLCHECK(arNvlsOn(k, k.stageMc(), k.stageMc(), len));
-    MCCLCHECK(launchCopy(k.c, k.stageLocal(), static_cast<char*>(recv) + off, 1, len, len, len, k.s));
-  }
-  return mcclSuccess;
+  // Chunks are multiples of 16 x n bytes so that every chunk but the last splits into whole vectors per rank.
+  return stagedPipeline(k, send, recv, true, bytes, (size_t)16 * k.n, [&](size_t stageOff, size_t off, size_t len) -> mcclResult_t {
+    if (len % 16 || len / 16 < (size_t)k.n) {              // a ragged tail: the peer-load kernel takes any length
+      char* in[MCCL_MAX_RANKS];
+      for (int p = 0; p < k.n; ++p) in[p] = k.stagePeer(p) + stageOff;
+      return twoShot(k, in, in, nullptr, len, true, mcclAlgoTwoShot);      // the result stays in the stage, like the NVLS chunks'
+    }
+    return arNvlsOn(k, k.stageMc() + stageOff, k.stageMc() + stageOff, len);
+  });
 }
 
 mcclResult_t ringTreeOn(const Call& k, char* const buf[], size_t bytes, int algo, int phases = 0, int shift = 0) {
@@ -932,7 +987,39 @@ mcclResult_t reduceTreeFwd(const Call& k, const void* send, void* recv, size_t b
 static mcclResult_t latchedError(mcclComm* c) {
   const uint32_t code = c->cu->statusHost->code;
   if (code == 0) return mcclSuccess;
-  return code == 3 ? mcclInvalidUsage : mcclRemoteError;
+  return (code == 3 || code == 4) ? mcclInvalidUsage : mcclRemoteError;
+}
+
+// The kernels take a buffer that lies in symmetric memory on this rank to lie at the same offset of the same
+// allocation on every rank (the peers' addresses are derived from the local one).  With MCCL_CHECK_SYMMETRY=1
+// every collective is preceded by a small kernel in which the ranks compare what they passed.
+static mcclResult_t checkSymmetry(mcclComm* c, CudaState* st, int coll, const void* send, void* recv, size_t count, size_t es,
+                                  int root, cudaStream_t s) {
+  static const bool on = envInt("MCCL_CHECK_SYMMETRY", 0) != 0;
+  if (!on || c->nRanks < 2) return mcclSuccess;
+  const size_t n = (size_t)c->nRanks, r = (size_t)c->rank;
+  size_t sendBytes = count * es, recvBytes = count * es;
+  if (coll == mcclCollAllGather) recvBytes *= n;
+  if (coll == mcclCollReduceScatter || coll == mcclCollAllToAll) sendBytes *= n;
+  if (coll == mcclCollAllToAll) recvBytes *= n;
+  View sv = viewOf(st, send, sendBytes), rv = viewOf(st, recv, recvBytes);
+  uint64_t sig[4] = {0, 0, 0, 0};
+  // Rooted calls: only the root's send (broadcast) or receive (reduce) buffer is used, so it is not compared.
+  if (sv.sym() && coll != mcclCollBroadcast) {
+    uint64_t off = sv.off;
+    if (coll == mcclCollAllGather && rv.sym() && rv.seg == sv.seg && sv.off == rv.off + r * sendBytes) off -= r * sendBytes;   // in place
+    sig[0] = sv.seg->serial; sig[1] = off;
+  }
+  if (rv.sym() && coll != mcclCollReduce) {
+    uint64_t off = rv.off;
+    if (coll == mcclCollReduceScatter && sv.sym() && rv.seg == sv.seg && rv.off == sv.off + r * recvBytes) off -= r * recvBytes;   // in place
+    sig[2] = rv.seg->serial; sig[3] = off;
+  }
+  sig[0] |= (uint64_t)(coll + 1) << 56;
+  sig[2] |= (uint64_t)(root + 1) << 56;
+  sig[1] ^= (uint64_t)count << 40;
+  symCheckKernel<<<1, kThreads, 0, s>>>(st->peers, sig[0], sig[1], sig[2], sig[3]);
+  return launched(c, "symCheckKernel");
 }
 
 mcclResult_t cudaCollective(mcclComm* c, int coll, const void* send, void* recv, size_t count, mcclDataType_t dt,
@@ -953,7 +1040,8 @@ mcclResult_t cudaCollective(mcclComm* c, int coll, const void* send, void* recv,
     // Single rank: every collective is a local copy (avg over one rank is the identity).
     if (recv != nullptr && send != nullptr) rc = launchCopy(c, send, recv, 1, count * k.es, count * k.es, count * k.es, k.s);
   } else {
-    switch (coll) {
+    rc = checkSymmetry(c, st, coll, send, recv, count, k.es, root, k.s);
+    if (rc == mcclSuccess) switch (coll) {
       case mcclCollAllReduce:     rc = allReduce(k, send, recv, count, algo); break;
       case mcclCollAllGather:     rc = allGather(k, send, recv, count, algo); break;
       case mcclCollReduceScatter: rc = reduceScatter(k, send, recv, count, algo); break;
@@ -1175,16 +1263,72 @@ mcclResult_t cudaCalibrate(mcclComm* c) {
       if (l.measured > 0.f) { l.bw = l.measured; minBw = std::min(minBw, l.measured); }
     }
   }
-  if (minBw < 1e9f) {
-    // One peer at a time cannot saturate the port; pulls from all peers at once reach more, so the
-    // single-pair figure is a floor for the all-pairs algorithms, not a replacement for the table.
-    for (int a = 0; a < mcclNumAlgos; ++a) c->tuner.stepUs[a] = maxLat / 3.f;
-    c->tuner.alphaUs[mcclAlgoTwoShot] = c->tuner.alphaUs[mcclAlgoNvls] = maxLat;
-    c->tuner.alphaUs[mcclAlgoOneShot] = maxLat * 0.6f;
+  // Per algorithm a two-point fit of the model's alpha and bandwidth: the all-reduce on the stage at a small and a
+  // large size (fp32 sum, best of three timings of a few back-to-back calls), the slowest rank's figures for all.
+  // One peer at a time cannot saturate the port, so the per-pair numbers above describe links (and reveal a dead
+  // one), while these fits describe what each kernel makes of all links together.
+  {
+    cudaEvent_t f0, f1;
+    CUDACHECK(cudaEventCreate(&f0));
+    CUDACHECK(cudaEventCreate(&f1));
+    const size_t big = std::min<size_t>(st->layout.stageBytes / 2, 32u << 20) / (16 * (size_t)k.n) * (16 * (size_t)k.n);
+    const size_t slot = (size_t)st->layout.oneShotSlotBytes / 16 * 16;
+    struct Point { int algo; size_t small, large; };
+    const Point points[3] = {{mcclAlgoOneShot, 4096, std::min<size_t>(slot, 1u << 20)}, {mcclAlgoTwoShot, 65536, big}, {mcclAlgoNvls, 65536, big}};
+    float us[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+    char* in[MCCL_MAX_RANKS];
+    for (int p = 0; p < k.n; ++p) in[p] = k.stagePeer(p);
+    for (int a = 0; a < 3; ++a) {
+      const int algo = points[a].algo;
+      if (!c->tuner.viable[algo] || (algo == mcclAlgoNvls && !st->nvls)) continue;
+      for (int pt = 0; pt < 2; ++pt) {
+        const size_t bytes = pt == 0 ? points[a].small : points[a].large;
+        const int iters = pt == 0 ? 8 : 3;
+        float best = 1e30f;
+        for (int rep = -1; rep < 3; ++rep) {          // rep -1 warms up
+          CUDACHECK(cudaEventRecord(f0, s));
+          for (int it = 0; it < iters; ++it) {
+            if (algo == mcclAlgoOneShot) MCCLCHECK(arOneShot(k, k.stageLocal(), k.stageLocal() + st->layout.stageBytes / 2, bytes));
+            else if (algo == mcclAlgoTwoShot) MCCLCHECK(twoShot(k, in, in, nullptr, bytes, true, mcclAlgoTwoShot));
+            else MCCLCHECK(arNvlsOn(k, k.stageMc(), k.stageMc(), bytes));
+          }
+          CUDACHECK(cudaEventRecord(f1, s));
+          CUDACHECK(cudaStreamSynchronize(s));
+          float ms = 0.f;
+          CUDACHECK(cudaEventElapsedTime(&ms, f0, f1));
+          if (rep >= 0) best = std::min(best, ms * 1000.f / iters);
+          MCCLCHECK(latchedError(c));
+        }
+        us[a][pt] = best;
+      }
+    }
+    cudaEventDestroy(f0);
+    cudaEventDestroy(f1);
+    std::vector<float> allUs((size_t)c->nRanks * 6);
+    MCCLCHECK(bootstrapAllGather(c->bs, &us[0][0], allUs.data(), sizeof(us)));
+    for (int a = 0; a < 3; ++a) {
+      float t[2] = {0.f, 0.f};
+      for (int r = 0; r < c->nRanks; ++r) for (int pt = 0; pt < 2; ++pt) t[pt] = std::max(t[pt], allUs[(size_t)r * 6 + a * 2 + pt]);
+      const int algo = points[a].algo;
+      if (t[0] <= 0.f || t[1] <= t[0]) continue;
+      const double f = algoTraffic(algo, mcclCollAllReduce, c->nRanks);
+      const float bwFit = (float)((double)(points[a].large - points[a].small) * f / (1000.0 * (t[1] - t[0])));
+      const float alphaFit = std::max(1.f, t[0] - (float)((double)points[a].small * f / (1000.0 * bwFit)));
+      // A fit far from the built-in constants means a disturbed measurement (a busy GPU): keep the constants then.
+      if (bwFit < 0.25f * c->tuner.bw[algo] || bwFit > 4.f * c->tuner.bw[algo]) {
+        MCCL_WARN("calibration of %s looks disturbed (%.1f GB/s against %.1f assumed): keeping the built-in constants", mcclAlgoStr(algo), bwFit, c->tuner.bw[algo]);
+        continue;
+      }
+      MCCL_INFO("calibration: %-8s alpha %.1f us (was %.1f), bandwidth %.1f GB/s (was %.1f)", mcclAlgoStr(algo), alphaFit,
+                c->tuner.alphaUs[algo], bwFit, c->tuner.bw[algo]);
+      c->tuner.alphaUs[algo] = alphaFit;
+      c->tuner.stepUs[algo] = 0.f;
+      c->tuner.bw[algo] = bwFit;
+    }
+    c->tuner.measured = true;
   }
+  if (minBw < 1e9f && minBw < 1.f) MCCL_WARN("calibration: a peer link moved less than 1 GB/s");
   MCCL_INFO("calibration: empty collective %.1f us, slowest pair %.1f GB/s", maxLat, minBw);
-  const char* cache = envStr("MCCL_TUNER_CACHE");
-  if (cache && c->rank == 0) tunerSaveCache(c->tuner, cache);
   return mcclSuccess;
 }
 

@@ -24,7 +24,8 @@ namespace mccl {
 // Device status word (pinned host memory, one per communicator).  A wait that runs out of time records
 // where it gave up and the kernel returns normally; nothing traps.
 struct DevStatus {
-  volatile uint32_t code;     // 0 = fine, 1 = timeout in a barrier, 2 = timeout in a step wait, 3 = aborted by host
+  volatile uint32_t code;     // 0 = fine, 1 = timeout in a barrier, 2 = timeout in a step wait, 3 = aborted by host,
+                              // 4 = the ranks disagree on the buffers of a call (MCCL_CHECK_SYMMETRY)
   volatile uint32_t peer;     // rank that did not answer
   volatile uint32_t cta;
   volatile uint32_t step;
@@ -53,6 +54,9 @@ struct CtrlFlags {
   // note[cta]: a word the root of a rooted collective publishes before the entry barrier of a call and its
   // peers read after it (which form of the algorithm the root can take part in).
   uint64_t note[MCCL_MAX_CTAS];
+  // symSig[src]: what rank `src` passed to the call being checked (MCCL_CHECK_SYMMETRY): which symmetric
+  // allocation and offset its send and receive buffers are, the collective and the count.
+  uint64_t symSig[MCCL_MAX_RANKS][4];
   uint64_t canary;            // 0x6d63636c63616e61, checked by tests after every run
 };
 

@@ -619,6 +619,34 @@ static __global__ void __launch_bounds__(kThreads, 1) barrierKernel(DevPeers P) 
   if (threadIdx.x == 0) mine->epoch[blockIdx.x] = epoch;
 }
 
+// Debug aid (MCCL_CHECK_SYMMETRY=1): every rank tells every peer what it passed to the coming call; a rank that
+// sees a different answer records code 4 with the peer's rank, which the host reports as mcclInvalidUsage.
+static __global__ void __launch_bounds__(kThreads, 1) symCheckKernel(DevPeers P, uint64_t s0, uint64_t s1, uint64_t s2, uint64_t s3) {
+  __shared__ int sFail;
+  const int t = threadIdx.x;
+  if (t == 0) sFail = 0;
+  CtrlFlags* mine = flagsOf(P, P.rank);
+  uint64_t epoch = mine->epoch[blockIdx.x];
+  if (t < P.n && t != P.rank) {
+    uint64_t* dst = flagsOf(P, t)->symSig[P.rank];
+    dst[0] = s0; dst[1] = s1; dst[2] = s2; dst[3] = s3;
+  }
+  bool ok = ctaBarrier(P, epoch, &sFail);
+  if (ok && t < P.n && t != P.rank) {
+    const uint64_t* got = mine->symSig[t];
+    if (ldAcquireSys(&got[0]) != s0 || ldAcquireSys(&got[1]) != s1 || ldAcquireSys(&got[2]) != s2 || ldAcquireSys(&got[3]) != s3) {
+      if (atomicCAS((unsigned int*)&P.status->code, 0u, 4u) == 0u) {
+        P.status->peer = (uint32_t)t;
+        P.status->cta = 0;
+        P.status->step = 0;
+        __threadfence_system();
+      }
+    }
+  }
+  if (ok) ctaBarrier(P, epoch, &sFail);          // nobody overwrites the words before everyone has compared
+  if (t == 0) mine->epoch[blockIdx.x] = epoch;
+}
+
 // rows x rowBytes, each row at its own pitch.
 static __global__ void __launch_bounds__(kThreads) copyKernel(const char* src, char* dst, uint64_t rows, uint64_t rowBytes,
                                                        uint64_t srcPitch, uint64_t dstPitch) {
@@ -626,7 +654,7 @@ static __global__ void __launch_bounds__(kThreads) copyKernel(const char* src, c
   const bool vec = aligned16(src) && aligned16(dst) && (rowBytes & 15) == 0 && (srcPitch & 15) == 0 && (dstPitch & 15) == 0;
   if (vec) {
     const uint64_t perRow = rowBytes / 16, total = perRow * rows;
-    constexpr int U = 4;                     // four loads in flight per thread
+    constexpr int U = 8;                     // eight loads in flight per thread
     uint64_t i = tid;
     for (; i + (uint64_t)(U - 1) * nth < total; i += (uint64_t)U * nth) {
       uint4 v[U];

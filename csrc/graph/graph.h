@@ -138,7 +138,10 @@ struct TunerModel {
   size_t oneShotMaxBytes;   // one-shot scratch slot size (cuda) / MCCL_DIRECT_MAX_BYTES (tcp)
   int    oneShotMaxRanks;
   bool   cuda;              // constants describe the cuda transport's kernels
+  bool   measured = false;  // alpha / bandwidth of the switch-era algorithms come from a calibration (now or cached)
 };
+// Where a calibration is kept between runs: MCCL_TUNER_CACHE, else ~/.cache/mccl_b200/tuner-<ranks>x<gpu>.txt.
+std::string tunerCachePath(int nRanks, const char* gpuName);
 
 mcclResult_t tunerInit(const TopoSystem& sys, const TopoGraph graphs[mcclNumAlgos], bool cudaTransport, TunerModel* out);
 // Overrides from MCCL_TUNER_CACHE (a file of "algo alpha_us step_us bw_gbs" lines) if set.

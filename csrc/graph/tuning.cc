@@ -13,6 +13,10 @@
 #include <cstring>
 #include <string>
 
+#include <sys/stat.h>
+#include <unistd.h>
+#include <string>
+#include <ctype.h>
 #include "graph.h"
 
 namespace mccl {
@@ -110,9 +114,20 @@ mcclResult_t tunerInit(const TopoSystem& sys, const TopoGraph graphs[mcclNumAlgo
   return mcclSuccess;
 }
 
+std::string tunerCachePath(int nRanks, const char* gpuName) {
+  const char* forced = envStr("MCCL_TUNER_CACHE");
+  if (forced && *forced) return forced;
+  const char* home = envStr("HOME");
+  std::string dir = std::string(home && *home ? home : "/tmp") + "/.cache/mccl_b200";
+  std::string gpu;
+  for (const char* p = gpuName ? gpuName : "gpu"; *p; ++p) gpu += (isalnum((unsigned char)*p) ? *p : '_');
+  return dir + "/tuner-" + std::to_string(nRanks) + "x" + gpu + ".txt";
+}
+
 mcclResult_t tunerLoadCache(TunerModel* m, const char* path) {
   FILE* f = fopen(path, "r");
   if (f == nullptr) return mcclSuccess;  // nothing cached yet
+  m->measured = true;
   char name[32];
   float alpha, step, bw;
   while (fscanf(f, "%31s %f %f %f", name, &alpha, &step, &bw) == 4) {
@@ -124,10 +139,20 @@ mcclResult_t tunerLoadCache(TunerModel* m, const char* path) {
 }
 
 mcclResult_t tunerSaveCache(const TunerModel& m, const char* path) {
-  FILE* f = fopen(path, "w");
+  std::string dir(path);
+  const size_t slash = dir.rfind('/');
+  if (slash != std::string::npos && slash > 0) {       // mkdir -p of the parent
+    dir.resize(slash);
+    for (size_t i = 1; i <= dir.size(); ++i)
+      if (i == dir.size() || dir[i] == '/') { std::string part = dir.substr(0, i); mkdir(part.c_str(), 0755); }
+  }
+  // Written beside the target and renamed into place, so a reader never sees half a file.
+  const std::string tmp = std::string(path) + ".tmp" + std::to_string((long)getpid());
+  FILE* f = fopen(tmp.c_str(), "w");
   if (f == nullptr) MCCLFAIL(mcclSystemError);
   for (int a = 0; a < mcclNumAlgos; ++a) fprintf(f, "%s %g %g %g\n", mcclAlgoStr(a), m.alphaUs[a], m.stepUs[a], m.bw[a]);
   fclose(f);
+  if (rename(tmp.c_str(), path) != 0) { remove(tmp.c_str()); MCCLFAIL(mcclSystemError); }
   return mcclSuccess;
 }
 

@@ -24,9 +24,12 @@ struct AdamArgs {
   int zeroGrad;              // clear the gradient after use, ready for the next accumulation
   const float* normSq;       // optional device scalar: squared global gradient norm (for clipping)
   float maxNorm;             // clip threshold; used only when normSq is set
+  const float* hyper;        // optional device array {lr, 1 - beta1^t, sqrt(1 - beta2^t)}: read at run time, so a
+                             // launch recorded in a CUDA graph follows the schedule when it is replayed
 };
 
 __global__ void __launch_bounds__(256) adamwKernel(AdamArgs a) {
+  if (a.hyper != nullptr) { a.lr = a.hyper[0]; a.biasCorr1 = a.hyper[1]; a.biasCorr2Sqrt = a.hyper[2]; }
   if (a.normSq != nullptr) {   // global-norm clipping: scale = min(1, maxNorm / ||g||), read on the device (no host sync)
     const float norm = sqrtf(*a.normSq) * a.gradScale;
     if (norm > a.maxNorm) a.gradScale *= a.maxNorm / (norm + 1e-6f);
@@ -75,10 +78,10 @@ __global__ void __launch_bounds__(256) adamwKernel(AdamArgs a) {
 
 }  // namespace
 
-extern "C" mcclResult_t mcclFusedAdamW(void* param, float* master, float* expAvg, float* expAvgSq, const void* grad,
-                                       uint64_t n, float lr, float beta1, float beta2, float eps, float weightDecay,
-                                       float gradScale, int step, int zeroGrad, const float* normSq, float maxNorm,
-                                       mcclStream_t stream) {
+static mcclResult_t adamwLaunch(void* param, float* master, float* expAvg, float* expAvgSq, const void* grad,
+                                uint64_t n, float lr, float beta1, float beta2, float eps, float weightDecay,
+                                float gradScale, int step, int zeroGrad, const float* normSq, float maxNorm,
+                                const float* hyper, mcclStream_t stream) {
   if (param == nullptr || master == nullptr || expAvg == nullptr || expAvgSq == nullptr || grad == nullptr || step < 1)
     return mcclInvalidArgument;
   if (n == 0) return mcclSuccess;
@@ -96,10 +99,30 @@ extern "C" mcclResult_t mcclFusedAdamW(void* param, float* master, float* expAvg
   a.zeroGrad = zeroGrad;
   a.normSq = normSq;
   a.maxNorm = maxNorm;
+  a.hyper = hyper;
   const uint64_t vec = (n + 7) / 8;
   int blocks = (int)((vec + 255) / 256);
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
   adamwKernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? mcclSuccess : mcclSystemError;
+}
+
+extern "C" mcclResult_t mcclFusedAdamW(void* param, float* master, float* expAvg, float* expAvgSq, const void* grad,
+                                       uint64_t n, float lr, float beta1, float beta2, float eps, float weightDecay,
+                                       float gradScale, int step, int zeroGrad, const float* normSq, float maxNorm,
+                                       mcclStream_t stream) {
+  return adamwLaunch(param, master, expAvg, expAvgSq, grad, n, lr, beta1, beta2, eps, weightDecay, gradScale, step, zeroGrad,
+                     normSq, maxNorm, nullptr, stream);
+}
+
+// The same step with the learning rate and the two bias corrections read from device memory when the kernel
+// runs: hyper = {lr, 1 - beta1^t, sqrt(1 - beta2^t)}.  For launches recorded in a CUDA graph.
+extern "C" mcclResult_t mcclFusedAdamWDeviceHyper(void* param, float* master, float* expAvg, float* expAvgSq, const void* grad,
+                                                  uint64_t n, const float* hyper, float beta1, float beta2, float eps,
+                                                  float weightDecay, float gradScale, int zeroGrad, const float* normSq,
+                                                  float maxNorm, mcclStream_t stream) {
+  if (hyper == nullptr) return mcclInvalidArgument;
+  return adamwLaunch(param, master, expAvg, expAvgSq, grad, n, 0.f, beta1, beta2, eps, weightDecay, gradScale, 1, zeroGrad,
+                     normSq, maxNorm, hyper, stream);
 }

@@ -295,6 +295,7 @@ mcclResult_t segmentCreate(mcclComm* c, size_t bytes, bool internal, Segment** o
   s->userBytes = bytes;
   s->internal = internal;
   const uint32_t serial = ++st->segSerial;
+  s->serial = serial;
   bool ok = true;
   if (st->vmm) {
     s->mode = SEG_VMM;
@@ -356,6 +357,7 @@ mcclResult_t segmentRegister(mcclComm* c, void* ptr, size_t bytes, Segment** out
   Segment* s = new Segment();
   s->mode = SEG_IPC;
   s->registered = true;
+  s->serial = ++st->segSerial;
   s->bytes = s->userBytes = bytes;
   s->local = static_cast<char*>(ptr);
   CUdeviceptr base = 0;

@@ -32,6 +32,7 @@ struct Segment {
   char* mc = nullptr;        // multicast alias (null without NVLS)
   bool registered = false;   // wraps caller-owned memory (mcclCommRegister)
   bool internal = false;     // control block / staging, not returned by lookups of user pointers
+  uint32_t serial = 0;       // creation number: equal on every rank, because segments are created collectively
   // VMM bookkeeping
   unsigned long long handle = 0;
   unsigned long long peerHandle[MCCL_MAX_RANKS] = {0};
@@ -53,6 +54,12 @@ struct CudaState {
   DevStatus* statusDev = nullptr;
   DevPeers peers;            // template copied into every kernel's arguments
   void* internalStream = nullptr;   // for library-internal work (finalize barrier, calibration)
+  // Staging of ordinary (non-symmetric) buffers: the copy into one half of the stage runs on its own stream
+  // while the collective works on the other half.
+  void* copyStream = nullptr;
+  void* evStart = nullptr;
+  void* evCopied[2] = {nullptr, nullptr};
+  void* evFree[2] = {nullptr, nullptr};
   void* probeHost = nullptr;        // pinned int for RecvAny
   uint64_t p2pSent[MCCL_MAX_RANKS] = {0};    // host mirrors of the FIFO counters are not needed: device keeps them
 };

@@ -12,6 +12,21 @@
  * enqueued on `stream`; with the "tcp" transport they are host pointers and `stream` is ignored.
  * Device buffers obtained from mcclMemAlloc (symmetric, peer-mapped, multicast-bound) are used in
  * place; any other device pointer is staged through the communicator's symmetric scratch.
+ *
+ * Symmetric buffers, the contract: a rank decides from its own pointer whether a buffer is symmetric, and
+ * derives the peers' addresses from it.  So an argument that lies in symmetric memory on one rank must be the
+ * same part (same allocation, same offset) of that allocation on EVERY rank of the call, and an argument that
+ * is an ordinary pointer on one rank must be ordinary on all.  The in-place forms count as the same part:
+ * all-gather with sendbuff = recvbuff + rank * sendcount, reduce-scatter with recvbuff = sendbuff + rank *
+ * recvcount.  A call that breaks the rule returns wrong data or runs into the device time limit; nothing
+ * detects it by default.  With MCCL_CHECK_SYMMETRY=1 every collective is preceded by a small kernel in which
+ * the ranks compare (allocation, offset, count, root); a mismatch is reported as mcclInvalidUsage by the next
+ * call and by mcclCommGetAsyncError.
+ *
+ * Groups: the calls between mcclGroupStart and mcclGroupEnd are independent of one another (none may consume
+ * another's result).  Per communicator GroupEnd issues first the all-reduce calls on symmetric buffers, as one
+ * kernel launch, then the other collectives in program order, then all Send/Recv as one launch.  On the cuda
+ * transport all calls of a group on one communicator must name the same stream (mcclInvalidUsage otherwise).
  */
 #ifndef MCCL_H_
 #define MCCL_H_

@@ -46,6 +46,11 @@ mcclResult_t mcclMoeGather(mcclComm_t comm, const void* exchange, const int32_t*
 mcclResult_t mcclFusedAdamW(void* param, float* master, float* expAvg, float* expAvgSq, const void* grad, uint64_t n, float lr,
                             float beta1, float beta2, float eps, float weightDecay, float gradScale, int step, int zeroGrad,
                             const float* normSq, float maxNorm, mcclStream_t stream);
+/* The same step with {lr, 1 - beta1^t, sqrt(1 - beta2^t)} read from the device array `hyper` when the kernel runs, so a
+   launch recorded in a CUDA graph follows the schedule on every replay. */
+mcclResult_t mcclFusedAdamWDeviceHyper(void* param, float* master, float* expAvg, float* expAvgSq, const void* grad, uint64_t n,
+                                       const float* hyper, float beta1, float beta2, float eps, float weightDecay, float gradScale,
+                                       int zeroGrad, const float* normSq, float maxNorm, mcclStream_t stream);
 uint64_t     mcclSumSquaresScratchFloats(uint64_t n);
 /* out = [out +] sum(x^2) over n bf16 values; scratch: mcclSumSquaresScratchFloats(n) floats, first word zero. */
 mcclResult_t mcclSumSquaresBf16(const void* x, uint64_t n, float* scratch, uint64_t scratchFloats, float* out, int accumulate,

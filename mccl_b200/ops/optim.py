@@ -28,8 +28,10 @@ def _fn():
 def fused_adamw_(param: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
                  grad: torch.Tensor, *, lr: float, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
                  grad_scale: float = 1.0, step: int = 1, zero_grad: bool = True, norm_sq: torch.Tensor | None = None,
-                 max_norm: float = 0.0, stream=None) -> None:
-    """In-place AdamW step on flat tensors: bf16 `param`/`grad`, fp32 `master`/`exp_avg`/`exp_avg_sq`."""
+                 max_norm: float = 0.0, stream=None, hyper: torch.Tensor | None = None) -> None:
+    """In-place AdamW step on flat tensors: bf16 `param`/`grad`, fp32 `master`/`exp_avg`/`exp_avg_sq`.  With `hyper` (three
+    fp32 values on the device: lr, 1 - beta1^t, sqrt(1 - beta2^t)) the kernel reads the schedule when it runs instead of
+    taking `lr` and `step` from this call, which is what a launch recorded in a CUDA graph needs."""
     if not param.is_cuda:
         raise RuntimeError("fused_adamw_ needs CUDA tensors (the kernel is sm_100a code)")
     assert param.dtype == torch.bfloat16 and grad.dtype == torch.bfloat16
@@ -37,6 +39,19 @@ def fused_adamw_(param: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tenso
     n = param.numel()
     assert master.numel() == n and grad.numel() == n and exp_avg.numel() == n and exp_avg_sq.numel() == n
     s = stream.cuda_stream if stream is not None else torch.cuda.current_stream(param.device).cuda_stream
+    if hyper is not None:
+        assert hyper.is_cuda and hyper.dtype == torch.float32 and hyper.numel() >= 3
+        lib = L.load()
+        g = lib.mcclFusedAdamWDeviceHyper
+        if not getattr(g, "_declared", False):
+            g.restype = C.c_int
+            g.argtypes = [C.c_void_p] * 5 + [C.c_uint64, C.c_void_p] + [C.c_float] * 5 + [C.c_int, C.c_void_p, C.c_float, C.c_void_p]
+            g._declared = True
+        L.check(g(param.data_ptr(), master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), grad.data_ptr(), n,
+                  hyper.data_ptr(), betas[0], betas[1], eps, weight_decay, grad_scale, 1 if zero_grad else 0,
+                  norm_sq.data_ptr() if norm_sq is not None else None, max_norm, C.c_void_p(s)), "mcclFusedAdamWDeviceHyper")
+        _counter["launches"] += 1
+        return
     L.check(_fn()(param.data_ptr(), master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), grad.data_ptr(), n,
                   lr, betas[0], betas[1], eps, weight_decay, grad_scale, step, 1 if zero_grad else 0,
                   norm_sq.data_ptr() if norm_sq is not None else None, max_norm, C.c_void_p(s)),

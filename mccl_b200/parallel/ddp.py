@@ -229,7 +229,7 @@ class DistributedDataParallel(nn.Module):
             if b.done_event is not None and cur is not None:
                 cur.wait_event(b.done_event)
 
-    def step(self, lr: float = 3e-4, max_grad_norm: Optional[float] = None) -> None:
+    def step(self, lr: float = 3e-4, max_grad_norm: Optional[float] = None, _hyper: Optional[torch.Tensor] = None) -> None:
         """Wait for the gradient buckets, then one fused AdamW kernel per bucket (it also clears the gradients).
         With `max_grad_norm` the global gradient norm is accumulated bucket by bucket on the device and the
         optimizer kernels clip by it without a host round trip."""
@@ -266,7 +266,7 @@ class DistributedDataParallel(nn.Module):
             if cuda:
                 fused_adamw_(p_slice, b.master, b.exp_avg, b.exp_avg_sq, g_slice, lr=lr, betas=self.betas, eps=self.eps,
                              weight_decay=b.weight_decay, step=self.step_count, zero_grad=not self.sharded, norm_sq=norm_sq,
-                             max_norm=max_grad_norm or 0.0)
+                             max_norm=max_grad_norm or 0.0, hyper=_hyper)
                 if self.sharded:
                     b.grad.zero_()                     # the other ranks' slices hold this rank's raw gradients
             else:  # CPU stand-in for tests of the bucket logic
@@ -294,6 +294,23 @@ class DistributedDataParallel(nn.Module):
                     cur.wait_event(b.gather_event)
                     b.gather_event = None
         self._reset()
+
+    def graphed_step(self, example_args, lr: float = 3e-4, max_grad_norm: Optional[float] = None, warmup: int = 1):
+        """Record one whole training step (forward, backward with the bucket all-reduces on their side stream, gradient
+        norm, optimizer) in a CUDA graph and return a callable that replays it:
+
+            step = ddp.graphed_step((idx, targets), lr=3e-4, max_grad_norm=1.0)
+            loss = step(idx, targets)            # a device tensor, overwritten by the next call
+
+        `example_args` are the positional tensors of the module's forward (it must return the loss); later calls pass
+        tensors of the same shapes and dtypes, which are copied into the graph's input buffers.  A replay costs the
+        host one launch, so a step that is bound by the host issuing a few thousand small kernels becomes bound by the
+        GPU.  The learning rate and Adam's bias corrections live in device memory and are refreshed before every replay
+        (`step(..., lr=...)` changes the rate).  `warmup` eager steps on the example batch run first (they are ordinary
+        training steps).  Every rank must record and replay in step with the others.  No autograd graph of an earlier
+        step may still be alive when this is called (drop the last loss tensor): its gradient accumulators would run on
+        the stream of that earlier step, which a recording cannot wait for."""
+        return _GraphedStep(self, example_args, lr, max_grad_norm, warmup)
 
     # ---- checkpointing
     def optimizer_state_dict(self) -> dict:
@@ -324,3 +341,61 @@ class DistributedDataParallel(nn.Module):
     def bucket_sizes_mb(self) -> List[float]:
         """Size of every gradient bucket in MB, in launch order."""
         return [b.numel * b.grad.element_size() / (1 << 20) for b in self.buckets]
+
+
+class _GraphedStep:
+    """See DistributedDataParallel.graphed_step."""
+
+    def __init__(self, ddp: DistributedDataParallel, example_args, lr: float, max_grad_norm: Optional[float], warmup: int):
+        if ddp.device.type != "cuda":
+            raise RuntimeError("graphed_step needs a CUDA device")
+        self.ddp, self.lr, self.max_grad_norm = ddp, lr, max_grad_norm
+        if ddp.step_count == 0 and warmup < 1:
+            warmup = 1                            # the first step allocates work buffers, which a recording cannot do
+        self.inputs = [a.to(ddp.device).contiguous().clone() for a in example_args]
+        self.hyper = torch.zeros(4, device=ddp.device, dtype=torch.float32)
+        self.hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+        cur = torch.cuda.current_stream(ddp.device)
+        side = torch.cuda.Stream(device=ddp.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(max(0, warmup)):
+                self._refresh(lr)
+                loss = ddp(*self.inputs)
+                loss.backward()
+                ddp.step(lr=lr, max_grad_norm=max_grad_norm, _hyper=self.hyper)
+        cur.wait_stream(side)
+        torch.cuda.synchronize(ddp.device)
+        from ..ops import loss as loss_ops
+        from ..ops import norm as norm_ops
+        from ..ops import optim
+        count = lambda: ((ddp.comm.launch_count if ddp.comm is not None else 0) + optim.launches() + loss_ops.launches() +
+                         norm_ops.launches())
+        before, steps_before = count(), ddp.step_count
+        self.graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.loss = ddp(*self.inputs)
+                self.loss.backward()
+                ddp.step(lr=lr, max_grad_norm=max_grad_norm, _hyper=self.hyper)
+        except RuntimeError as exc:
+            raise RuntimeError("recording the step in a CUDA graph failed; if an earlier step's loss (and with it its autograd "
+                               "graph) is still referenced, drop it before calling graphed_step") from exc
+        ddp.step_count = steps_before            # recording ran no step
+        self.launches_per_step = count() - before
+
+    def _refresh(self, lr: float) -> None:
+        d = self.ddp
+        t = d.step_count + 1                     # the step about to run
+        self.hyper_host[0] = lr
+        self.hyper_host[1] = 1.0 - d.betas[0] ** t
+        self.hyper_host[2] = (1.0 - d.betas[1] ** t) ** 0.5
+        self.hyper.copy_(self.hyper_host, non_blocking=True)
+
+    def __call__(self, *args, lr: Optional[float] = None) -> torch.Tensor:
+        for dst, src in zip(self.inputs, args):
+            dst.copy_(src, non_blocking=True)
+        self._refresh(self.lr if lr is None else lr)
+        self.graph.replay()
+        self.ddp.step_count += 1
+        return self.loss

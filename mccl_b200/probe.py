@@ -40,6 +40,10 @@ def _env_world():
 
 def _comm(transport=None):
     rank, world, ip, port = _env_world()
+    if transport == "cuda" or (transport is None and os.environ.get("MCCL_TRANSPORT", "") == "cuda"):
+        # one GPU per rank: the local rank of the launcher, else the rank itself
+        import torch
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)) % max(torch.cuda.device_count(), 1))
     return Communicator(world, unique_id_from_env(ip, port), rank, transport=transport)
 
 

@@ -192,6 +192,47 @@ def split_and_ddp():
     comm.finalize(); comm.destroy()
 
 
+def ddp_graphed():
+    """The whole step recorded in a CUDA graph (bucket all-reduces on their side stream included) follows the same
+    trajectory as the step issued kernel by kernel, and the replicas stay bit-identical."""
+    from mccl_b200.models.gpt2 import GPT2, GPT2Config
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    comm = make_comm()
+    cfg = GPT2Config.tiny()
+    g = torch.Generator().manual_seed(7 + RANK)
+    batches = torch.randint(0, cfg.vocab_size, (3, 4, cfg.seq_len + 1), generator=g).to(DEV)
+
+    def build():
+        torch.manual_seed(0)
+        return DistributedDataParallel(GPT2(cfg).to(device=DEV, dtype=torch.bfloat16), comm, bucket_mb=0.25)
+
+    eager = build()
+    ref = []
+    for i in range(7):
+        t = batches[i % 3]
+        loss = eager(t[:, :-1], t[:, 1:]); loss.backward(); eager.step(lr=3e-3, max_grad_norm=1.0)
+        ref.append(loss.item())
+    ddp = build()
+    t = batches[0]
+    step = ddp.graphed_step((t[:, :-1], t[:, 1:]), lr=3e-3, max_grad_norm=1.0, warmup=1)     # the warm-up is step 0
+    got = [ref[0]]
+    for i in range(1, 7):
+        t = batches[i % 3]
+        got.append(step(t[:, :-1], t[:, 1:]).item())
+    assert step.launches_per_step > 0 and ddp.step_count == 7
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (ref, got)
+    assert got[-1] < got[1], got
+    torch.cuda.synchronize()
+    assert canary_ok(comm)
+    flat = torch.cat([b.param.float() for b in ddp.buckets])
+    gathered = torch.empty(flat.numel() * WORLD, device=DEV)
+    comm.all_gather(flat, gathered); torch.cuda.synchronize()
+    for r in range(WORLD):
+        assert torch.equal(gathered[r * flat.numel():(r + 1) * flat.numel()], flat), f"replica {r} diverged"
+    comm.finalize(); comm.destroy()
+
+
 def ddp_sharded():
     """Sharded optimizer on GPUs: same losses as the replicated optimizer step for step (same averaged gradients,
     same arithmetic per element, clipping by the same global norm), replicas bit-identical, state 1/world."""
@@ -613,6 +654,33 @@ def tp_ffn():
         err = ((out.float() - ref).abs().max() / ref.abs().max()).item()
         assert err < 1e-2, ("ffn output", it, err)
     comm.finalize(); comm.destroy()
+
+
+def symmetry_check():
+    """MCCL_CHECK_SYMMETRY=1: calls that keep the contract pass, a send buffer at a rank-dependent offset of a
+    symmetric allocation is reported as invalid usage."""
+    comm = make_comm()
+    k = 4096
+    sym = comm.empty(k * WORLD, torch.float32)
+    out = comm.empty(k * WORLD, torch.float32)
+    sym.copy_(gen(RANK, k * WORLD, torch.float32))
+    comm.all_reduce(sym, out, op="sum")
+    comm.all_gather(out[RANK * k:(RANK + 1) * k], out)               # in place: the same part by contract
+    comm.reduce_scatter(sym, sym[RANK * k:(RANK + 1) * k], op="sum")    # in place
+    plain = torch.ones(100, device=DEV)
+    comm.all_reduce(plain)
+    torch.cuda.synchronize()
+    assert comm.async_error() == L.SUCCESS
+    comm.all_gather(sym[RANK * k:(RANK + 1) * k], out)               # out of place, offset depends on the rank: refused
+    torch.cuda.synchronize()
+    assert comm.async_error() == L.INVALID_USAGE, comm.async_error()
+    try:
+        comm.all_reduce(plain)
+        raise AssertionError("the communicator must refuse work after a contract violation")
+    except mccl.MCCLError as exc:
+        assert exc.code == L.INVALID_USAGE
+    comm.host_barrier()
+    comm.destroy()
 
 
 def grouped_allreduce():

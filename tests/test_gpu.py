@@ -456,6 +456,42 @@ def test_rooted_collectives_spread_over_all_ranks():
 
 
 @need2
+def test_ddp_step_recorded_in_a_cuda_graph():
+    assert_all_ok(run_ranks(2, "ddp_graphed", worker="_gpu_worker.py", timeout=600))
+
+
+def test_graphed_step_on_one_gpu_matches_eager():
+    _require_cuda()
+    from mccl_b200.models.gpt2 import GPT2, GPT2Config
+    from mccl_b200.parallel.ddp import DistributedDataParallel
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = GPT2Config.tiny()
+    batches = torch.randint(0, cfg.vocab_size, (3, 4, cfg.seq_len + 1), generator=torch.Generator().manual_seed(3)).to(dev)
+
+    def build():
+        torch.manual_seed(0)
+        return DistributedDataParallel(GPT2(cfg).to(device=dev, dtype=torch.bfloat16), None)
+
+    eager, ref = build(), []
+    for i in range(6):
+        t = batches[i % 3]
+        loss = eager(t[:, :-1], t[:, 1:]); loss.backward(); eager.step(lr=3e-3, max_grad_norm=1.0)
+        ref.append(loss.item())
+    ddp = build()
+    step = ddp.graphed_step((batches[0][:, :-1], batches[0][:, 1:]), lr=3e-3, max_grad_norm=1.0, warmup=1)
+    got = [ref[0]] + [step(batches[i % 3][:, :-1], batches[i % 3][:, 1:]).item() for i in range(1, 6)]
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (ref, got)
+    assert got[-1] < got[1] and ddp.step_count == 6
+
+
+@need2
+def test_symmetric_buffer_contract_is_checked_on_request():
+    assert_all_ok(run_ranks(2, "symmetry_check", worker="_gpu_worker.py", env={"MCCL_CHECK_SYMMETRY": "1"}, timeout=300))
+
+
+@need2
 def test_group_of_all_reduce_calls_is_one_launch():
     assert_all_ok(run_ranks(min(NGPU, 4), "grouped_allreduce", worker="_gpu_worker.py", timeout=300))
 
