@@ -92,6 +92,8 @@ def main() -> int:
     ap.add_argument("--budget-s", type=float, default=600.0, help="stop starting new cells after this many seconds")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--passes", default="1,2,3,4")
+    ap.add_argument("--colls", default="allreduce,allgather,reducescatter,broadcast,reduce")
+    ap.add_argument("--min-mb", type=float, default=0.0, help="skip cells smaller than this")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -235,7 +237,8 @@ def main() -> int:
     b = 1024
     while b <= args.max_mb << 20:
         sizes.append(b); b *= 4
-    colls = ("allreduce", "allgather", "reducescatter", "broadcast", "reduce")
+    colls = tuple(c for c in ("allreduce", "allgather", "reducescatter", "broadcast", "reduce") if c in args.colls.split(","))
+    sizes = [s_ for s_ in sizes if s_ >= args.min_mb * (1 << 20)]
     ops_of = lambda coll: ("sum", "prod", "max", "min", "avg") if coll in REDUCING else ("sum",)
     passes = set(args.passes.split(","))
     done = set()

@@ -59,8 +59,11 @@ struct GemmArgs {
   __nv_bfloat16* out;          // RS: [M/n, N]
   float* accum;                // RS: [M/n, N] fp32 running sum of the partials that have arrived
   int panel;                   // stripes per rasterisation panel (divides the stripes of a row block)
+  CUtensorMap mapC;            // two-SM kernel: C as [M, N] bf16, box 64 x 32, for the epilogue's TMA stores
+  int tmaStore;                // 1: mapC is valid
   int debug;                   // tuning aid of the two-SM kernel (MCCL_GEMM_DEBUG): bit 0 = skip the loads after the
-                               // first ring fill, bit 1 = skip the epilogue's global stores; results are then meaningless
+                               // first ring fill, bit 1 = skip the epilogue's global stores (results are then meaningless), bit 2 = per-thread
+                               // 16-byte stores instead of the TMA store
 };
 
 template <int BN> struct Smem {

@@ -28,11 +28,13 @@ constexpr int kThreadsGemm2 = 256;
 template <int BN> struct Smem2 {
   static constexpr int A_BYTES = BM * BK * 2;              // this CTA's 128 rows
   static constexpr int B_BYTES = (BN / 2) * BK * 2;        // this CTA's half of the B tile
-  // as many stages as fit beside the barriers in the 227 KB a CTA may use, eight at most (BN 256 and 224: seven)
-  static constexpr int FIT = (232448 - 1536) / (A_BYTES + B_BYTES);
+  // Epilogue staging: per epilogue warp two buffers of 32 rows x 128 bytes (64 bf16), from which TMA stores go out.
+  static constexpr int EPI_BYTES = 4 * 2 * 32 * 128;
+  // as many stages as fit beside that and the barriers in the 227 KB a CTA may use, eight at most (BN 256 and 224: six)
+  static constexpr int FIT = (232448 - 1536 - EPI_BYTES) / (A_BYTES + B_BYTES);
   static constexpr int STAGES = FIT > 8 ? 8 : FIT;
   static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
-  static constexpr int TOTAL = TILE_BYTES + 512 + 1024;    // barriers + alignment slack
+  static constexpr int TOTAL = TILE_BYTES + EPI_BYTES + 512 + 1024;    // + barriers + alignment slack
 };
 
 namespace umma2 {
@@ -120,7 +122,8 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES2 * S::A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::TILE_BYTES);
+  uint8_t* sEpi = smem + S::TILE_BYTES;            // 1024-byte aligned: every tile size is a multiple of 1024
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::TILE_BYTES + S::EPI_BYTES);
   uint64_t* full = bars;                          // [STAGES2] used in the leader: all four loads of a stage
   uint64_t* empty = bars + STAGES2;               // [STAGES2] in each CTA: the MMAs have read the stage
   uint64_t* tmemFull = bars + 2 * STAGES2;        // [2] in each CTA: accumulator complete
@@ -144,6 +147,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
     umma::fenceBarrierInit();
     umma::prefetchTensorMap(&a.mapA);
     umma::prefetchTensorMap(&a.mapB);
+    if (a.tmaStore) umma::prefetchTensorMap(&a.mapC);
   }
   if (warp == 2) { umma2::tmemAlloc(tmemSlot, kTmemCols); umma2::tmemRelinquish(); }
   umma::tcFenceBefore();
@@ -234,6 +238,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
     // ---------------- epilogue (both CTAs, own 128 rows)
     const int q = warp - 4;
     int acc = 0; uint32_t accPhase = 0;
+    uint32_t epiCount = 0;                          // chunks staged so far: consecutive chunks alternate buffers, across tiles too
     for (int t = pair; t < totalTiles; t += numPairs) {
       int stripe, nt;
       tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
@@ -245,8 +250,47 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
       const int stripe128 = stripe * 2 + (int)ctaRank;                 // this CTA's 128 rows of the pair's tile
       const size_t row = (size_t)stripe128 * BM + q * 32 + lane;
       __nv_bfloat16* dstRow = a.C + row * (size_t)a.N + (size_t)nt * BN;
+      // Whole 64-column chunks leave through shared memory and one TMA store per warp and chunk (each warp its 32
+      // rows: no barrier between warps); a 32-column remainder of BN, and everything when the tuning aid asks
+      // for it, takes the per-thread stores below.
+      const bool viaTma = a.tmaStore && !(a.debug & 4);
+      int cDone = 0;
+      if (viaTma) {
+        uint8_t* myEpi = sEpi + q * 8192;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+        for (int c64 = 0; c64 < BN / 64; ++c64) {
+          uint8_t* buf = myEpi + (epiCount++ & 1) * 4096;
+          uint32_t v[64];
+          const uint32_t taddr = tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u + (uint32_t)c64 * 64u;
+          umma::tmemLoad32x32(taddr, v);
+          umma::tmemLoad32x32(taddr + 32u, v + 32);
+          if (lane == 0) umma::tmaStoreWaitRead<1>();          // the store that read this buffer two chunks ago is done with it
+          umma::tmemLoadWait();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float x0 = __uint_as_float(v[8 * j + 2 * e]), x1 = __uint_as_float(v[8 * j + 2 * e + 1]);
+              if (a.epilogue == EPI_SILU) { x0 = silu(x0); x1 = silu(x1); }
+              o2[e] = __floats2bfloat162_rn(x0, x1);
+            }
+            // 128-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ (r % 8)
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+          }
+          umma::fenceProxyAsyncShared();
+          __syncwarp();
+          if (lane == 0 && !(a.debug & 2)) {
+            umma::tmaStore2d(&a.mapC, buf, nt * BN + c64 * 64, stripe128 * BM + q * 32);
+            umma::tmaStoreCommit();
+          }
+        }
+        cDone = (BN / 64) * 2;
+      }
+#pragma unroll 1
+      for (int c = cDone; c < BN / 32; ++c) {
         uint32_t v[32];
         umma::tmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u + (uint32_t)c * 32u, v);
         umma::tmemLoadWait();
@@ -269,6 +313,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
       acc ^= 1; if (acc == 0) accPhase ^= 1;
       if (MODE == MODE_RS) {
         // Count the tile towards its 128-row stripe; tell the owner of the row block when the stripe is whole.
+        if (viaTma && lane == 0) { umma::tmaStoreWaitAll(); umma::fenceProxyAsyncGlobal(); }   // this warp's rows of the tile are written
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 4 && lane == 0) {
           __threadfence_system();
@@ -282,6 +327,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
         }
       }
     }
+    if (a.tmaStore && lane == 0) umma::tmaStoreWaitAll();      // shared memory stays valid until the stores have read it
   } else if (warp >= 8 && MODE != MODE_PLAIN) {
     commWarps<MODE>(a, sFail, n, rank, 2 * stripesPerBlock);
   }

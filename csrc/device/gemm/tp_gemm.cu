@@ -66,6 +66,23 @@ int pickBN(int M, int N, int sms) {
   return best;
 }
 
+// Tile width of the two-SM kernel for `stripes` 256-row stripes on `pairs` SM pairs.  An MMA over 128 rows per SM
+// takes the same time for every N up to 256, so the time of a tile hardly depends on its width (a 224-wide tile
+// measured 0.965 of a 256-wide one: less operand traffic): minimise waves x tile time.
+int pickBN2(int stripes, int N, int pairs) {
+  const int cand[] = {256, 224, 192, 160, 128, 96, 64};
+  int best = 0;
+  double bestCost = 1e30;
+  for (int bn : cand) {
+    if (N % bn) continue;
+    const long tiles = (long)stripes * (N / bn);
+    const long waves = (tiles + pairs - 1) / pairs;
+    const double cost = (double)waves * (0.72 + 0.28 * bn / 256.0);
+    if (cost < bestCost - 1e-9) { bestCost = cost; best = bn; }
+  }
+  return best;
+}
+
 int* errFlagFor(int device) {
   static std::mutex mu;
   static int* flags[64] = {nullptr};
@@ -259,7 +276,7 @@ mcclResult_t mcclTpGemm2(const void* A, const void* B, void* C, int M, int N, in
     return mcclInvalidArgument;
   }
   const int pairsMax = std::max(1, (maxCtas > 0 ? maxCtas : smCount()) / 2);
-  int bn = pickBN(M / 2, N, pairsMax);                // M / 2: pickBN counts 128-row stripes, a pair takes 256 rows
+  int bn = pickBN2(M / BM2, N, pairsMax);
   const int forcedBn = (int)envInt("MCCL_GEMM_BN", 0);          // tuning aid: a tile width that divides N
   if (forcedBn > 0 && N % forcedBn == 0) bn = forcedBn;
   const void* fn = nullptr;
@@ -279,6 +296,8 @@ mcclResult_t mcclTpGemm2(const void* A, const void* B, void* C, int M, int N, in
   if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
   a.budgetNs = 2000000000ull;
   a.debug = (int)envInt("MCCL_GEMM_DEBUG", 0);
+  MCCLCHECK(makeMap(&a.mapC, C, M, N, 32));
+  a.tmaStore = 1;
   a.panel = pickPanel(M / BM2);
   if (envInt("MCCL_GEMM_PANEL", 0) > 0) a.panel = (int)envInt("MCCL_GEMM_PANEL", 0);
   const int tiles = (M / BM2) * (N / bn);
@@ -310,12 +329,12 @@ mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFul
   int sms = std::min(smCount(), MCCL_MAX_CTAS);
   int bn = 0;
   if (two) {
-    bn = pickBN(M / 2, N, sms / 2);
+    bn = pickBN2(M / BM2, N, sms / 2);
     if (bn == 0 || !pairKernel<MODE_AG>(bn, &fn2, &smem2)) return mcclInvalidArgument;
     MCCLCHECK(pairPrepare(fn2, smem2));
     pairs = std::min(residentPairs(fn2, kThreadsGemm, smem2), sms / 2);
     if (pairs <= 0) return mcclSystemError;
-    if (pairs != sms / 2) bn = pickBN(M / 2, N, pairs);
+    if (pairs != sms / 2) bn = pickBN2(M / BM2, N, pairs);
     if (bn == 0 || !pairKernel<MODE_AG>(bn, &fn2, &smem2)) return mcclInvalidArgument;
     MCCLCHECK(pairPrepare(fn2, smem2));
   } else {
@@ -329,6 +348,7 @@ mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFul
   a.M = M; a.N = N; a.K = K;
   a.C = static_cast<__nv_bfloat16*>(out);
   a.epilogue = epilogue;
+  if (two) { MCCLCHECK(makeMap(&a.mapC, out, M, N, 32)); a.tmaStore = 1; }
   int* hostFlag = errFlagFor(comm->device);
   if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
   a.peers = comm->cu->peers;
@@ -380,12 +400,12 @@ mcclResult_t mcclTpGemmReduceScatter(mcclComm_t comm, const void* H, const void*
   int sms = std::min(smCount(), MCCL_MAX_CTAS);
   int bn = 0;
   if (two) {
-    bn = pickBN(M / 2, N, sms / 2);
+    bn = pickBN2(M / BM2, N, sms / 2);
     if (bn == 0 || !pairKernel<MODE_RS>(bn, &fn2, &smem2)) return mcclInvalidArgument;
     MCCLCHECK(pairPrepare(fn2, smem2));
     pairs = std::min(residentPairs(fn2, kThreadsGemm, smem2), sms / 2);
     if (pairs <= 0) return mcclSystemError;
-    if (pairs != sms / 2) bn = pickBN(M / 2, N, pairs);
+    if (pairs != sms / 2) bn = pickBN2(M / BM2, N, pairs);
     if (bn == 0 || !pairKernel<MODE_RS>(bn, &fn2, &smem2)) return mcclInvalidArgument;
     MCCLCHECK(pairPrepare(fn2, smem2));
   } else {
@@ -399,6 +419,7 @@ mcclResult_t mcclTpGemmReduceScatter(mcclComm_t comm, const void* H, const void*
   a.M = M; a.N = N; a.K = K;
   a.C = static_cast<__nv_bfloat16*>(partial);
   a.epilogue = EPI_NONE;
+  if (two) { MCCLCHECK(makeMap(&a.mapC, partial, M, N, 32)); a.tmaStore = 1; }
   int* hostFlag = errFlagFor(comm->device);
   if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
   a.peers = comm->cu->peers;

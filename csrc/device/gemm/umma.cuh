@@ -71,6 +71,19 @@ __device__ __forceinline__ void tmaLoad2d(void* smemDst, const CUtensorMap* map,
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       :: "r"(smemAddr(smemDst)), "l"(map), "r"(smemAddr(bar)), "r"(x), "r"(y) : "memory");
 }
+// 2-D tiled store shared -> global (bulk async-group completion).  x = innermost coordinate, a multiple of 64
+// bf16 here; the source tile is laid out with the map's 128-byte swizzle.
+__device__ __forceinline__ void tmaStore2d(const CUtensorMap* map, const void* smemSrc, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               :: "l"(map), "r"(smemAddr(smemSrc)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmaStoreCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's store groups still READ their shared-memory source (the buffer may be reused).
+template <int N> __device__ __forceinline__ void tmaStoreWaitRead() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
+// Wait until every store group of this thread has completed (its global writes are performed).
+__device__ __forceinline__ void tmaStoreWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Shared-memory writes of this thread become visible to the async proxy (TMA) after this fence.
+__device__ __forceinline__ void fenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void prefetchTensorMap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory");
 }
