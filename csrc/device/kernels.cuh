@@ -316,19 +316,24 @@ __device__ __forceinline__ void ringBody(const RingArgs& a) {
   const uint64_t tag = epoch << 10;                 // step signals of this call: tag + steps completed
   const uint64_t V = a.bytes / 16;
   char* own = a.buf[r];
-  const char* prevBuf = a.buf[a.prev];
-  uint64_t* nextSig = &flagsOf(P, a.next)->sig[cta][r];
-  const uint64_t* prevSig = &mine->sig[cta][a.prev];
+  // Counter-rotating channels: even CTAs pass data prev -> me -> next, odd CTAs the other way round (the dual
+  // ring of the reference, src/device/all_reduce.h:118-136, generalised to channels).  A CTA's signals use its own
+  // slots, so the two directions never meet; every rank makes the same choice for CTA b.
+  const int dir = (G > 1 && (cta & 1)) ? -1 : 1;
+  const int from = dir > 0 ? a.prev : a.next, to = dir > 0 ? a.next : a.prev;
+  const char* prevBuf = a.buf[from];
+  uint64_t* nextSig = &flagsOf(P, to)->sig[cta][r];
+  const uint64_t* prevSig = &mine->sig[cta][from];
   int done = 0;
   const bool hasRS = a.phases == 0 || (a.phases & 1), hasAG = a.phases == 0 || (a.phases & 2);
   const int nSteps = (hasRS ? n - 1 : 0) + (hasAG ? n - 1 : 0);
   for (int step = 0; ok && step < nSteps; ++step) {
     const bool reducing = hasRS && step < n - 1;
     const int i = reducing ? step : step - (hasRS ? n - 1 : 0);
-    const int ringChunk = reducing ? ((r - (i + 1)) % n + n) % n : ((r - i) % n + n) % n;
-    const int chunk = ((ringChunk - a.shift) % n + n) % n;
+    const int ringChunk = reducing ? ((r - dir * (i + 1)) % n + n) % n : ((r - dir * i) % n + n) % n;
+    const int chunk = ((ringChunk - dir * a.shift) % n + n) % n;
     if (step > 0) {
-      if (tid == 0 && !waitFlag(prevSig, tag + step, P, 2u, a.prev, step)) sFail = 1;
+      if (tid == 0 && !waitFlag(prevSig, tag + step, P, 2u, from, step)) sFail = 1;
       __syncthreads();
       if (sFail) { ok = false; break; }
     }

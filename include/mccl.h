@@ -191,6 +191,16 @@ mcclResult_t mcclGroupAbort(void);
  * it in place. */
 mcclResult_t mcclMemAlloc(mcclComm_t comm, size_t bytes, void** ptr);
 mcclResult_t mcclMemFree(mcclComm_t comm, void* ptr);
+/* A pool over ONE symmetric allocation: Create and Destroy are collective (they are mcclMemAlloc / mcclMemFree),
+ * Alloc and Free are local bookkeeping (first fit, 256-byte granularity, neighbours merged on free).  Every rank
+ * must make the same sequence of Alloc / Free calls, so that a sub-allocation is the same part of the allocation
+ * on every rank.  Alloc returns mcclSystemError (and NULL) when no free range is large enough. */
+typedef struct mcclSymPool* mcclSymPool_t;
+mcclResult_t mcclSymPoolCreate(mcclComm_t comm, size_t bytes, mcclSymPool_t* pool);
+mcclResult_t mcclSymPoolAlloc(mcclSymPool_t pool, size_t bytes, void** ptr);
+mcclResult_t mcclSymPoolFree(mcclSymPool_t pool, void* ptr);
+mcclResult_t mcclSymPoolStats(mcclSymPool_t pool, size_t* total, size_t* inUse, size_t* largestFree);
+mcclResult_t mcclSymPoolDestroy(mcclSymPool_t pool);
 /* Collective registration of an existing cudaMalloc'ed range (CUDA IPC); after it the range is used in
  * place by the peer-to-peer algorithms. */
 mcclResult_t mcclCommRegister(mcclComm_t comm, void* ptr, size_t bytes, void** handle);

@@ -71,11 +71,15 @@ def build(verbose: bool = False, force: bool = False) -> Path:
                         print(log)
     if jobs or not LIB.exists():
         LIB.parent.mkdir(parents=True, exist_ok=True)
-        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static",
+        # Linked beside the target and renamed into place: whoever copies or loads the tree never sees half a library.
+        tmp = LIB.with_name(f".{LIB.name}.{os.getpid()}.tmp")
+        cmd = [NVCC, "-shared", "-o", str(tmp), *map(str, objs), "-cudart", "static",
                "-gencode", "arch=compute_100a,code=sm_100a", "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
+            tmp.unlink(missing_ok=True)
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{p.stdout}\n{p.stderr}")
+        os.replace(tmp, LIB)
         if verbose:
             print(f"[mccl build] linked {LIB.relative_to(ROOT)}")
     return LIB

@@ -396,6 +396,11 @@ class Communicator:
         self._sym[t.data_ptr()] = holder
         return t
 
+    def pool(self, nbytes: int) -> "SymmetricPool":
+        """Collective: one symmetric allocation of `nbytes` to carve tensors from without further collectives (see
+        SymmetricPool)."""
+        return SymmetricPool(self, nbytes)
+
     def register(self, tensor) -> int:
         """Collective: map an existing CUDA tensor (cudaMalloc memory, e.g. from torch's allocator) into every
         peer through CUDA IPC so the peer-load algorithms use it in place.  Returns a handle for deregister()."""
@@ -428,3 +433,70 @@ class _SymBlock:
         self.__cuda_array_interface__ = {
             "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
         }
+
+
+class SymmetricPool:
+    """Tensors carved from ONE symmetric allocation (mcclSymPool*).  Creating and destroying the pool are collective;
+    `empty` and `free` are local bookkeeping, so they cost microseconds instead of a handle exchange, but every rank
+    must make the same sequence of `empty` / `free` calls (a tensor is then the same part of the allocation on every
+    rank, which is what the kernels assume of symmetric buffers)."""
+
+    def __init__(self, comm: Communicator, nbytes: int):
+        self.comm = comm
+        self._lib = comm._lib
+        self._p = C.c_void_p()
+        self._declare()
+        L.check(self._lib.mcclSymPoolCreate(comm._h, C.c_size_t(nbytes), C.byref(self._p)), "mcclSymPoolCreate")
+        self._holders = {}
+
+    def _declare(self) -> None:
+        lib = self._lib
+        if getattr(lib, "_sympool_declared", False):
+            return
+        vp, sz = C.c_void_p, C.c_size_t
+        lib.mcclSymPoolCreate.restype = C.c_int; lib.mcclSymPoolCreate.argtypes = [vp, sz, C.POINTER(vp)]
+        lib.mcclSymPoolAlloc.restype = C.c_int; lib.mcclSymPoolAlloc.argtypes = [vp, sz, C.POINTER(vp)]
+        lib.mcclSymPoolFree.restype = C.c_int; lib.mcclSymPoolFree.argtypes = [vp, vp]
+        lib.mcclSymPoolStats.restype = C.c_int; lib.mcclSymPoolStats.argtypes = [vp, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]
+        lib.mcclSymPoolDestroy.restype = C.c_int; lib.mcclSymPoolDestroy.argtypes = [vp]
+        lib._sympool_declared = True
+
+    def alloc_raw(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        L.check(self._lib.mcclSymPoolAlloc(self._p, C.c_size_t(nbytes), C.byref(p)), "mcclSymPoolAlloc")
+        return p.value
+
+    def free_raw(self, ptr: int) -> None:
+        self._holders.pop(ptr, None)
+        L.check(self._lib.mcclSymPoolFree(self._p, C.c_void_p(ptr)), "mcclSymPoolFree")
+
+    def empty(self, shape, dtype=None):
+        """A tensor from the pool (CUDA on the cuda transport, host memory on tcp); local, same call order on every rank."""
+        dtype = dtype or torch.float32
+        numel = int(np.prod(shape)) if not isinstance(shape, int) else int(shape)
+        nbytes = max(numel * torch.empty((), dtype=dtype).element_size(), 16)
+        ptr = self.alloc_raw(nbytes)
+        if self.comm.transport == "cuda":
+            holder = _SymBlock(self.comm, ptr, nbytes)
+            t = torch.as_tensor(holder, device=f"cuda:{self.comm.device}").view(dtype)[:numel].view(shape)
+        else:
+            holder = (C.c_char * nbytes).from_address(ptr)
+            t = torch.frombuffer(holder, dtype=torch.uint8).view(dtype)[:numel].view(shape)
+        self._holders[ptr] = holder
+        return t
+
+    def free(self, tensor) -> None:
+        self.free_raw(tensor.data_ptr())
+
+    def stats(self) -> dict:
+        """{'total', 'in_use', 'largest_free'} in bytes."""
+        a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
+        L.check(self._lib.mcclSymPoolStats(self._p, C.byref(a), C.byref(b), C.byref(c)))
+        return {"total": a.value, "in_use": b.value, "largest_free": c.value}
+
+    def destroy(self) -> None:
+        """Collective: give the allocation back (no tensor from the pool may be used afterwards)."""
+        if self._p:
+            self._holders.clear()
+            L.check(self._lib.mcclSymPoolDestroy(self._p), "mcclSymPoolDestroy")
+            self._p = C.c_void_p()

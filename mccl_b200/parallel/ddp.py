@@ -104,6 +104,13 @@ class DistributedDataParallel(nn.Module):
         self._bucket_of = {}
         if self.world > 1 and sync_params:
             self._sync_initial_state(module)
+        # All communication buffers come from ONE symmetric allocation (one handle exchange, one multicast binding)
+        # instead of one collective allocation per bucket.
+        self._pool = None
+        if self.world > 1 and self.device.type == "cuda":
+            es = params[0].element_size()
+            per = sum((b.numel * es + 255) // 256 * 256 for b in self.buckets)
+            self._pool = comm.pool(per * (2 if self.sharded else 1) + 4096)
         for b in self.buckets:
             self._materialize(b)
             for p in b.params:
@@ -133,13 +140,13 @@ class DistributedDataParallel(nn.Module):
 
     def _materialize(self, b: _Bucket) -> None:
         dev, dt = self.device, self.dtype
-        if self.world > 1 and dev.type == "cuda":
-            b.grad = self.comm.empty(b.numel, dt)           # collective: same order on every rank
+        if self._pool is not None:
+            b.grad = self._pool.empty(b.numel, dt)          # local bookkeeping: same order on every rank
             b.grad.zero_()
         else:
             b.grad = torch.zeros(b.numel, device=dev, dtype=dt)
-        if self.sharded and dev.type == "cuda":
-            b.param = self.comm.empty(b.numel, dt)          # all-gathered in place after the optimizer step
+        if self.sharded and self._pool is not None:
+            b.param = self._pool.empty(b.numel, dt)         # all-gathered in place after the optimizer step
             b.param.zero_()
         else:
             b.param = torch.zeros(b.numel, device=dev, dtype=dt)
@@ -239,7 +246,7 @@ class DistributedDataParallel(nn.Module):
         if max_grad_norm is not None and cuda:
             if self._norm_sq is None:
                 # four floats: a 16-byte message takes the one-shot all-reduce when the norm is summed over ranks
-                self._norm_sq = (self.comm.empty(4, torch.float32) if self.sharded else
+                self._norm_sq = (self._pool.empty(4, torch.float32) if self.sharded else
                                  torch.zeros(4, device=self.device, dtype=torch.float32))
                 self._norm_sq.zero_()
                 self._norm_scratch = torch.zeros(scratch_floats(max(b.hi - b.lo for b in self.buckets)), device=self.device,

@@ -508,3 +508,32 @@ def test_python_wrappers_refuse_mismatched_buffers():
     comm.broadcast(x, y)
     assert torch.equal(x, y)
     comm.finalize(); comm.destroy()
+
+
+def test_symmetric_pool_bookkeeping():
+    """One allocation, local first-fit sub-allocations: aligned, disjoint, merged on free, refused when full."""
+    import torch
+    import mccl_b200 as mccl
+    comm = mccl.Communicator(1, mccl.get_unique_id(), 0, transport="tcp")
+    pool = comm.pool(64 * 1024)
+    a = pool.empty(1000, torch.float32)           # 4000 bytes -> 4096
+    b = pool.empty(3, torch.bfloat16)             # 16 bytes minimum -> 256
+    c = pool.empty((8, 16), torch.float32)
+    assert a.data_ptr() % 256 == 0 and b.data_ptr() == a.data_ptr() + 4096 and c.data_ptr() == b.data_ptr() + 256
+    a.fill_(1.0); b.fill_(2.0); c.fill_(3.0)
+    assert a.sum() == 1000 and c.shape == (8, 16) and float(b[0]) == 2.0
+    st = pool.stats()
+    assert st["total"] == 65536 and st["in_use"] == 4096 + 256 + 512
+    pool.free(b)
+    d = pool.empty(40, torch.float32)             # 160 bytes: first fit reuses b's range
+    assert d.data_ptr() == a.data_ptr() + 4096
+    pool.free(a); pool.free(d); pool.free(c)
+    st = pool.stats()
+    assert st["in_use"] == 0 and st["largest_free"] == 65536       # neighbours merged back into one range
+    with pytest.raises(mccl.MCCLError):
+        pool.empty(70000, torch.uint8)
+    with pytest.raises(mccl.MCCLError):
+        pool.free_raw(a.data_ptr())               # not live any more
+    comm.all_reduce(pool.empty(16, torch.float32).zero_())      # a pool tensor is an ordinary buffer for the collectives
+    pool.destroy()
+    comm.finalize(); comm.destroy()
