@@ -315,11 +315,14 @@ NvlsArgs baseNvls(const Call& k, size_t bytes, bool rootOnly = false) {
   return a;
 }
 
-// Rooted collectives with one shard per rank (NvlsRootedArgs).  Off unless MCCL_NVLS_SPREAD=1: the root-only
-// form below stays the default until this one has been timed against it.
-bool nvlsSpread() {
-  static const bool on = envInt("MCCL_NVLS_SPREAD", 0) != 0;
-  return on;
+// Rooted collectives with one shard per rank (NvlsRootedArgs) or with the root moving the whole message.  Measured
+// on 4 B200 (us, NCCL / root only / spread): broadcast 64 MB 143 / 161 / 159, 1 GB 1635 / 2125 / 2042; reduce 64 MB
+// 145 / 162 / 162, 256 MB 452 / 618 / 511, 1 GB 1656 / 2385 / 1936; below 64 MB the root-only form is the faster
+// one (16 MB: 59 against 63 - 67).  So: spread from 64 MB up.  MCCL_NVLS_SPREAD=0 never, =1 at every size.
+bool nvlsSpread(size_t bytes) {
+  static const int mode = (int)envInt("MCCL_NVLS_SPREAD", -1);
+  if (mode >= 0) return mode != 0;
+  return bytes >= ((size_t)64 << 20);
 }
 
 mcclResult_t launchNvlsRooted(const Call& k, const NvlsRootedArgs& a) {
@@ -579,7 +582,7 @@ mcclResult_t broadcast(const Call& k, const void* send, void* recv, size_t count
   const View rv = viewOf(k.st, recv, bytes);
   const bool direct = algo == mcclAlgoOneShot;
   if (algo == mcclAlgoNvls && k.st->nvls && rv.sym() && rv.mc() && bytes % 16 == 0 && al16(recv) && (k.r != root || al16(send))) {
-    if (nvlsSpread() && bytes >= (size_t)k.n * 16) {
+    if (nvlsSpread(bytes) && bytes >= (size_t)k.n * 16) {
       // The peers read the root's destination buffer, so an out-of-place root copies there first.
       if (k.r == root) MCCLCHECK(launchCopy(k.c, send, recv, 1, bytes, bytes, bytes, k.s));
       NvlsRootedArgs a;
@@ -650,7 +653,7 @@ mcclResult_t reduce(const Call& k, const void* send, void* recv, size_t count, i
   const bool direct = algo == mcclAlgoOneShot;
   if (algo == mcclAlgoNvls && k.st->nvls && sv.sym() && sv.mc() && nvlsType(k.dt, k.op, k.n) && bytes % 16 == 0 && al16(send) &&
       (k.r != root || al16(recv))) {
-    if (nvlsSpread() && bytes >= (size_t)k.n * 16) {
+    if (nvlsSpread(bytes) && bytes >= (size_t)k.n * 16) {
       NvlsRootedArgs a;
       memset(&a, 0, sizeof(a));
       a.peers = k.st->peers;
