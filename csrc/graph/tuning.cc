@@ -212,6 +212,15 @@ mcclResult_t tunerPick(const TunerModel& m, int coll, int n, size_t bytes, int d
   if (algo == nullptr) MCCLFAIL(mcclInvalidArgument);
   // Measured on 2 and 8 B200: for all-gather, reduce-scatter, broadcast and reduce the NVLS form is at
   // least as fast as the peer-load form at every size, so the model is only consulted for all-reduce.
+  // Exception, measured on 4 B200: multicast delivers about 505 GB/s into each GPU, peer loads 650 and more, so from
+  // 64 MB up all-gather and reduce-scatter are faster in the peer-load ("direct") form there (64 MB, us: all-gather
+  // 111.7 direct / 120.7 NVLS / 116.8 NCCL; reduce-scatter 107.0 / 124.8 / 118.2).  On 8 GPUs the two forms measured
+  // the same, so the rule is kept to small worlds.
+  if (cudaTransport && (coll == mcclCollAllGather || coll == mcclCollReduceScatter) && n <= 4 && bytes >= ((size_t)64 << 20) &&
+      (enabled == nullptr || enabled[mcclAlgoOneShot]) && m.viable[mcclAlgoOneShot]) {
+    *algo = mcclAlgoOneShot;
+    return mcclSuccess;
+  }
   if (cudaTransport && coll != mcclCollAllReduce && (enabled == nullptr || enabled[mcclAlgoNvls]) && m.viable[mcclAlgoNvls] &&
       algoSupports(mcclAlgoNvls, coll, dt, op, true) && nvlsAvgExact(dt, op, n)) {
     *algo = mcclAlgoNvls;
