@@ -5,7 +5,7 @@ from the ranks' inputs (bit-exact for int32, within the dtype's tolerance for fl
 to NCCL and, on a subset of sizes, every forced algorithm next to the tuner's choice.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
-        bench/coll_matrix.py [--max-mb 1024] [--budget-s 600] [--out matrix.jsonl]
+        bench/coll_matrix.py [--max-mb 1024] [--time-limit-s 600] [--out matrix.jsonl]
 
 Inputs: element i of rank r is a fixed function of (r, i): uniform in [-1, 1] for floats, integers in [-1000, 1000]
 for int32 (factors near 1 or of magnitude 1 for `prod`, so that products stay representable).  Any window of any
@@ -14,7 +14,7 @@ rather than on all of a 1 GB message.
 
 `size` is the per-rank message of AllReduce / Broadcast / Reduce and the total (n x per-rank part) of AllGather /
 ReduceScatter.  Buffers are symmetric.  CUDA-event times, maximum over ranks.  The cells run in three passes, most
-important first, until `--budget-s` is spent: (1) every (collective, op, dtype) at four sizes, checked; (2) the
+important first, until `--time-limit-s` is spent: (1) every (collective, op, dtype) at four sizes, checked; (2) the
 timing grid against NCCL (bf16 and fp32, sum, every size); (3) every forced algorithm at three sizes, checked.
 The last line summarises cells run / exact / within tolerance / at least as fast as NCCL.
 """
@@ -75,7 +75,7 @@ def windows(n: int):
     return [(0, WINDOW), (mid, mid + WINDOW), (n - WINDOW, n)]
 
 
-def verdict(got, want, dt):
+def grade(got, want, dt):
     """'exact', 'close' or 'WRONG' for one window."""
     if not dt.is_floating_point:
         return "exact" if torch.equal(got.long(), want.long()) else "WRONG"
@@ -89,7 +89,7 @@ def verdict(got, want, dt):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=int, default=1024)
-    ap.add_argument("--budget-s", type=float, default=600.0, help="stop starting new cells after this many seconds")
+    ap.add_argument("--time-limit-s", type=float, default=600.0, help="stop starting new cells after this many seconds")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--passes", default="1,2,3,4")
     ap.add_argument("--colls", default="allreduce,allgather,reducescatter,broadcast,reduce")
@@ -112,7 +112,7 @@ def main() -> int:
 
     def out_of_time():
         # rank 0 decides, so that every rank stops at the same cell
-        return struct.unpack("d", comm.host_all_gather(struct.pack("d", time.time() - t_start))[0])[0] > args.budget_s
+        return struct.unpack("d", comm.host_all_gather(struct.pack("d", time.time() - t_start))[0])[0] > args.time_limit_s
 
     def timed(fn):
         fn(); fn()
@@ -191,18 +191,18 @@ def main() -> int:
                 if order[v] > order[worst]: worst = v
             if coll == "allreduce" or (coll == "reduce" and rank == 0):
                 for lo, hi in windows(n):
-                    note(verdict(big[lo:hi], reference(world, lo, hi, dt, op, dev), dt))
+                    note(grade(big[lo:hi], reference(world, lo, hi, dt, op, dev), dt))
             elif coll == "reducescatter":
                 for lo, hi in windows(m):
-                    note(verdict(small[lo:hi], reference(world, rank * m + lo, rank * m + hi, dt, op, dev), dt))
+                    note(grade(small[lo:hi], reference(world, rank * m + lo, rank * m + hi, dt, op, dev), dt))
             elif coll == "allgather":
                 for p in sorted({0, world // 2, world - 1}):
                     w = min(m, WINDOW)
-                    note(verdict(big[p * m:p * m + w], values(p, 0, w, dt, op, dev), dt))
-                    note(verdict(big[(p + 1) * m - w:(p + 1) * m], values(p, m - w, m, dt, op, dev), dt))
+                    note(grade(big[p * m:p * m + w], values(p, 0, w, dt, op, dev), dt))
+                    note(grade(big[(p + 1) * m - w:(p + 1) * m], values(p, m - w, m, dt, op, dev), dt))
             elif coll == "broadcast":
                 for lo, hi in windows(n):
-                    note(verdict(big[lo:hi], values(0, lo, hi, dt, op, dev), dt))
+                    note(grade(big[lo:hi], values(0, lo, hi, dt, op, dev), dt))
             if comm.async_error() != 0:
                 worst = "WRONG"
             worst = max((b.decode() for b in comm.host_all_gather(worst.encode().ljust(5))), key=lambda v: order[v.strip()]).strip()
@@ -286,7 +286,7 @@ def main() -> int:
     for t in bufs.get("sym", []):
         comm.free_raw(t.data_ptr())
     if rank == 0:
-        stats["stopped_by_budget"] = stopped
+        stats["stopped_by_time_limit"] = stopped
         stats["seconds"] = round(time.time() - t_start, 1)
         stats["world"] = world
         line = json.dumps({"summary": stats})

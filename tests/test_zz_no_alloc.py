@@ -38,6 +38,18 @@ def test_no_alloc_sum_squares_matches_regular_entry_point():
         assert noalloc(x.data_ptr(), n, b.data_ptr(), 1, stream) == 0          # accumulate on top
         torch.cuda.synchronize()
         assert torch.allclose(b[0], 2 * ref, rtol=2e-5)
+    # Exactly the largest count the fixed work area covers: every one of its partial-sum slots is in use.
+    n = 4096 * 65536
+    x = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    for lo in range(0, n, 1 << 26):
+        x[lo:lo + (1 << 26)].copy_(torch.randn(min(1 << 26, n - lo), device=dev))
+    ref = sum(x[lo:lo + (1 << 26)].double().pow(2).sum().item() for lo in range(0, n, 1 << 26))
+    for _ in range(2):                                                        # twice in a row: no leftovers at full size either
+        assert noalloc(x.data_ptr(), n, b.data_ptr(), 0, stream) == 0
+        torch.cuda.synchronize()
+        assert abs(b.item() - ref) <= 1e-4 * ref, (b.item(), ref)
+    del x
+    x = torch.ones(8, device=dev, dtype=torch.bfloat16)
     # Larger than the fixed work area: refused before anything is launched.
     too_many = 4096 * 65536 + 1
     assert noalloc(x.data_ptr(), too_many, b.data_ptr(), 0, stream) == 4       # mcclInvalidArgument
