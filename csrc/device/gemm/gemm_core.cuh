@@ -59,6 +59,13 @@ struct GemmArgs {
   __nv_bfloat16* out;          // RS: [M/n, N]
   float* accum;                // RS: [M/n, N] fp32 running sum of the partials that have arrived
   int panel;                   // stripes per rasterisation panel (divides the stripes of a row block)
+  // Two-SM kernel, split tail: when the tiles do not fill the last wave, the last `tailTiles` tiles are cut along K
+  // into `tailSlices` slices each, one slice per SM pair, so the last wave costs 1 / tailSlices of a tile instead of
+  // a whole one.  The slices add their fp32 partial tiles into `tailWs` (zero between launches: the CTA that adds
+  // last converts the sum to C and clears what it read); `tailCount` counts arrivals per (tile, half).
+  int tailTiles, tailSlices;
+  float* tailWs;
+  unsigned int* tailCount;
   CUtensorMap mapC;            // two-SM kernel: C as [M, N] bf16, box 64 x 32, for the epilogue's TMA stores
   int tmaStore;                // 1: mapC is valid
   int debug;                   // tuning aid of the two-SM kernel (MCCL_GEMM_DEBUG): bit 0 = skip the loads after the

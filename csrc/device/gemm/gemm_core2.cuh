@@ -91,6 +91,11 @@ __device__ __forceinline__ void mmaCommitMaskAddr(uint32_t barAddr, uint16_t mas
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                :: "r"(barAddr), "h"(mask) : "memory");
 }
+// Four fp32 added to global memory in one instruction (performed at L2).
+__device__ __forceinline__ void redAddF32x4(float* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(p), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)),
+               "f"(__uint_as_float(c)), "f"(__uint_as_float(d)) : "memory");
+}
 // Arrive on the barrier at this offset in both CTAs once every MMA issued so far has completed: one commit per
 // CTA, each naming that CTA's barrier by its shared::cluster address (a commit tracks all earlier MMAs of the
 // issuing thread, so the two are independent observers of the same work).
@@ -139,6 +144,13 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
   const int n = (MODE == MODE_PLAIN) ? 1 : a.peers.n, rank = (MODE == MODE_PLAIN) ? 0 : a.peers.rank;
   const int stripesPerBlock = stripes / n;          // 256-row stripes of one rank's row block
   const uint64_t budget = a.budgetNs;
+  // Split tail (see GemmArgs): this pair's slice of one of the last tiles, if any.
+  const int mainTiles = totalTiles - a.tailTiles;
+  const bool hasTail = a.tailTiles > 0 && pair < a.tailTiles * a.tailSlices;
+  const int tailIdx = hasTail ? pair / a.tailSlices : 0;                       // which of the tail tiles
+  const int tailSlice = hasTail ? pair - tailIdx * a.tailSlices : 0;
+  const int tailKb0 = hasTail ? (int)((long long)tailSlice * kBlocks / a.tailSlices) : 0;
+  const int tailLen = hasTail ? (int)((long long)(tailSlice + 1) * kBlocks / a.tailSlices) - tailKb0 : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) { umma::mbarInit(&full[s], 1); umma::mbarInit(&empty[s], 1); }
@@ -160,17 +172,22 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
     // ---------------- TMA producer (both CTAs)
     int stage = 0; uint32_t phase = 0;
     const bool noLoads = a.debug & 1;
-    for (int t = pair; t < totalTiles && *sFail == 0; t += numPairs) {
+    // main tiles, whole K each; then this pair's slice of a tail tile
+    for (int t = pair, turn = 0; *sFail == 0; t += numPairs, ++turn) {
+      const bool tail = t >= mainTiles;
+      if (tail && !hasTail) break;
+      const int tile = tail ? mainTiles + tailIdx : t;
       int stripe, nt;
-      tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
+      tileCoords<MODE>(tile, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
       if (MODE == MODE_AG) {
         const int shard = stripe / stripesPerBlock;
         if (!waitGpuFlag(&a.shardReady[shard], (uint64_t)gridDim.x, budget)) { *sFail = 1; atomicExch(a.errFlag, 20); break; }
         umma::fenceProxyAsyncGlobal();
       }
-      for (int kb = 0; kb < kBlocks; ++kb) {
+      const int kbLo = tail ? tailKb0 : 0, kbHi = tail ? tailKb0 + tailLen : kBlocks;
+      for (int kb = kbLo; kb < kbHi; ++kb) {
         if (!umma::mbarWaitParked(&empty[stage], phase ^ 1, budget)) { *sFail = 1; atomicExch(a.errFlag, 21); break; }
-        if (noLoads && (t != pair || kb >= STAGES2)) {       // tuning aid: the whole handshake, no data
+        if (noLoads && (turn != 0 || kb >= STAGES2)) {       // tuning aid: the whole handshake, no data
           if (ctaRank == 0) umma::mbarArrive(&full[stage]);
           if (++stage == STAGES2) { stage = 0; phase ^= 1; }
           continue;
@@ -181,6 +198,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
         umma2::tmaLoad2dPair(sB + stage * S::B_BYTES, &a.mapB, leaderFull, kb * BK, nt * BN + (int)ctaRank * (BN / 2));
         if (++stage == STAGES2) { stage = 0; phase ^= 1; }
       }
+      if (tail) break;
     }
   } else if (warp == 1 && lane == 0 && ctaRank == 0) {
     // ---------------- MMA issuer (leader only)
@@ -195,8 +213,9 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
     const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0, descHi = (uint32_t)(descA0 >> 32);
     const uint32_t emptyAddr = umma::smemAddr(empty), tmemFullAddr = umma::smemAddr(tmemFull);
     const uint32_t emptyPeer = umma2::mapToCta(emptyAddr, 1), tmemFullPeer = umma2::mapToCta(tmemFullAddr, 1);
-    const int myTiles = pair < totalTiles ? (totalTiles - pair + numPairs - 1) / numPairs : 0;
-    int remaining = myTiles * kBlocks;
+    const int myTiles = pair < mainTiles ? (mainTiles - pair + numPairs - 1) / numPairs : 0;
+    int remaining = myTiles * kBlocks + tailLen;
+    int tilesStarted = 0, curLen = kBlocks;          // k blocks of the tile being accumulated (the tail slice is shorter)
     int kb = 0, acc = 0; uint32_t phase = 0, accPhase = 0;
     uint32_t d = tmemBase;
     bool fail = false;
@@ -209,6 +228,8 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
           if (*sFail != 0) { fail = true; break; }
           if (!umma::mbarWait(&tmemEmpty[acc], accPhase ^ 1, budget)) { fail = true; *sFail = 1; atomicExch(a.errFlag, 22); break; }
           d = tmemBase + (uint32_t)acc * 256u;
+          curLen = tilesStarted < myTiles ? kBlocks : tailLen;
+          ++tilesStarted;
         }
         if (!kEarlyWait && !umma::mbarWait(&full[s], phase, budget)) { fail = true; *sFail = 1; atomicExch(a.errFlag, 23); break; }
         umma::tcFenceAfter();
@@ -224,7 +245,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
         if (kMcCommit) umma2::mmaCommitMaskAddr(emptyAddr + 8u * s, 3);
         else { umma2::mmaCommitTo(emptyAddr + 8u * s); umma2::mmaCommitTo(emptyPeer + 8u * s); }
         --remaining;
-        if (++kb == kBlocks) {
+        if (++kb == curLen) {
           kb = 0;
           if (kMcCommit) umma2::mmaCommitMaskAddr(tmemFullAddr + 8u * acc, 3);
           else { umma2::mmaCommitTo(tmemFullAddr + 8u * acc); umma2::mmaCommitTo(tmemFullPeer + 8u * acc); }
@@ -239,7 +260,7 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
     const int q = warp - 4;
     int acc = 0; uint32_t accPhase = 0;
     uint32_t epiCount = 0;                          // chunks staged so far: consecutive chunks alternate buffers, across tiles too
-    for (int t = pair; t < totalTiles; t += numPairs) {
+    for (int t = pair; t < mainTiles; t += numPairs) {
       int stripe, nt;
       tileCoords<MODE>(t, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
       bool good = *sFail == 0 && umma::mbarWaitParked(&tmemFull[acc], accPhase, budget);
@@ -324,6 +345,60 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
             __threadfence_system();
             stReleaseSys(&a.tileReadyPeer[owner][(size_t)rank * per128 + within], a.callIndex);
           }
+        }
+      }
+    }
+    if (hasTail && MODE != MODE_RS) {
+      // ---- this pair's K slice of a tail tile: add the fp32 partial into the workspace; the CTA that adds last
+      // turns the sum into C and leaves the workspace and its counter zero for the next launch.
+      int stripe, nt;
+      tileCoords<MODE>(mainTiles + tailIdx, tilesN, a.panel, stripesPerBlock, rank, n, &stripe, &nt);
+      bool good = *sFail == 0 && umma::mbarWaitParked(&tmemFull[acc], accPhase, budget);
+      if (!good && *sFail == 0) { *sFail = 1; atomicExch(a.errFlag, 24); }
+      good = !namedBarrierOr(1, 128, !good);
+      if (good) {
+        umma::tcFenceAfter();
+        float* half = a.tailWs + ((size_t)tailIdx * BM2 + (size_t)ctaRank * BM) * BN;      // this CTA's 128 rows of the tile's sum
+        float* wsRow = half + (size_t)(q * 32 + lane) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          umma::tmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u + (uint32_t)c * 32u, v);
+          umma::tmemLoadWait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) umma2::redAddF32x4(wsRow + c * 32 + j * 4, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+        umma::tcFenceBefore();
+        __threadfence();
+        int last = 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 4 && lane == 0) last = atomicAdd(&a.tailCount[tailIdx * 2 + (int)ctaRank], 1u) == (unsigned)(a.tailSlices - 1);
+        if (namedBarrierOr(1, 128, last != 0)) {
+          __threadfence();
+          const int t128 = threadIdx.x - 128, quads = BN / 4;
+          __nv_bfloat16* cBase = a.C + ((size_t)(stripe * 2 + (int)ctaRank) * BM) * (size_t)a.N + (size_t)nt * BN;
+          // Eight loads in flight per thread: with one, the 128 threads would spend the L2 latency 64 times over.
+          constexpr int U = 8;
+          float4* sum4 = reinterpret_cast<float4*>(half);
+          for (int i0 = t128; i0 < BM * quads; i0 += 128 * U) {
+            float4 x[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) { const int i = i0 + u * 128; if (i < BM * quads) x[u] = __ldcg(sum4 + i); }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int i = i0 + u * 128;
+              if (i >= BM * quads) continue;
+              __stcg(sum4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
+              const int row = i / quads, c4 = i - row * quads;
+              float4 y = x[u];
+              if (a.epilogue == EPI_SILU) { y.x = silu(y.x); y.y = silu(y.y); y.z = silu(y.z); y.w = silu(y.w); }
+              __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+              uint2 o;
+              o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+              *reinterpret_cast<uint2*>(cBase + (size_t)row * a.N + c4 * 4) = o;
+            }
+          }
+          if (t128 == 0) a.tailCount[tailIdx * 2 + (int)ctaRank] = 0u;
         }
       }
     }

@@ -69,18 +69,56 @@ int pickBN(int M, int N, int sms) {
 // Tile width of the two-SM kernel for `stripes` 256-row stripes on `pairs` SM pairs.  An MMA over 128 rows per SM
 // takes the same time for every N up to 256, so the time of a tile hardly depends on its width (a 224-wide tile
 // measured 0.965 of a 256-wide one: less operand traffic): minimise waves x tile time.
-int pickBN2(int stripes, int N, int pairs) {
+// Split tail of the two-SM kernel: with `tiles` tiles on `pairs` SM pairs, how many of the last tiles are cut along
+// K and into how many slices (0 / 0: none).  Used when the last wave would be less than half full and a slice keeps
+// at least two k blocks.
+void tailSplit(long tiles, int pairs, int kBlocks, bool allowed, int* tailTiles, int* tailSlices) {
+  *tailTiles = *tailSlices = 0;
+  static const bool on = envInt("MCCL_GEMM_SPLIT_TAIL", 1) != 0;
+  if (!allowed || !on || tiles <= pairs) return;
+  const int rem = (int)(tiles % pairs);
+  if (rem == 0 || rem * 2 > pairs) return;
+  const int slices = pairs / rem;
+  if (kBlocks / slices < 2) return;
+  *tailTiles = rem;
+  *tailSlices = slices;
+}
+
+int pickBN2(int stripes, int N, int pairs, int kBlocks = 0, bool tailAllowed = false) {
   const int cand[] = {256, 224, 192, 160, 128, 96, 64};
   int best = 0;
   double bestCost = 1e30;
   for (int bn : cand) {
     if (N % bn) continue;
     const long tiles = (long)stripes * (N / bn);
-    const long waves = (tiles + pairs - 1) / pairs;
-    const double cost = (double)waves * (0.72 + 0.28 * bn / 256.0);
+    double waves = (double)((tiles + pairs - 1) / pairs);
+    int tt, ts;
+    tailSplit(tiles, pairs, kBlocks, tailAllowed, &tt, &ts);
+    if (tt > 0) waves = (double)(tiles / pairs) + 1.0 / ts + 0.05;      // the slice wave and the fp32 fix-up
+    const double cost = waves * (0.72 + 0.28 * bn / 256.0);
     if (cost < bestCost - 1e-9) { bestCost = cost; best = bn; }
   }
   return best;
+}
+
+// fp32 workspace and arrival counters of the split tail, one per (device, stream), zero between launches.
+struct TailWs { float* ws; unsigned int* count; };
+bool tailWorkspace(int device, cudaStream_t s, TailWs* out) {
+  static std::mutex mu;
+  static std::vector<std::pair<std::pair<int, cudaStream_t>, TailWs>> all;
+  std::lock_guard<std::mutex> lk(mu);
+  for (auto& e : all) if (e.first.first == device && e.first.second == s) { *out = e.second; return true; }
+  const size_t tilesMax = 80, wsBytes = tilesMax * BM2 * 256 * sizeof(float), cntBytes = tilesMax * 2 * sizeof(unsigned int);
+  char* p = nullptr;
+  if (cudaMalloc((void**)&p, wsBytes + cntBytes) != cudaSuccess || cudaMemset(p, 0, wsBytes + cntBytes) != cudaSuccess ||
+      cudaDeviceSynchronize() != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  TailWs w{reinterpret_cast<float*>(p), reinterpret_cast<unsigned int*>(p + wsBytes)};
+  all.push_back({{device, s}, w});
+  *out = w;
+  return true;
 }
 
 int* errFlagFor(int device) {
@@ -276,7 +314,7 @@ mcclResult_t mcclTpGemm2(const void* A, const void* B, void* C, int M, int N, in
     return mcclInvalidArgument;
   }
   const int pairsMax = std::max(1, (maxCtas > 0 ? maxCtas : smCount()) / 2);
-  int bn = pickBN2(M / BM2, N, pairsMax);
+  int bn = pickBN2(M / BM2, N, pairsMax, K / BK, true);
   const int forcedBn = (int)envInt("MCCL_GEMM_BN", 0);          // tuning aid: a tile width that divides N
   if (forcedBn > 0 && N % forcedBn == 0) bn = forcedBn;
   const void* fn = nullptr;
@@ -298,6 +336,12 @@ mcclResult_t mcclTpGemm2(const void* A, const void* B, void* C, int M, int N, in
   a.debug = (int)envInt("MCCL_GEMM_DEBUG", 0);
   MCCLCHECK(makeMap(&a.mapC, C, M, N, 32));
   a.tmaStore = 1;
+  {
+    TailWs w;
+    tailSplit((long)(M / BM2) * (N / bn), pairsMax, K / BK, true, &a.tailTiles, &a.tailSlices);
+    if (a.tailTiles > 0 && a.tailTiles <= 80 && tailWorkspace(dev, reinterpret_cast<cudaStream_t>(stream), &w)) { a.tailWs = w.ws; a.tailCount = w.count; }
+    else a.tailTiles = a.tailSlices = 0;
+  }
   a.panel = pickPanel(M / BM2);
   if (envInt("MCCL_GEMM_PANEL", 0) > 0) a.panel = (int)envInt("MCCL_GEMM_PANEL", 0);
   const int tiles = (M / BM2) * (N / bn);
@@ -329,12 +373,12 @@ mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFul
   int sms = std::min(smCount(), MCCL_MAX_CTAS);
   int bn = 0;
   if (two) {
-    bn = pickBN2(M / BM2, N, sms / 2);
+    bn = pickBN2(M / BM2, N, sms / 2, K / BK, true);
     if (bn == 0 || !pairKernel<MODE_AG>(bn, &fn2, &smem2)) return mcclInvalidArgument;
     MCCLCHECK(pairPrepare(fn2, smem2));
     pairs = std::min(residentPairs(fn2, kThreadsGemm, smem2), sms / 2);
     if (pairs <= 0) return mcclSystemError;
-    if (pairs != sms / 2) bn = pickBN2(M / BM2, N, pairs);
+    if (pairs != sms / 2) bn = pickBN2(M / BM2, N, pairs, K / BK, true);
     if (bn == 0 || !pairKernel<MODE_AG>(bn, &fn2, &smem2)) return mcclInvalidArgument;
     MCCLCHECK(pairPrepare(fn2, smem2));
   } else {
@@ -348,7 +392,14 @@ mcclResult_t mcclTpAllGatherGemm(mcclComm_t comm, const void* xShard, void* xFul
   a.M = M; a.N = N; a.K = K;
   a.C = static_cast<__nv_bfloat16*>(out);
   a.epilogue = epilogue;
-  if (two) { MCCLCHECK(makeMap(&a.mapC, out, M, N, 32)); a.tmaStore = 1; }
+  if (two) {
+    MCCLCHECK(makeMap(&a.mapC, out, M, N, 32));
+    a.tmaStore = 1;
+    TailWs w;
+    tailSplit((long)(M / BM2) * (N / bn), pairs, K / BK, true, &a.tailTiles, &a.tailSlices);
+    if (a.tailTiles > 0 && a.tailTiles <= 80 && tailWorkspace(comm->device, s, &w)) { a.tailWs = w.ws; a.tailCount = w.count; }
+    else a.tailTiles = a.tailSlices = 0;
+  }
   int* hostFlag = errFlagFor(comm->device);
   if (hostFlag == nullptr || cudaHostGetDevicePointer((void**)&a.errFlag, hostFlag, 0) != cudaSuccess) return mcclSystemError;
   a.peers = comm->cu->peers;

@@ -165,10 +165,12 @@ def test_two_sm_gemm_matches_fp32_reference():
     from mccl_b200.ops import gemm as G
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
-    for (M, N, K) in [(256, 64, 64), (256, 448, 192), (1024, 3584, 1024), (512, 8192, 3584), (8192, 256, 128)]:
+    # the last two shapes leave a last wave of 4 and 8 tiles, which is cut along K over all SM pairs (split tail)
+    for (M, N, K) in [(256, 64, 64), (256, 448, 192), (1024, 3584, 1024), (512, 8192, 3584), (8192, 256, 128),
+                      (8192, 3584, 4096), (8192, 7168, 2048)]:
         x = (torch.randn(M, K, device=dev) * 0.5).to(torch.bfloat16)
         w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
-        for epi in ("none", "silu"):
+        for epi in ("none", "silu", "none"):           # the repeat reuses the split tail's workspace: it must come back clean
             y = G.gemm(x, w, epilogue=epi, two_sm=True)
             torch.cuda.synchronize()
             assert G.last_error() == 0
