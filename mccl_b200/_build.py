@@ -85,5 +85,49 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB
 
 
+def resources() -> str:
+    """Markdown table of what ptxas reported for every kernel of the last build (registers, spills, static shared
+    memory), template instantiations of one kernel folded into one row."""
+    import re
+    from collections import OrderedDict
+    found = []
+    for f in sorted(OBJ.rglob("*.ptxas.txt")):
+        entry, spill = None, ("0", "0", "0")
+        for line in f.read_text().splitlines():
+            m = re.search(r"Compiling entry function '(\S+)' for 'sm_100a'", line)
+            if m:
+                entry, spill = m.group(1), ("0", "0", "0")
+                continue
+            m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+            if m and entry:
+                spill = m.groups()
+            m = re.search(r"Used (\d+) registers", line)
+            if m and entry:
+                smem = re.search(r"(\d+) bytes smem", line)
+                found.append((f.name.replace(".ptxas.txt", ""), entry, int(m.group(1)),
+                              int(spill[1]) + int(spill[2]), int(smem.group(1)) if smem else 0))
+                entry = None
+    names = subprocess.run(["c++filt"], input="\n".join(k[1] for k in found), capture_output=True,
+                           text=True).stdout.splitlines()
+    rows: "OrderedDict[tuple, list]" = OrderedDict()
+    for k, name in zip(found, names):
+        name = name.replace("(anonymous namespace)::", "").replace("mccl::", "")
+        name = re.sub(r"^void ", "", re.sub(r"\(.*\)$", "", name))
+        base = name.split("<")[0]
+        rows.setdefault((k[0], base), []).append(k)
+    out = ["| file | kernel | instantiations | registers | spill bytes (stores + loads), worst | static smem bytes, worst |",
+           "|---|---|---|---|---|---|"]
+    for (src, base), ks in rows.items():
+        regs = [k[2] for k in ks]
+        out.append(f"| {src} | `{base}` | {len(ks)} | {min(regs)}" + (f" - {max(regs)}" if max(regs) != min(regs) else "")
+                   + f" | {max(k[3] for k in ks)} | {max(k[4] for k in ks)} |")
+    out.append("")
+    out.append(f"{len(found)} kernels in {len(rows)} families; {sum(1 for k in found if k[3])} with spills.")
+    return "\n".join(out)
+
+
 if __name__ == "__main__":
-    build(verbose=True, force="--force" in sys.argv)
+    if "--resources" in sys.argv:
+        print(resources())
+    else:
+        build(verbose=True, force="--force" in sys.argv)
