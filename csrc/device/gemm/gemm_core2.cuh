@@ -358,15 +358,18 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
       good = !namedBarrierOr(1, 128, !good);
       if (good) {
         umma::tcFenceAfter();
-        float* half = a.tailWs + ((size_t)tailIdx * BM2 + (size_t)ctaRank * BM) * BN;      // this CTA's 128 rows of the tile's sum
-        float* wsRow = half + (size_t)(q * 32 + lane) * BN;
+        // This CTA's 128 rows of the tile's sum, kept as [column quad][row][4]: the 32 lanes of one `red` (32 rows,
+        // one quad) touch 512 contiguous bytes instead of 32 rows a kilobyte apart.
+        float* half = a.tailWs + ((size_t)tailIdx * BM2 + (size_t)ctaRank * BM) * BN;
+        float* wsRow = half + (size_t)(q * 32 + lane) * 4;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
           umma::tmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u + (uint32_t)c * 32u, v);
           umma::tmemLoadWait();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) umma2::redAddF32x4(wsRow + c * 32 + j * 4, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          for (int j = 0; j < 8; ++j)
+            umma2::redAddF32x4(wsRow + (size_t)(c * 8 + j) * (BM * 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         }
         umma::tcFenceBefore();
         __threadfence();
@@ -375,30 +378,32 @@ __global__ void __launch_bounds__(MODE == MODE_PLAIN ? kThreadsGemm2 : kThreadsG
         if (warp == 4 && lane == 0) last = atomicAdd(&a.tailCount[tailIdx * 2 + (int)ctaRank], 1u) == (unsigned)(a.tailSlices - 1);
         if (namedBarrierOr(1, 128, last != 0)) {
           __threadfence();
-          const int t128 = threadIdx.x - 128, quads = BN / 4;
-          __nv_bfloat16* cBase = a.C + ((size_t)(stripe * 2 + (int)ctaRank) * BM) * (size_t)a.N + (size_t)nt * BN;
+          const int row = threadIdx.x - 128;                  // one output row per thread, 16 columns (one 32-byte sector) at a time
+          __nv_bfloat16* cRow = a.C + ((size_t)(stripe * 2 + (int)ctaRank) * BM + row) * (size_t)a.N + (size_t)nt * BN;
+          float4* sum4 = reinterpret_cast<float4*>(half) + row;
           // Eight loads in flight per thread: with one, the 128 threads would spend the L2 latency 64 times over.
-          constexpr int U = 8;
-          float4* sum4 = reinterpret_cast<float4*>(half);
-          for (int i0 = t128; i0 < BM * quads; i0 += 128 * U) {
-            float4 x[U];
+#pragma unroll 1
+          for (int c16 = 0; c16 < BN / 16; c16 += 2) {
+            float4 x[8];
 #pragma unroll
-            for (int u = 0; u < U; ++u) { const int i = i0 + u * 128; if (i < BM * quads) x[u] = __ldcg(sum4 + i); }
+            for (int u = 0; u < 8; ++u) x[u] = __ldcg(sum4 + (size_t)(c16 * 4 + u) * BM);
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const int i = i0 + u * 128;
-              if (i >= BM * quads) continue;
-              __stcg(sum4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
-              const int row = i / quads, c4 = i - row * quads;
-              float4 y = x[u];
-              if (a.epilogue == EPI_SILU) { y.x = silu(y.x); y.y = silu(y.y); y.z = silu(y.z); y.w = silu(y.w); }
-              __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
-              uint2 o;
-              o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
-              *reinterpret_cast<uint2*>(cBase + (size_t)row * a.N + c4 * 4) = o;
+            for (int u = 0; u < 8; ++u) __stcg(sum4 + (size_t)(c16 * 4 + u) * BM, make_float4(0.f, 0.f, 0.f, 0.f));
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {                     // two quads = 8 columns = one 16-byte store
+              uint32_t o[4];
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {
+                float4 y = x[h * 2 + k];
+                if (a.epilogue == EPI_SILU) { y.x = silu(y.x); y.y = silu(y.y); y.z = silu(y.z); y.w = silu(y.w); }
+                __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+                o[k * 2] = *reinterpret_cast<uint32_t*>(&lo);
+                o[k * 2 + 1] = *reinterpret_cast<uint32_t*>(&hi);
+              }
+              *reinterpret_cast<uint4*>(cRow + c16 * 16 + h * 8) = make_uint4(o[0], o[1], o[2], o[3]);
             }
           }
-          if (t128 == 0) a.tailCount[tailIdx * 2 + (int)ctaRank] = 0u;
+          if (row == 0) a.tailCount[tailIdx * 2 + (int)ctaRank] = 0u;
         }
       }
     }

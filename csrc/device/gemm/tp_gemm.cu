@@ -78,8 +78,10 @@ void tailSplit(long tiles, int pairs, int kBlocks, bool allowed, int* tailTiles,
   if (!allowed || !on || tiles <= pairs) return;
   const int rem = (int)(tiles % pairs);
   if (rem == 0 || rem * 2 > pairs) return;
-  const int slices = pairs / rem;
-  if (kBlocks / slices < 2) return;
+  int slices = pairs / rem;
+  static const int cap = (int)envInt("MCCL_GEMM_TAIL_SLICES", 0);      // tuning: at most this many slices per tile
+  if (cap > 0 && slices > cap) slices = cap;
+  if (slices < 2 || kBlocks / slices < 2) return;
   *tailTiles = rem;
   *tailSlices = slices;
 }
