@@ -62,11 +62,14 @@ mcclResult_t launched(mcclComm* c, const char* what) {
   return mcclSuccess;
 }
 
+// `maxBlocks`: 592 (four blocks per SM) fills every thread slot of the GPU, which is right for a copy that runs
+// alone; a copy meant to run BESIDE a collective takes one block per SM, or the collective's CTAs would find no
+// room until the copy has ended.
 mcclResult_t launchCopy(mcclComm* c, const void* src, void* dst, uint64_t rows, uint64_t rowBytes, uint64_t srcPitch,
-                        uint64_t dstPitch, cudaStream_t s) {
+                        uint64_t dstPitch, cudaStream_t s, int maxBlocks = 592) {
   if (rows == 0 || rowBytes == 0 || (src == dst && srcPitch == dstPitch)) return mcclSuccess;
   const uint64_t total = rows * rowBytes;
-  int blocks = (int)std::min<uint64_t>((total / 16 + kThreads - 1) / kThreads + 1, 592);
+  int blocks = (int)std::min<uint64_t>((total / 16 + kThreads - 1) / kThreads + 1, (uint64_t)maxBlocks);
   copyKernel<<<blocks, kThreads, 0, s>>>(static_cast<const char*>(src), static_cast<char*>(dst), rows, rowBytes, srcPitch, dstPitch);
   return launched(c, "copyKernel");
 }
@@ -209,6 +212,7 @@ mcclResult_t stagedPipeline(const Call& k, const void* send, void* recv, bool co
     return mcclSuccess;
   }
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(st->copyStream);
+  static const int besideBlocks = std::max(1, (int)envInt("MCCL_STAGE_COPY_CTAS", 148));
   cudaEvent_t evStart = reinterpret_cast<cudaEvent_t>(st->evStart);
   auto copied = [&](int c) { return reinterpret_cast<cudaEvent_t>(st->evCopied[c & 1]); };
   auto freed = [&](int c) { return reinterpret_cast<cudaEvent_t>(st->evFree[c & 1]); };
@@ -216,7 +220,7 @@ mcclResult_t stagedPipeline(const Call& k, const void* send, void* recv, bool co
   auto copyIn = [&](int c) -> mcclResult_t {
     const size_t off = (size_t)c * half, len = std::min(half, bytes - off);
     if (c >= 2 && !copyBack) CUDACHECK(cudaStreamWaitEvent(cs, freed(c), 0));    // the collective that read this half is done
-    MCCLCHECK(launchCopy(k.c, src + off, k.stageLocal() + (size_t)(c & 1) * half, 1, len, len, len, cs));
+    MCCLCHECK(launchCopy(k.c, src + off, k.stageLocal() + (size_t)(c & 1) * half, 1, len, len, len, cs, c == 0 ? 592 : besideBlocks));
     CUDACHECK(cudaEventRecord(copied(c), cs));
     return mcclSuccess;
   };
@@ -231,7 +235,7 @@ mcclResult_t stagedPipeline(const Call& k, const void* send, void* recv, bool co
     CUDACHECK(cudaEventRecord(freed(c), k.s));
     if (copyBack) {
       CUDACHECK(cudaStreamWaitEvent(cs, freed(c), 0));
-      MCCLCHECK(launchCopy(k.c, k.stageLocal() + (size_t)(c & 1) * half, dst + off, 1, len, len, len, cs));
+      MCCLCHECK(launchCopy(k.c, k.stageLocal() + (size_t)(c & 1) * half, dst + off, 1, len, len, len, cs, c + 1 == chunks ? 592 : besideBlocks));
     }
   }
   if (copyBack) {                                         // the caller's stream continues once the last result is out

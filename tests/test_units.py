@@ -537,3 +537,16 @@ def test_symmetric_pool_bookkeeping():
     comm.all_reduce(pool.empty(16, torch.float32).zero_())      # a pool tensor is an ordinary buffer for the collectives
     pool.destroy()
     comm.finalize(); comm.destroy()
+
+
+def test_build_resources_table_lists_every_kernel_family():
+    """The report folded from the compiler's per-kernel output names the hot kernels and reports no spills in them."""
+    from mccl_b200 import _build
+    if not any(_build.OBJ.rglob("*.ptxas.txt")):
+        pytest.skip("no compiler reports: the library was not built from source in this tree")
+    table = _build.resources()
+    rows = {line.split("|")[2].strip().strip("`"): [c.strip() for c in line.split("|")[1:-1]]
+            for line in table.splitlines() if line.startswith("| ") and "`" in line}
+    for kernel in ("gemm::tpGemm2Kernel", "nvlsKernel", "pullKernel", "oneShotKernel", "p2pKernel", "moeKernel", "adamwKernel"):
+        assert kernel in rows, kernel
+        assert rows[kernel][4] == "0", (kernel, rows[kernel])          # spill bytes
