@@ -63,8 +63,9 @@ mcclResult_t launched(mcclComm* c, const char* what) {
 }
 
 // `maxBlocks`: 592 (four blocks per SM) fills every thread slot of the GPU, which is right for a copy that runs
-// alone; a copy meant to run BESIDE a collective takes one block per SM, or the collective's CTAs would find no
-// room until the copy has ended.
+// alone; a copy meant to run BESIDE a collective takes half of the SMs, or the collective's CTAs would find no room
+// until the copy has ended (one copy block and one block of the NVLS kernel do not fit the register file of one SM
+// together: with a copy block on every SM, a 1 GB all-reduce ran at 0.78 of the symmetric path, with 74 at 0.89).
 mcclResult_t launchCopy(mcclComm* c, const void* src, void* dst, uint64_t rows, uint64_t rowBytes, uint64_t srcPitch,
                         uint64_t dstPitch, cudaStream_t s, int maxBlocks = 592) {
   if (rows == 0 || rowBytes == 0 || (src == dst && srcPitch == dstPitch)) return mcclSuccess;
@@ -212,7 +213,7 @@ mcclResult_t stagedPipeline(const Call& k, const void* send, void* recv, bool co
     return mcclSuccess;
   }
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(st->copyStream);
-  static const int besideBlocks = std::max(1, (int)envInt("MCCL_STAGE_COPY_CTAS", 148));
+  static const int besideBlocks = std::max(1, (int)envInt("MCCL_STAGE_COPY_CTAS", 74));
   cudaEvent_t evStart = reinterpret_cast<cudaEvent_t>(st->evStart);
   auto copied = [&](int c) { return reinterpret_cast<cudaEvent_t>(st->evCopied[c & 1]); };
   auto freed = [&](int c) { return reinterpret_cast<cudaEvent_t>(st->evFree[c & 1]); };
