@@ -1155,7 +1155,7 @@ mcclResult_t cudaP2pBatch(mcclComm* c, const std::vector<P2pOp>& ops, mcclStream
     if (selfS[i]->bytes != selfR[i]->bytes) MCCLFAIL(mcclInvalidUsage);
     MCCLCHECK(launchCopy(c, selfS[i]->buf, selfR[i]->buf, 1, selfS[i]->bytes, selfS[i]->bytes, selfS[i]->bytes, s));
   }
-  // One CTA per (peer, direction) flow, all flows of the batch in ONE launch (two launches in a row could wait for
+  // One row of MCCL_P2P_CHANNELS CTAs per (peer, direction) flow, all flows of the batch in ONE launch (two launches in a row could wait for
   // each other across ranks).  The descriptors travel as kernel arguments; a batch longer than that holds goes
   // through stream-ordered device memory.
   std::vector<P2pDesc> descs;
@@ -1186,7 +1186,7 @@ mcclResult_t cudaP2pBatch(mcclComm* c, const std::vector<P2pOp>& ops, mcclStream
     CUDACHECK(cudaMemcpyAsync(devDescs, descs.data(), descs.size() * sizeof(P2pDesc), cudaMemcpyHostToDevice, s));
     a.more = static_cast<const P2pDesc*>(devDescs);
   }
-  p2pKernel<<<flows, kThreads, 0, s>>>(a);
+  p2pKernel<<<dim3(flows, p2pChannels(c->nRanks)), kThreads, 0, s>>>(a);
   mcclResult_t rc = launched(c, "p2pKernel");
   if (devDescs) {
     CUDACHECK(cudaFreeAsync(devDescs, s));

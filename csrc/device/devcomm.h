@@ -9,6 +9,7 @@
 #include <stdint.h>
 
 #define MCCL_MAX_RANKS 16      // ranks of one NVSwitch domain a kernel can address
+#define MCCL_P2P_CHANNELS 32   // most CTAs that share one Send/Recv message (each with its own part of the FIFO slot)
 #define MCCL_MAX_CTAS 160      // upper bound on CTAs ("channels") of one collective kernel
 #define MCCL_COLL_THREADS 512
 #define MCCL_ONESHOT_MAX_CTAS 8   // the one-shot kernel never runs more CTAs: its call counters are kept equal over this many
@@ -45,12 +46,13 @@ struct CtrlFlags {
   // oneShotCalls[cta]: one-shot calls made so far.  Every launch leaves the first MCCL_ONESHOT_MAX_CTAS entries
   // equal, whatever its grid, so the slot half a call uses (its parity) is the same for every CTA.
   uint64_t oneShotCalls[MCCL_MAX_CTAS];
-  // Send/Recv FIFOs: head[src] = chunks rank `src` has written into my slot; tail[dst] = chunks rank
-  // `dst` has drained from its slot for me.  sent/recvd are this rank's own running totals.
-  uint64_t p2pHead[MCCL_MAX_RANKS];
-  uint64_t p2pTail[MCCL_MAX_RANKS];
-  uint64_t p2pSent[MCCL_MAX_RANKS];
-  uint64_t p2pRecvd[MCCL_MAX_RANKS];
+  // Send/Recv FIFOs, one per (peer, channel): head[src][ch] = chunks rank `src` has written into channel `ch` of
+  // my slot; tail[dst][ch] = chunks rank `dst` has drained from its slot for me.  sent/recvd are this rank's own
+  // running totals.
+  uint64_t p2pHead[MCCL_MAX_RANKS][MCCL_P2P_CHANNELS];
+  uint64_t p2pTail[MCCL_MAX_RANKS][MCCL_P2P_CHANNELS];
+  uint64_t p2pSent[MCCL_MAX_RANKS][MCCL_P2P_CHANNELS];
+  uint64_t p2pRecvd[MCCL_MAX_RANKS][MCCL_P2P_CHANNELS];
   // note[cta]: a word the root of a rooted collective publishes before the entry barrier of a call and its
   // peers read after it (which form of the algorithm the root can take part in).
   uint64_t note[MCCL_MAX_CTAS];
@@ -216,6 +218,11 @@ struct P2pArgs {
   const P2pDesc* more;             // batches longer than MCCL_MAX_P2P_OPS: all descriptors, in device memory
   P2pDesc ops[MCCL_MAX_P2P_OPS];
 };
+
+// Send/Recv channels per flow for a communicator of n ranks: every CTA of a batch (2 (n - 1) flows at most) must fit
+// the GPU at the same time, because a sender's CTAs wait for the peer's receiving CTAs and the other way round.
+// 2 x 32, 6 x 16, 14 x 8 and 30 x 4 CTAs all fit 148 SMs at one CTA per SM.
+MCCL_HD inline int p2pChannels(int n) { return n <= 2 ? 32 : n <= 4 ? 16 : n <= 8 ? 8 : 4; }
 
 // Shard r of a message of `bytes` bytes cut into n shards on 16-byte boundaries; the last shard takes the tail.
 MCCL_HD inline uint64_t shardOff(uint64_t bytes, int n, int r) { return (uint64_t)(((unsigned __int128)(bytes / 16) * (unsigned)r) / (unsigned)n) * 16; }

@@ -538,12 +538,51 @@ static __global__ void __launch_bounds__(kThreads, 1) groupAllReduceKernel(const
 }
 
 // ---- Send / Recv -------------------------------------------------------------------------------------------------
-// One CTA per flow (peer, direction); ops of a flow run in order.  The sender writes chunks into the
-// receiver's slot (two halves) and publishes a running chunk count; the receiver drains and acknowledges.
+// One row of CTAs per flow (peer, direction), MCCL_P2P_CHANNELS CTAs in the row; ops of a flow run in order.  A
+// message is cut into one contiguous part per channel (how many channels and where the cuts are depends on the
+// message size and the slot size only, so sender and receiver agree without talking).  In its channel the sender
+// writes chunks into its part of the receiver's slot (two halves) and publishes a running chunk count; the
+// receiver drains and acknowledges.  Copies keep eight 16-byte pieces in flight per thread.
+struct P2pSplit { int channels; uint64_t per; uint64_t half; };
+
+__device__ __forceinline__ P2pSplit p2pSplit(uint64_t bytes, uint64_t slotBytes, int n) {
+  P2pSplit sp;
+  int maxCh = p2pChannels(n);
+  sp.half = slotBytes / (2 * (uint64_t)maxCh) / 16 * 16;
+  if (sp.half < 4096) { sp.half = slotBytes / 2 / 16 * 16; maxCh = 1; }      // a slot too small to share
+  const uint64_t want = (bytes + (64u << 10) - 1) / (64u << 10);              // at least 64 KB per channel
+  sp.channels = (int)(want < (uint64_t)maxCh ? (want > 0 ? want : 1) : (uint64_t)maxCh);
+  sp.per = ((bytes + sp.channels - 1) / sp.channels + 255) / 256 * 256;
+  return sp;
+}
+
+template <bool REMOTE_LOAD, bool REMOTE_STORE>
+__device__ __forceinline__ void p2pCopy16(const char* src, char* dst, uint64_t vecs, int tid) {
+  constexpr int U = 8;
+  uint64_t i = tid;
+  for (; i + (uint64_t)(U - 1) * kThreads < vecs; i += (uint64_t)U * kThreads) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const char* p = src + (i + (uint64_t)u * kThreads) * 16;
+      v[u] = REMOTE_LOAD ? ldSys128(p) : ldLocal128(p);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      char* p = dst + (i + (uint64_t)u * kThreads) * 16;
+      if (REMOTE_STORE) stSys128(p, v[u]); else stLocal128(p, v[u]);
+    }
+  }
+  for (; i < vecs; i += kThreads) {
+    const uint4 v = REMOTE_LOAD ? ldSys128(src + i * 16) : ldLocal128(src + i * 16);
+    if (REMOTE_STORE) stSys128(dst + i * 16, v); else stLocal128(dst + i * 16, v);
+  }
+}
+
 static __global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_constant__ P2pArgs a) {
   __shared__ int sFail;
   const DevPeers& P = a.peers;
-  const int tid = threadIdx.x, me = P.rank;
+  const int tid = threadIdx.x, me = P.rank, ch = blockIdx.y;
   if (tid == 0) sFail = 0;
   __syncthreads();
   CtrlFlags* mine = flagsOf(P, me);
@@ -553,48 +592,48 @@ static __global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_con
     if ((op.isSend >> 1) != (int)blockIdx.x) continue;
     const bool isSend = op.isSend & 1;
     const int peer = op.peer;
-    const uint64_t half = P.layout.p2pSlotBytes / 2;
-    const uint64_t nChunks = (op.bytes + half - 1) / half;
+    const P2pSplit sp = p2pSplit(op.bytes, P.layout.p2pSlotBytes, P.n);
+    const uint64_t lo = (uint64_t)ch * sp.per;
+    if (ch >= sp.channels || lo >= op.bytes) continue;                       // this channel carries nothing of this message
+    const uint64_t part = min(sp.per, op.bytes - lo), half = sp.half;
+    const uint64_t nChunks = (part + half - 1) / half;
+    const uint64_t chanOff = (uint64_t)ch * 2 * half;
     if (isSend) {
-      uint64_t sent = mine->p2pSent[peer];
-      char* slot = P.ctrl[peer] + P.layout.p2pOff + (uint64_t)me * P.layout.p2pSlotBytes;
+      uint64_t sent = mine->p2pSent[peer][ch];
+      char* slot = P.ctrl[peer] + P.layout.p2pOff + (uint64_t)me * P.layout.p2pSlotBytes + chanOff;
       for (uint64_t c = 0; c < nChunks && sFail == 0; ++c) {
         const uint64_t seq = sent + c + 1;
-        if (tid == 0 && seq > 2 && !waitFlag(&mine->p2pTail[peer], seq - 2, P, 2u, peer, (int)c)) sFail = 1;
+        if (tid == 0 && seq > 2 && !waitFlag(&mine->p2pTail[peer][ch], seq - 2, P, 2u, peer, (int)c)) sFail = 1;
         __syncthreads();
         if (sFail) break;
-        const uint64_t off = c * half, len = min(half, op.bytes - off);
+        const uint64_t off = c * half, len = min(half, part - off);
         char* dst = slot + (seq & 1) * half;
-        const char* src = op.buf + off;
-        if (aligned16(src) && (len & 15) == 0) {
-          for (uint64_t i = tid; i < len / 16; i += kThreads) stSys128(dst + i * 16, ldLocal128(src + i * 16));
-        } else {
-          for (uint64_t i = tid; i < len; i += kThreads) dst[i] = src[i];
-        }
+        const char* src = op.buf + lo + off;
+        const uint64_t vec = aligned16(src) ? len / 16 : 0;               // the slot itself is always aligned
+        p2pCopy16<false, true>(src, dst, vec, tid);
+        for (uint64_t i = vec * 16 + tid; i < len; i += kThreads) dst[i] = src[i];
         __syncthreads();
-        if (tid == 0) { __threadfence_system(); stReleaseSys(&flagsOf(P, peer)->p2pHead[me], seq); }
+        if (tid == 0) { __threadfence_system(); stReleaseSys(&flagsOf(P, peer)->p2pHead[me][ch], seq); }
       }
-      if (tid == 0) mine->p2pSent[peer] = sent + nChunks;
+      if (tid == 0) mine->p2pSent[peer][ch] = sent + nChunks;
     } else {
-      uint64_t got = mine->p2pRecvd[peer];
-      const char* slot = P.ctrl[me] + P.layout.p2pOff + (uint64_t)peer * P.layout.p2pSlotBytes;
+      uint64_t got = mine->p2pRecvd[peer][ch];
+      const char* slot = P.ctrl[me] + P.layout.p2pOff + (uint64_t)peer * P.layout.p2pSlotBytes + chanOff;
       for (uint64_t c = 0; c < nChunks && sFail == 0; ++c) {
         const uint64_t seq = got + c + 1;
-        if (tid == 0 && !waitFlag(&mine->p2pHead[peer], seq, P, 2u, peer, (int)c)) sFail = 1;
+        if (tid == 0 && !waitFlag(&mine->p2pHead[peer][ch], seq, P, 2u, peer, (int)c)) sFail = 1;
         __syncthreads();
         if (sFail) break;
-        const uint64_t off = c * half, len = min(half, op.bytes - off);
+        const uint64_t off = c * half, len = min(half, part - off);
         const char* src = slot + (seq & 1) * half;
-        char* dst = op.buf + off;
-        if (aligned16(dst) && (len & 15) == 0) {
-          for (uint64_t i = tid; i < len / 16; i += kThreads) stLocal128(dst + i * 16, ldSys128(src + i * 16));
-        } else {
-          copyBytes(src, dst, 0, len, tid, kThreads);
-        }
+        char* dst = op.buf + lo + off;
+        const uint64_t vec = aligned16(dst) ? len / 16 : 0;
+        p2pCopy16<true, false>(src, dst, vec, tid);
+        copyBytes(src, dst, vec * 16, len, tid, kThreads);
         __syncthreads();
-        if (tid == 0) { __threadfence_system(); stReleaseSys(&flagsOf(P, peer)->p2pTail[me], seq); }
+        if (tid == 0) { __threadfence_system(); stReleaseSys(&flagsOf(P, peer)->p2pTail[me][ch], seq); }
       }
-      if (tid == 0) mine->p2pRecvd[peer] = got + nChunks;
+      if (tid == 0) mine->p2pRecvd[peer][ch] = got + nChunks;
     }
     __syncthreads();
   }
@@ -609,7 +648,8 @@ static __global__ void recvAnyProbeKernel(DevPeers P, int* out) {
   for (;;) {
     for (int p = 0; p < P.n; ++p) {
       if (p == P.rank) continue;
-      if (ldAcquireSys(&mine->p2pHead[p]) > mine->p2pRecvd[p]) { *out = p; __threadfence_system(); return; }
+      if (ldAcquireSys(&mine->p2pHead[p][0]) > mine->p2pRecvd[p][0]) { *out = p;   // channel 0 carries a part of every message
+        __threadfence_system(); return; }
     }
     if (P.status->abort != 0 || globalTimerNs() - t0 > P.timeoutNs) { *out = -1; __threadfence_system(); return; }
   }
