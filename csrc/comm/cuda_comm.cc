@@ -15,7 +15,7 @@ namespace mccl {
 DEFINE_MCCL_PARAM(DeviceTimeoutMs, "DEVICE_TIMEOUT_MS", 10000);
 DEFINE_MCCL_PARAM(StageMb, "STAGE_MB", 256);
 DEFINE_MCCL_PARAM(OneShotSlotKb, "ONESHOT_SLOT_KB", 1024);
-DEFINE_MCCL_PARAM(P2pSlotKb, "P2P_SLOT_KB", 0);      // 0: two 256 KB halves per channel
+DEFINE_MCCL_PARAM(P2pSlotKb, "P2P_SLOT_KB", 0);      // 0: MCCL_P2P_DEPTH chunks of 512 KB per channel
 DEFINE_MCCL_PARAM(NvlsEnable, "NVLS_ENABLE", 1);
 
 mcclResult_t cudaFillRankInfo(int device, RankInfo* ri) {
@@ -103,7 +103,7 @@ mcclResult_t cudaCommInit(mcclComm* c) {
   L.flagsOff = 0;
   L.oneShotSlotBytes = (uint64_t)mcclParamOneShotSlotKb() * 1024;
   L.oneShotOff = alignUp(sizeof(CtrlFlags), 4096);
-  L.p2pSlotBytes = mcclParamP2pSlotKb() > 0 ? (uint64_t)mcclParamP2pSlotKb() * 1024 : (uint64_t)p2pChannels(c->nRanks) * (512u << 10);
+  L.p2pSlotBytes = mcclParamP2pSlotKb() > 0 ? (uint64_t)mcclParamP2pSlotKb() * 1024 : (uint64_t)p2pChannels(c->nRanks) * MCCL_P2P_DEPTH * (512u << 10);
   L.p2pOff = L.oneShotOff + 2 * (uint64_t)c->nRanks * L.oneShotSlotBytes;
   L.stageOff = alignUp(L.p2pOff + (uint64_t)c->nRanks * L.p2pSlotBytes, 1u << 21);
   L.stageBytes = (uint64_t)mcclParamStageMb() << 20;

@@ -9,6 +9,7 @@
 #include <stdint.h>
 
 #define MCCL_MAX_RANKS 16      // ranks of one NVSwitch domain a kernel can address
+#define MCCL_P2P_DEPTH 4       // chunks of a Send/Recv channel's ring in the receiver's memory
 #define MCCL_P2P_CHANNELS 32   // most CTAs that share one Send/Recv message (each with its own part of the FIFO slot)
 #define MCCL_MAX_CTAS 160      // upper bound on CTAs ("channels") of one collective kernel
 #define MCCL_COLL_THREADS 512
@@ -69,7 +70,7 @@ struct CtrlLayout {
   uint64_t flagsOff;
   uint64_t oneShotOff;      // 2 buffers x n ranks x oneShotSlotBytes
   uint64_t oneShotSlotBytes;
-  uint64_t p2pOff;          // n ranks x p2pSlotBytes (two halves each)
+  uint64_t p2pOff;          // n ranks x p2pSlotBytes (channels x MCCL_P2P_DEPTH chunks each)
   uint64_t p2pSlotBytes;
   uint64_t stageOff;        // staging area for buffers that are not symmetric
   uint64_t stageBytes;
@@ -221,8 +222,8 @@ struct P2pArgs {
 
 // Send/Recv channels per flow for a communicator of n ranks: every CTA of a batch (2 (n - 1) flows at most) must fit
 // the GPU at the same time, because a sender's CTAs wait for the peer's receiving CTAs and the other way round.
-// 2 x 32, 6 x 16, 14 x 8 and 30 x 4 CTAs all fit 148 SMs at one CTA per SM.
-MCCL_HD inline int p2pChannels(int n) { return n <= 2 ? 32 : n <= 4 ? 16 : n <= 8 ? 8 : 4; }
+// 4 x 32, 6 x 20, 14 x 8 and 30 x 4 CTAs all fit 148 SMs at one CTA per SM.
+MCCL_HD inline int p2pChannels(int n) { return n <= 3 ? 32 : n == 4 ? 20 : n <= 8 ? 8 : 4; }
 
 // Shard r of a message of `bytes` bytes cut into n shards on 16-byte boundaries; the last shard takes the tail.
 MCCL_HD inline uint64_t shardOff(uint64_t bytes, int n, int r) { return (uint64_t)(((unsigned __int128)(bytes / 16) * (unsigned)r) / (unsigned)n) * 16; }

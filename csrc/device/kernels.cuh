@@ -541,15 +541,16 @@ static __global__ void __launch_bounds__(kThreads, 1) groupAllReduceKernel(const
 // One row of CTAs per flow (peer, direction), MCCL_P2P_CHANNELS CTAs in the row; ops of a flow run in order.  A
 // message is cut into one contiguous part per channel (how many channels and where the cuts are depends on the
 // message size and the slot size only, so sender and receiver agree without talking).  In its channel the sender
-// writes chunks into its part of the receiver's slot (two halves) and publishes a running chunk count; the
-// receiver drains and acknowledges.  Copies keep eight 16-byte pieces in flight per thread.
-struct P2pSplit { int channels; uint64_t per; uint64_t half; };
+// writes chunks into its part of the receiver's slot (a ring of MCCL_P2P_DEPTH chunks, so that the round trip of
+// an acknowledgement is hidden behind the chunks in flight) and publishes a running chunk count; the receiver
+// drains and acknowledges.  Copies keep eight 16-byte pieces in flight per thread.
+struct P2pSplit { int channels; uint64_t per; uint64_t half; };      // half: bytes of one chunk of the ring
 
 __device__ __forceinline__ P2pSplit p2pSplit(uint64_t bytes, uint64_t slotBytes, int n) {
   P2pSplit sp;
   int maxCh = p2pChannels(n);
-  sp.half = slotBytes / (2 * (uint64_t)maxCh) / 16 * 16;
-  if (sp.half < 4096) { sp.half = slotBytes / 2 / 16 * 16; maxCh = 1; }      // a slot too small to share
+  sp.half = slotBytes / (MCCL_P2P_DEPTH * (uint64_t)maxCh) / 16 * 16;
+  if (sp.half < 4096) { sp.half = slotBytes / MCCL_P2P_DEPTH / 16 * 16; maxCh = 1; }      // a slot too small to share
   const uint64_t want = (bytes + (64u << 10) - 1) / (64u << 10);              // at least 64 KB per channel
   sp.channels = (int)(want < (uint64_t)maxCh ? (want > 0 ? want : 1) : (uint64_t)maxCh);
   sp.per = ((bytes + sp.channels - 1) / sp.channels + 255) / 256 * 256;
@@ -597,23 +598,23 @@ static __global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_con
     if (ch >= sp.channels || lo >= op.bytes) continue;                       // this channel carries nothing of this message
     const uint64_t part = min(sp.per, op.bytes - lo), half = sp.half;
     const uint64_t nChunks = (part + half - 1) / half;
-    const uint64_t chanOff = (uint64_t)ch * 2 * half;
+    const uint64_t chanOff = (uint64_t)ch * MCCL_P2P_DEPTH * half;
     if (isSend) {
       uint64_t sent = mine->p2pSent[peer][ch];
       char* slot = P.ctrl[peer] + P.layout.p2pOff + (uint64_t)me * P.layout.p2pSlotBytes + chanOff;
       for (uint64_t c = 0; c < nChunks && sFail == 0; ++c) {
         const uint64_t seq = sent + c + 1;
-        if (tid == 0 && seq > 2 && !waitFlag(&mine->p2pTail[peer][ch], seq - 2, P, 2u, peer, (int)c)) sFail = 1;
+        if (tid == 0 && seq > MCCL_P2P_DEPTH && !waitFlag(&mine->p2pTail[peer][ch], seq - MCCL_P2P_DEPTH, P, 2u, peer, (int)c)) sFail = 1;
         __syncthreads();
         if (sFail) break;
         const uint64_t off = c * half, len = min(half, part - off);
-        char* dst = slot + (seq & 1) * half;
+        char* dst = slot + (seq % MCCL_P2P_DEPTH) * half;
         const char* src = op.buf + lo + off;
         const uint64_t vec = aligned16(src) ? len / 16 : 0;               // the slot itself is always aligned
         p2pCopy16<false, true>(src, dst, vec, tid);
         for (uint64_t i = vec * 16 + tid; i < len; i += kThreads) dst[i] = src[i];
         __syncthreads();
-        if (tid == 0) { __threadfence_system(); stReleaseSys(&flagsOf(P, peer)->p2pHead[me][ch], seq); }
+        if (tid == 0) stReleaseSys(&flagsOf(P, peer)->p2pHead[me][ch], seq);       // the release orders the CTA's stores (seen through the barrier) before the count
       }
       if (tid == 0) mine->p2pSent[peer][ch] = sent + nChunks;
     } else {
@@ -625,13 +626,13 @@ static __global__ void __launch_bounds__(kThreads, 1) p2pKernel(const __grid_con
         __syncthreads();
         if (sFail) break;
         const uint64_t off = c * half, len = min(half, part - off);
-        const char* src = slot + (seq & 1) * half;
+        const char* src = slot + (seq % MCCL_P2P_DEPTH) * half;
         char* dst = op.buf + lo + off;
         const uint64_t vec = aligned16(dst) ? len / 16 : 0;
         p2pCopy16<true, false>(src, dst, vec, tid);
         copyBytes(src, dst, vec * 16, len, tid, kThreads);
         __syncthreads();
-        if (tid == 0) { __threadfence_system(); stReleaseSys(&flagsOf(P, peer)->p2pTail[me][ch], seq); }
+        if (tid == 0) stReleaseSys(&flagsOf(P, peer)->p2pTail[me][ch], seq);
       }
       if (tid == 0) mine->p2pRecvd[peer][ch] = got + nChunks;
     }
