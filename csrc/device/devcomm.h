@@ -225,6 +225,23 @@ struct P2pArgs {
 // 4 x 32, 6 x 20, 14 x 8 and 30 x 4 CTAs all fit 148 SMs at one CTA per SM.
 MCCL_HD inline int p2pChannels(int n) { return n <= 3 ? 32 : n == 4 ? 20 : n <= 8 ? 8 : 4; }
 
+// How one Send/Recv message of `bytes` bytes is cut: `channels` contiguous parts of `per` bytes (the last one takes
+// what is left), each moved in chunks of `chunk` bytes through its channel's ring of MCCL_P2P_DEPTH chunks.  A pure
+// function of the message size, the slot size and the communicator's size, so sender and receiver agree without
+// talking; at least 64 KB per channel.
+struct P2pSplit { int channels; uint64_t per; uint64_t half; };      // half: bytes of one chunk of the ring
+
+MCCL_HD inline P2pSplit p2pSplit(uint64_t bytes, uint64_t slotBytes, int n) {
+  P2pSplit sp;
+  int maxCh = p2pChannels(n);
+  sp.half = slotBytes / (MCCL_P2P_DEPTH * (uint64_t)maxCh) / 16 * 16;
+  if (sp.half < 4096) { sp.half = slotBytes / MCCL_P2P_DEPTH / 16 * 16; maxCh = 1; }      // a slot too small to share
+  const uint64_t want = (bytes + (64u << 10) - 1) / (64u << 10);
+  sp.channels = (int)(want < (uint64_t)maxCh ? (want > 0 ? want : 1) : (uint64_t)maxCh);
+  sp.per = ((bytes + sp.channels - 1) / sp.channels + 255) / 256 * 256;
+  return sp;
+}
+
 // Shard r of a message of `bytes` bytes cut into n shards on 16-byte boundaries; the last shard takes the tail.
 MCCL_HD inline uint64_t shardOff(uint64_t bytes, int n, int r) { return (uint64_t)(((unsigned __int128)(bytes / 16) * (unsigned)r) / (unsigned)n) * 16; }
 MCCL_HD inline uint64_t shardEnd(uint64_t bytes, int n, int r) { return r == n - 1 ? bytes : shardOff(bytes, n, r + 1); }

@@ -544,19 +544,6 @@ static __global__ void __launch_bounds__(kThreads, 1) groupAllReduceKernel(const
 // writes chunks into its part of the receiver's slot (a ring of MCCL_P2P_DEPTH chunks, so that the round trip of
 // an acknowledgement is hidden behind the chunks in flight) and publishes a running chunk count; the receiver
 // drains and acknowledges.  Copies keep eight 16-byte pieces in flight per thread.
-struct P2pSplit { int channels; uint64_t per; uint64_t half; };      // half: bytes of one chunk of the ring
-
-__device__ __forceinline__ P2pSplit p2pSplit(uint64_t bytes, uint64_t slotBytes, int n) {
-  P2pSplit sp;
-  int maxCh = p2pChannels(n);
-  sp.half = slotBytes / (MCCL_P2P_DEPTH * (uint64_t)maxCh) / 16 * 16;
-  if (sp.half < 4096) { sp.half = slotBytes / MCCL_P2P_DEPTH / 16 * 16; maxCh = 1; }      // a slot too small to share
-  const uint64_t want = (bytes + (64u << 10) - 1) / (64u << 10);              // at least 64 KB per channel
-  sp.channels = (int)(want < (uint64_t)maxCh ? (want > 0 ? want : 1) : (uint64_t)maxCh);
-  sp.per = ((bytes + sp.channels - 1) / sp.channels + 255) / 256 * 256;
-  return sp;
-}
-
 template <bool REMOTE_LOAD, bool REMOTE_STORE>
 __device__ __forceinline__ void p2pCopy16(const char* src, char* dst, uint64_t vecs, int tid) {
   constexpr int U = 8;

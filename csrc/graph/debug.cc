@@ -5,6 +5,7 @@
 #include <cstring>
 #include <vector>
 
+#include "../device/devcomm.h"
 #include "../device/host_reduce.h"
 #include "graph.h"
 
@@ -128,6 +129,13 @@ mcclResult_t mcclDbgXmlRoundTrip(const char* text, char** out) {
 }
 
 int64_t mcclDbgParam(const char* env, int64_t deflt) { return loadParam(env, deflt); }
+
+// The cut of a Send/Recv message over channels: out3 = {channels, bytes per channel, bytes per chunk}.
+void mcclDbgP2pSplit(uint64_t bytes, uint64_t slotBytes, int n, uint64_t* out3) {
+  const P2pSplit sp = p2pSplit(bytes, slotBytes, n);
+  out3[0] = (uint64_t)sp.channels; out3[1] = sp.per; out3[2] = sp.half;
+}
+int mcclDbgP2pChannels(int n) { return p2pChannels(n); }
 
 // Path table of a synthetic cuda system with the (cutA, cutB) NVLink pair severed.
 // types[a*n+b] = path type, hops[a*n+b] = hop count.

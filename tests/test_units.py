@@ -550,3 +550,40 @@ def test_build_resources_table_lists_every_kernel_family():
     for kernel in ("gemm::tpGemm2Kernel", "nvlsKernel", "pullKernel", "oneShotKernel", "p2pKernel", "moeKernel", "adamwKernel"):
         assert kernel in rows, kernel
         assert rows[kernel][4] == "0", (kernel, rows[kernel])          # spill bytes
+
+
+def test_send_recv_split_over_channels_tiles_every_message(lib):
+    """Sender and receiver compute the cut of a message from (bytes, slot size, ranks) alone: the parts must tile
+    the message exactly, every chunk must fit its channel's ring, and all CTAs of a full batch (one row of
+    channels per direction and peer) must fit the 148 SMs at once, because they wait for one another across GPUs."""
+    lib.mcclDbgP2pSplit.argtypes = [C.c_uint64, C.c_uint64, C.c_int, C.POINTER(C.c_uint64)]
+    lib.mcclDbgP2pSplit.restype = None
+    lib.mcclDbgP2pChannels.argtypes = [C.c_int]
+    lib.mcclDbgP2pChannels.restype = C.c_int
+    depth = 4
+    rng = np.random.default_rng(7)
+    for n in (2, 3, 4, 5, 8, 16):
+        ch_max = lib.mcclDbgP2pChannels(n)
+        assert 1 <= ch_max <= 32
+        assert 2 * (n - 1) * ch_max <= 148
+        default_slot = ch_max * depth * (512 << 10)
+        for slot in (default_slot, 4096 << 10, 64 << 10, 16 << 10):
+            sizes = [1, 13, 4096, 65536, 65537, (1 << 20) + 13, (5 << 20) + 4099, 256 << 20, (1 << 32) + 48]
+            sizes += [int(x) for x in rng.integers(1, 1 << 28, size=40)]
+            for nbytes in sizes:
+                out = (C.c_uint64 * 3)()
+                lib.mcclDbgP2pSplit(nbytes, slot, n, out)
+                channels, per, chunk = int(out[0]), int(out[1]), int(out[2])
+                assert 1 <= channels <= ch_max
+                assert per % 256 == 0 and chunk % 16 == 0 and chunk >= 16
+                assert channels * depth * chunk <= slot                      # every channel's ring lies inside the slot
+                covered = 0
+                for ch in range(channels):
+                    lo = ch * per
+                    if lo >= nbytes:
+                        continue
+                    covered += min(per, nbytes - lo)
+                assert covered == nbytes, (n, slot, nbytes, channels, per)
+                assert (channels - 1) * per < nbytes or channels == 1       # no channel starts beyond the end ...
+                if nbytes >= channels * (64 << 10):
+                    assert per >= 64 << 10                                   # ... and none carries a sliver of a large message
