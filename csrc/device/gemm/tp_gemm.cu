@@ -108,6 +108,12 @@ struct TailWs { float* ws; unsigned int* count; };
 bool tailWorkspace(int device, cudaStream_t s, TailWs* out) {
   static std::mutex mu;
   static std::vector<std::pair<std::pair<int, cudaStream_t>, TailWs>> all;
+  // A launch that is being recorded into a CUDA graph keeps whole tiles: the workspace belongs to a stream, and a
+  // graph's kernels run wherever the graph is replayed, possibly beside a launch that uses the same workspace;
+  // nor may memory be allocated and the device synchronised while a stream records.
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess) { cudaGetLastError(); return false; }
+  if (capturing != cudaStreamCaptureStatusNone) return false;
   std::lock_guard<std::mutex> lk(mu);
   for (auto& e : all) if (e.first.first == device && e.first.second == s) { *out = e.second; return true; }
   const size_t tilesMax = 80, wsBytes = tilesMax * BM2 * 256 * sizeof(float), cntBytes = tilesMax * 2 * sizeof(unsigned int);
