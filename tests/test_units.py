@@ -587,3 +587,44 @@ def test_send_recv_split_over_channels_tiles_every_message(lib):
                 assert (channels - 1) * per < nbytes or channels == 1       # no channel starts beyond the end ...
                 if nbytes >= channels * (64 << 10):
                     assert per >= 64 << 10                                   # ... and none carries a sliver of a large message
+
+
+def test_collective_matrix_oracle_is_position_addressable_and_exact():
+    """The checker of bench/coll_matrix.py: a window of a rank's input computed on its own equals the same slice of
+    the whole input, the reference equals a plain reduction of all ranks' inputs, the windows cover start, middle and
+    end, and the grading tells an exact result from a rounded one and from a wrong one."""
+    import importlib.util
+    import torch
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench", "coll_matrix.py")
+    spec = importlib.util.spec_from_file_location("coll_matrix_under_test", path)
+    cm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cm)
+    dev = torch.device("cpu")
+    n, world = 5000, 4
+    for dname, dt in cm.DT.items():
+        for op in ("sum", "prod", "max", "min", "avg"):
+            whole = [cm.values(r, 0, n, dt, op, dev) for r in range(world)]
+            assert whole[0].dtype == dt
+            assert torch.equal(cm.values(2, 1234, 1300, dt, op, dev), whole[2][1234:1300])
+            assert not torch.equal(whole[0], whole[1])                       # ranks differ
+            ref = cm.reference(world, 100, 400, dt, op, dev)
+            st = torch.stack([w[100:400].double() if dt.is_floating_point else w[100:400].long() for w in whole])
+            if op == "sum":
+                want = st.sum(0)
+            elif op == "avg":
+                want = st.sum(0) / world if dt.is_floating_point else torch.div(st.sum(0).to(dt), world, rounding_mode="trunc")
+            elif op == "prod":
+                want = st.prod(0)
+            else:
+                want = st.max(0).values if op == "max" else st.min(0).values
+            assert torch.equal(ref.double(), want.double()), (dname, op)
+    assert cm.windows(10) == [(0, 10)]
+    big = 10 * cm.WINDOW + 3
+    w = cm.windows(big)
+    assert w[0] == (0, cm.WINDOW) and w[-1] == (big - cm.WINDOW, big) and w[1][0] % 8 == 0 and w[1][1] - w[1][0] == cm.WINDOW
+    want = torch.tensor([1.0, 2.0, 3.0], dtype=torch.float64) / 3
+    assert cm.grade(want.to(torch.bfloat16), want, torch.bfloat16) == "exact"
+    assert cm.grade((want * (1 + 1e-2)).to(torch.bfloat16), want, torch.bfloat16) == "close"
+    assert cm.grade((want + 1.0).to(torch.bfloat16), want, torch.bfloat16) == "WRONG"
+    ints = torch.tensor([1, -2, 3], dtype=torch.int32)
+    assert cm.grade(ints, ints.long(), torch.int32) == "exact" and cm.grade(ints + 1, ints.long(), torch.int32) == "WRONG"
